@@ -1,0 +1,78 @@
+"""Build the native parts in-tree (no JIT cache, the .so files sit beside the sources).
+
+    python build.py            # everything
+    python build.py --force    # rebuild even if up to date
+
+  libgputok_b200.so   CUDA kernels + C ABI (nvcc, sm_100a only)
+  libgtk_textgen.so   seeded synthetic text generator (gcc, CPU only)
+  gputok_gpu*.so      pybind11 module exposing the reference's GpuTokenizer surface (g++)
+"""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+import sysconfig
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+INCLUDE = os.path.join(os.path.dirname(HERE), "include")
+
+LIB = os.path.join(HERE, "libgputok_b200.so")
+TEXTGEN = os.path.join(HERE, "libgtk_textgen.so")
+PYMOD = os.path.join(HERE, "gputok_gpu" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
+
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared"]
+
+
+def _stale(target: str, sources: list[str]) -> bool:
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(s) > t for s in sources)
+
+
+def _run(cmd: list[str]) -> None:
+    print("+", " ".join(cmd), flush=True)
+    subprocess.run(cmd, check=True, cwd=HERE)
+
+
+def build_cuda(force: bool = False, ptxas_verbose: bool = False) -> str:
+    srcs = [os.path.join(CSRC, f) for f in ("gtk_kernels.cu", "gtk_api.cu", "gtk_table.cpp")]
+    deps = srcs + [os.path.join(CSRC, f) for f in ("gtk_device.cuh", "gtk_table.hpp")] + \
+        [os.path.join(INCLUDE, "gputok_b200.h")]
+    if force or _stale(LIB, deps):
+        nvcc = os.environ.get("NVCC", "nvcc")
+        extra = ["-Xptxas", "-v"] if ptxas_verbose else []
+        _run([nvcc] + NVCC_FLAGS + extra + srcs + ["-o", LIB])
+    return LIB
+
+
+def build_textgen(force: bool = False) -> str:
+    src = os.path.join(CSRC, "gtk_textgen.c")
+    if force or _stale(TEXTGEN, [src]):
+        _run(["gcc", "-O3", "-std=gnu11", "-fPIC", "-shared", "-fvisibility=hidden", src, "-o", TEXTGEN,
+              "-lm", "-lpthread"])
+    return TEXTGEN
+
+
+def build_pymod(force: bool = False) -> str:
+    import pybind11
+
+    src = os.path.join(CSRC, "gputok_pybind.cpp")
+    if force or _stale(PYMOD, [src, os.path.join(INCLUDE, "gputok_b200.h"), LIB]):
+        _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden",
+              "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"], src,
+              "-L", HERE, "-lgputok_b200", "-Wl,-rpath,$ORIGIN", "-o", PYMOD])
+    return PYMOD
+
+
+def build_all(force: bool = False) -> None:
+    build_cuda(force)
+    build_textgen(force)
+    build_pymod(force)
+
+
+if __name__ == "__main__":
+    build_all(force="--force" in sys.argv)

@@ -1,0 +1,646 @@
+// gtk_api.cu -- the C ABI declared in include/gputok_b200.h.
+//
+// One handle = one device, one stream, one merge table in HBM and a set of
+// grow-only arenas (device and pinned host), so a call allocates nothing once
+// the arenas have reached the working size.  The reference allocates and
+// frees five device buffers inside every call (gputok_binding.cu:906-910,
+// 981-986), which its own profile shows to be 70-95 % of the API time.
+#include "../../include/gputok_b200.h"
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <new>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "gtk_device.cuh"
+#include "gtk_table.hpp"
+
+namespace {
+
+thread_local std::string g_global_error;
+
+struct CudaFail {
+  std::string what;
+};
+
+#define GTK_CUDA(expr)                                                                              \
+  do {                                                                                              \
+    cudaError_t e__ = (expr);                                                                       \
+    if (e__ != cudaSuccess) {                                                                       \
+      throw CudaFail{std::string(#expr) + ": " + cudaGetErrorString(e__)};                          \
+    }                                                                                               \
+  } while (0)
+
+// grow-only device / pinned-host buffers
+struct DevBuf {
+  void* p = nullptr;
+  size_t cap = 0;
+  void reserve(size_t bytes)
+  {
+    if (bytes <= cap) return;
+    if (p) GTK_CUDA(cudaFree(p));
+    p = nullptr;
+    cap = 0;
+    size_t want = std::max(bytes + bytes / 4, size_t(4096));
+    GTK_CUDA(cudaMalloc(&p, want));
+    cap = want;
+  }
+  void release()
+  {
+    if (p) cudaFree(p);
+    p = nullptr;
+    cap = 0;
+  }
+  template <class T>
+  T* as() const { return static_cast<T*>(p); }
+};
+
+struct PinBuf {
+  void* p = nullptr;
+  size_t cap = 0;
+  void reserve(size_t bytes)
+  {
+    if (bytes <= cap) return;
+    if (p) GTK_CUDA(cudaFreeHost(p));
+    p = nullptr;
+    cap = 0;
+    size_t want = std::max(bytes + bytes / 4, size_t(4096));
+    GTK_CUDA(cudaHostAlloc(&p, want, cudaHostAllocDefault));
+    cap = want;
+  }
+  void release()
+  {
+    if (p) cudaFreeHost(p);
+    p = nullptr;
+    cap = 0;
+  }
+  template <class T>
+  T* as() const { return static_cast<T*>(p); }
+};
+
+}  // namespace
+
+struct gtk_tokenizer {
+  std::unique_ptr<gtk::HostTable> table;
+  int chunk_tokens = 2048;
+  int max_iters = 50;
+  int device = -1;
+  int sm_count = 0;
+  int opt_grid = 0, base_grid = 0;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev[6] = {};
+  std::mutex mu;
+  mutable std::string last_error;
+
+  // table in HBM
+  DevBuf d_slots, d_bpr, d_mor, d_sor, d_adj, d_b2i;
+  gtk::DeviceTable dtab{};
+
+  // arenas
+  DevBuf d_bytes, d_text_off, d_text_chunk_base, d_chunk_off, d_tile_chunk0, d_staging, d_unit_first, d_unit_cnt,
+      d_chunk_cnt, d_unit_base, d_chunk_id_off, d_text_id_off, d_out_ids, d_seg_scratch, d_scan_sums, d_counters,
+      d_totals;
+  PinBuf h_ids, h_text_id_off, h_chunk_id_off, h_totals;
+  // host-side result of gtk_encode_cpu
+  std::vector<int32_t> cpu_ids;
+  std::vector<int64_t> cpu_text_off, cpu_chunk_off;
+  bool result_is_cpu = false;
+  int64_t res_n_ids = 0, res_n_chunks = 0, res_n_texts = 0;
+  float stage_ms[5] = {0, 0, 0, 0, 0};
+  int32_t last_launches = 0;
+
+  int fail(int code, const std::string& msg) const
+  {
+    last_error = msg;
+    return code;
+  }
+};
+
+namespace {
+
+void upload(DevBuf& buf, const void* src, size_t bytes, cudaStream_t s)
+{
+  buf.reserve(bytes);
+  GTK_CUDA(cudaMemcpyAsync(buf.p, src, bytes, cudaMemcpyHostToDevice, s));
+}
+
+void upload_table(gtk_tokenizer* h)
+{
+  const gtk::HostTable& t = *h->table;
+  upload(h->d_slots, t.slots.data(), t.slots.size() * sizeof(gtk::HashSlot), h->stream);
+  upload(h->d_bpr, t.byte_pair_rank.data(), t.byte_pair_rank.size() * sizeof(uint16_t), h->stream);
+  upload(h->d_mor, t.merged_of_rank.data(), t.merged_of_rank.size() * sizeof(uint32_t), h->stream);
+  upload(h->d_sor, t.same_of_rank.data(), t.same_of_rank.size(), h->stream);
+  upload(h->d_adj, t.adj, sizeof(t.adj), h->stream);
+  upload(h->d_b2i, t.byte_to_id, sizeof(t.byte_to_id), h->stream);
+  GTK_CUDA(cudaStreamSynchronize(h->stream));
+  h->dtab.slots = h->d_slots.as<uint4>();
+  h->dtab.byte_pair_rank = h->d_bpr.as<uint16_t>();
+  h->dtab.merged_of_rank = h->d_mor.as<uint32_t>();
+  h->dtab.same_of_rank = h->d_sor.as<uint8_t>();
+  h->dtab.adj = h->d_adj.as<uint32_t>();
+  h->dtab.byte_to_id = h->d_b2i.as<uint16_t>();
+  h->dtab.log2_capacity = t.log2_capacity;
+  h->dtab.max_probe = t.max_probe;
+  h->dtab.monotone = t.monotone ? 1 : 0;
+  h->dtab.merged_is_256_plus_rank = t.merged_is_256_plus_rank ? 1 : 0;
+}
+
+// Upper bound on the number of chunks without touching the device: every text
+// contributes its full chunks plus at most one partial chunk.
+int64_t chunk_upper_bound(int64_t n_bytes, int64_t n_texts, int chunk_tokens)
+{
+  return n_bytes / chunk_tokens + n_texts + 1;
+}
+
+struct Plan {
+  gtk::EncodeBuffers b{};
+  int64_t chunk_cap = 0;
+};
+
+// Size the arenas for a batch and fill the kernel argument block.
+Plan plan_batch(gtk_tokenizer* h, const uint8_t* d_bytes, int64_t n_bytes, const int64_t* d_text_off,
+                int64_t n_texts, int32_t* d_out_ids, int64_t out_capacity, int64_t* d_chunk_id_off,
+                bool want_text_id_off)
+{
+  Plan p;
+  gtk::EncodeBuffers& b = p.b;
+  const int64_t chunk_cap = chunk_upper_bound(n_bytes, n_texts, h->chunk_tokens);
+  const int64_t n_tiles = (n_bytes + gtk::kTile - 1) / gtk::kTile;
+  p.chunk_cap = chunk_cap;
+  h->d_text_chunk_base.reserve(size_t(n_texts + 1) * 8);
+  h->d_chunk_off.reserve(size_t(chunk_cap + 1) * 8);
+  h->d_tile_chunk0.reserve(size_t(n_tiles + 1) * 4);
+  h->d_staging.reserve(size_t(n_bytes + 16) * 2);
+  h->d_unit_first.reserve(size_t(n_tiles + 1) * 8);
+  h->d_unit_cnt.reserve(size_t(n_tiles + 1) * 4);
+  h->d_chunk_cnt.reserve(size_t(chunk_cap + 1) * 4);
+  h->d_unit_base.reserve(size_t(n_tiles + 2) * 8);
+  if (!d_chunk_id_off) {
+    h->d_chunk_id_off.reserve(size_t(chunk_cap + 1) * 8);
+    d_chunk_id_off = h->d_chunk_id_off.as<int64_t>();
+  }
+  if (want_text_id_off) h->d_text_id_off.reserve(size_t(n_texts + 1) * 8);
+  const int64_t scan_items = std::max<int64_t>(std::max(chunk_cap, n_tiles), n_texts);
+  h->d_scan_sums.reserve(size_t(scan_items / 4096 + 2) * 8);
+  h->d_counters.reserve(64);
+  h->d_totals.reserve(64);
+  // workspace for segments / chunks that do not fit in shared memory
+  const int64_t longest = std::min<int64_t>(h->chunk_tokens, n_bytes);
+  int64_t scratch_tokens = 0;
+  if (longest > gtk::kHalo) scratch_tokens = (longest + 63) & ~int64_t(63);
+  const int ctas = std::max(h->opt_grid, h->base_grid);
+  if (scratch_tokens) h->d_seg_scratch.reserve(size_t(ctas) * 2 * size_t(scratch_tokens) * 2);
+
+  b.bytes = d_bytes;
+  b.n_bytes = n_bytes;
+  b.text_off = d_text_off;
+  b.n_texts = n_texts;
+  b.chunk_bytes = h->chunk_tokens;
+  b.text_chunk_base = h->d_text_chunk_base.as<int64_t>();
+  b.chunk_off = h->d_chunk_off.as<int64_t>();
+  b.chunk_cap = chunk_cap;
+  b.tile_chunk0 = h->d_tile_chunk0.as<int32_t>();
+  b.n_tiles = n_tiles;
+  b.staging = h->d_staging.as<uint16_t>();
+  b.unit_first = h->d_unit_first.as<int64_t>();
+  b.unit_cnt = h->d_unit_cnt.as<int32_t>();
+  b.chunk_cnt = h->d_chunk_cnt.as<int32_t>();
+  b.unit_base = h->d_unit_base.as<int64_t>();
+  b.chunk_id_off = d_chunk_id_off;
+  b.text_id_off = want_text_id_off ? h->d_text_id_off.as<int64_t>() : nullptr;
+  b.out_ids = d_out_ids;
+  b.out_capacity = out_capacity;
+  b.seg_scratch = scratch_tokens ? h->d_seg_scratch.as<uint16_t>() : nullptr;
+  b.seg_scratch_tokens = scratch_tokens;
+  b.scan_block_sums = h->d_scan_sums.as<int64_t>();
+  b.counters = h->d_counters.as<int32_t>();
+  b.totals = h->d_totals.as<int64_t>();
+  return p;
+}
+
+const char* status_text(int s)
+{
+  switch (s) {
+    case gtk::kStatusLongQueueOverflow: return "long-segment queue overflow";
+    case gtk::kStatusScratchTooSmall: return "segment workspace too small";
+    case gtk::kStatusBadSegment: return "merge pass made no progress";
+    default: return "unknown kernel status";
+  }
+}
+
+// Chunker -> merge -> scans.  Leaves totals (n_chunks, n_ids) and the status
+// word in the pinned totals buffer; the caller synchronises and then packs.
+void run_front(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* launches)
+{
+  cudaStream_t s = h->stream;
+  GTK_CUDA(cudaMemsetAsync(b.counters, 0, 64, s));
+  GTK_CUDA(cudaMemsetAsync(b.chunk_cnt, 0, size_t(b.chunk_cap + 1) * 4, s));
+  GTK_CUDA(cudaEventRecord(h->ev[0], s));
+  *launches += gtk::launch_chunker(b, s);
+  GTK_CUDA(cudaEventRecord(h->ev[1], s));
+  if (mode == GTK_MODE_BASE) *launches += gtk::launch_merge_base(b, h->dtab, h->base_grid, s);
+  else *launches += gtk::launch_merge_opt(b, h->dtab, h->opt_grid, s);
+  GTK_CUDA(cudaEventRecord(h->ev[2], s));
+  *launches += gtk::launch_output_scans(b, mode == GTK_MODE_BASE, s);
+  GTK_CUDA(cudaEventRecord(h->ev[3], s));
+  GTK_CUDA(cudaGetLastError());
+  int64_t* ht = h->h_totals.as<int64_t>();
+  GTK_CUDA(cudaMemcpyAsync(ht, b.totals, 16, cudaMemcpyDeviceToHost, s));
+  GTK_CUDA(cudaMemcpyAsync(ht + 2, b.counters, 16, cudaMemcpyDeviceToHost, s));
+}
+
+void run_pack(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* launches)
+{
+  cudaStream_t s = h->stream;
+  GTK_CUDA(cudaEventRecord(h->ev[5], s));
+  *launches += gtk::launch_pack(b, mode == GTK_MODE_BASE, h->sm_count * 8, s);
+  GTK_CUDA(cudaEventRecord(h->ev[4], s));
+  GTK_CUDA(cudaGetLastError());
+}
+
+void collect_stage_times(gtk_tokenizer* h)
+{
+  float ms = 0;
+  for (int i = 0; i < 3; ++i) {
+    if (cudaEventElapsedTime(&ms, h->ev[i], h->ev[i + 1]) == cudaSuccess) h->stage_ms[i] = ms;
+  }
+  if (cudaEventElapsedTime(&ms, h->ev[5], h->ev[4]) == cudaSuccess) h->stage_ms[3] = ms;
+  // the pipeline time excludes the host round trip between scans and pack
+  h->stage_ms[4] = h->stage_ms[0] + h->stage_ms[1] + h->stage_ms[2] + h->stage_ms[3];
+}
+
+int validate_offsets(gtk_tokenizer* h, const int64_t* text_offsets, int64_t n_texts)
+{
+  if (n_texts < 0) return h->fail(GTK_ERR_INVALID_ARG, "n_texts must be >= 0");
+  if (n_texts > 0 && !text_offsets) return h->fail(GTK_ERR_INVALID_ARG, "text_offsets is null");
+  if (n_texts > 0 && text_offsets[0] != 0) return h->fail(GTK_ERR_INVALID_ARG, "text_offsets[0] must be 0");
+  for (int64_t t = 0; t < n_texts; ++t)
+    if (text_offsets[t + 1] < text_offsets[t]) return h->fail(GTK_ERR_INVALID_ARG, "text_offsets must be non-decreasing");
+  return GTK_OK;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------------
+// C ABI
+// ------------------------------------------------------------------------------------------------
+
+extern "C" {
+
+GTK_API const char* gtk_version(void) { return "gputok_b200 0.1 (sm_100a)"; }
+
+GTK_API const char* gtk_global_error(void) { return g_global_error.c_str(); }
+
+GTK_API int gtk_create(const char* merges_path, int chunk_tokens, int max_iters, int device, gtk_tokenizer** out)
+{
+  if (!out) {
+    g_global_error = "out is null";
+    return GTK_ERR_INVALID_ARG;
+  }
+  *out = nullptr;
+  if (!merges_path) {
+    g_global_error = "merges_path is null";
+    return GTK_ERR_INVALID_ARG;
+  }
+  if (chunk_tokens <= 0) {
+    g_global_error = "chunk_tokens must be > 0";
+    return GTK_ERR_INVALID_ARG;
+  }
+  if (max_iters <= 0) max_iters = 50;
+  gtk_tokenizer* h = nullptr;
+  try {
+    h = new gtk_tokenizer();
+    h->chunk_tokens = chunk_tokens;
+    h->max_iters = max_iters;
+    h->device = device;
+    try {
+      h->table.reset(new gtk::HostTable(merges_path));
+    } catch (const std::runtime_error& e) {
+      g_global_error = e.what();
+      delete h;
+      return GTK_ERR_IO;
+    }
+    if (device >= 0) {
+      if (!h->table->fits_u16) {
+        g_global_error = "merge table has ids >= 65535 or ranks >= 65534: outside the 16-bit kernels";
+        delete h;
+        return GTK_ERR_TABLE;
+      }
+      int count = 0;
+      cudaError_t e = cudaGetDeviceCount(&count);
+      if (e != cudaSuccess || device >= count) {
+        g_global_error = std::string("CUDA device ") + std::to_string(device) + " not available: " +
+                         (e != cudaSuccess ? cudaGetErrorString(e) : "ordinal out of range");
+        delete h;
+        return GTK_ERR_NO_DEVICE;
+      }
+      GTK_CUDA(cudaSetDevice(device));
+      GTK_CUDA(cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, device));
+      GTK_CUDA(cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking));
+      for (auto& ev : h->ev) GTK_CUDA(cudaEventCreate(&ev));
+      upload_table(h);
+      h->opt_grid = h->sm_count * std::max(1, gtk::opt_kernel_max_blocks_per_sm());
+      h->base_grid = h->sm_count * std::max(1, gtk::base_kernel_max_blocks_per_sm());
+      h->h_totals.reserve(64);
+    }
+    *out = h;
+    return GTK_OK;
+  } catch (const CudaFail& f) {
+    g_global_error = f.what;
+    delete h;
+    return GTK_ERR_CUDA;
+  } catch (const std::bad_alloc&) {
+    g_global_error = "out of host memory";
+    delete h;
+    return GTK_ERR_INVALID_ARG;
+  }
+}
+
+GTK_API void gtk_destroy(gtk_tokenizer* h)
+{
+  if (!h) return;
+  if (h->device >= 0) {
+    cudaSetDevice(h->device);
+    if (h->stream) cudaStreamSynchronize(h->stream);
+    for (DevBuf* b : {&h->d_slots, &h->d_bpr, &h->d_mor, &h->d_sor, &h->d_adj, &h->d_b2i, &h->d_bytes, &h->d_text_off,
+                      &h->d_text_chunk_base, &h->d_chunk_off, &h->d_tile_chunk0, &h->d_staging, &h->d_unit_first,
+                      &h->d_unit_cnt, &h->d_chunk_cnt, &h->d_unit_base, &h->d_chunk_id_off, &h->d_text_id_off,
+                      &h->d_out_ids, &h->d_seg_scratch, &h->d_scan_sums, &h->d_counters, &h->d_totals})
+      b->release();
+    for (PinBuf* b : {&h->h_ids, &h->h_text_id_off, &h->h_chunk_id_off, &h->h_totals}) b->release();
+    for (auto& ev : h->ev)
+      if (ev) cudaEventDestroy(ev);
+    if (h->stream) cudaStreamDestroy(h->stream);
+  }
+  delete h;
+}
+
+GTK_API const char* gtk_last_error(const gtk_tokenizer* h) { return h ? h->last_error.c_str() : "null handle"; }
+
+GTK_API int gtk_table_info_get(const gtk_tokenizer* h, gtk_table_info* out)
+{
+  if (!h || !out) return GTK_ERR_INVALID_ARG;
+  const gtk::HostTable& t = *h->table;
+  out->vocab_size = int32_t(t.id_to_symbols.size());
+  out->num_merges = int32_t(t.rows.size());
+  out->max_rank = t.max_rank;
+  out->hash_capacity = 1u << t.log2_capacity;
+  out->hash_max_probe = t.max_probe;
+  out->hash_bytes = uint32_t(t.slots.size() * sizeof(gtk::HashSlot));
+  out->monotone = t.monotone;
+  out->merged_is_256_plus_rank = t.merged_is_256_plus_rank;
+  out->byte_ids_identity = t.byte_ids_identity;
+  out->adj_bigrams = t.adj_count;
+  out->chunk_tokens = h->chunk_tokens;
+  out->max_iters = h->max_iters;
+  out->device = h->device;
+  out->sm_count = h->sm_count;
+  return GTK_OK;
+}
+
+GTK_API int gtk_encode_device(gtk_tokenizer* h, int mode, const uint8_t* d_bytes, int64_t n_bytes,
+                              const int64_t* d_text_offsets, int64_t n_texts, int32_t* d_out_ids,
+                              int64_t out_capacity, int64_t* d_out_chunk_offsets, int64_t chunk_capacity,
+                              int64_t* n_ids, int64_t* n_chunks, float* kernel_ms)
+{
+  if (!h) return GTK_ERR_INVALID_ARG;
+  std::lock_guard<std::mutex> lock(h->mu);
+  if (h->device < 0) return h->fail(GTK_ERR_NO_DEVICE, "host-only handle: no GPU entry points");
+  if (mode != GTK_MODE_OPT && mode != GTK_MODE_BASE) return h->fail(GTK_ERR_INVALID_ARG, "unknown mode");
+  if (n_bytes < 0 || n_texts < 0) return h->fail(GTK_ERR_INVALID_ARG, "negative size");
+  if (n_ids) *n_ids = 0;
+  if (n_chunks) *n_chunks = 0;
+  if (kernel_ms) *kernel_ms = 0.f;
+  h->last_launches = 0;
+  std::fill(h->stage_ms, h->stage_ms + 5, 0.f);
+  if (n_texts == 0 || n_bytes == 0) return GTK_OK;
+  if (!d_bytes || !d_text_offsets || !d_out_ids) return h->fail(GTK_ERR_INVALID_ARG, "null device pointer");
+  try {
+    GTK_CUDA(cudaSetDevice(h->device));
+    const int64_t need_chunks = chunk_upper_bound(n_bytes, n_texts, h->chunk_tokens);
+    int64_t* chunk_dst = d_out_chunk_offsets;
+    if (chunk_dst && chunk_capacity < need_chunks + 1) chunk_dst = nullptr;  // scan into the arena, copy what fits
+    Plan p = plan_batch(h, d_bytes, n_bytes, d_text_offsets, n_texts, d_out_ids, out_capacity, chunk_dst, false);
+    int launches = 0;
+    run_front(h, p.b, mode, &launches);
+    GTK_CUDA(cudaStreamSynchronize(h->stream));
+    const int64_t* ht = h->h_totals.as<int64_t>();
+    const int64_t C = ht[0], N = ht[1];
+    const int status = reinterpret_cast<const int32_t*>(ht + 2)[1];
+    if (status != gtk::kStatusOk) return h->fail(GTK_ERR_KERNEL, status_text(status));
+    if (N > out_capacity) return h->fail(GTK_ERR_CAPACITY, "d_out_ids too small: need " + std::to_string(N) + " ids");
+    if (d_out_chunk_offsets && !chunk_dst) {
+      if (chunk_capacity < C + 1)
+        return h->fail(GTK_ERR_CAPACITY, "d_out_chunk_offsets too small: need " + std::to_string(C + 1));
+      GTK_CUDA(cudaMemcpyAsync(d_out_chunk_offsets, p.b.chunk_id_off, size_t(C + 1) * 8, cudaMemcpyDeviceToDevice,
+                               h->stream));
+    }
+    run_pack(h, p.b, mode, &launches);
+    GTK_CUDA(cudaStreamSynchronize(h->stream));
+    collect_stage_times(h);
+    h->last_launches = launches;
+    if (n_ids) *n_ids = N;
+    if (n_chunks) *n_chunks = C;
+    if (kernel_ms) *kernel_ms = h->stage_ms[4];
+    return GTK_OK;
+  } catch (const CudaFail& f) {
+    return h->fail(GTK_ERR_CUDA, f.what);
+  }
+}
+
+GTK_API int gtk_encode(gtk_tokenizer* h, int mode, const uint8_t* bytes, const int64_t* text_offsets,
+                       int64_t n_texts, float* kernel_ms)
+{
+  if (!h) return GTK_ERR_INVALID_ARG;
+  std::lock_guard<std::mutex> lock(h->mu);
+  if (h->device < 0) return h->fail(GTK_ERR_NO_DEVICE, "host-only handle: no GPU entry points");
+  if (mode != GTK_MODE_OPT && mode != GTK_MODE_BASE) return h->fail(GTK_ERR_INVALID_ARG, "unknown mode");
+  if (int rc = validate_offsets(h, text_offsets, n_texts)) return rc;
+  if (kernel_ms) *kernel_ms = 0.f;
+  h->result_is_cpu = false;
+  h->res_n_ids = h->res_n_chunks = 0;
+  h->res_n_texts = n_texts;
+  h->last_launches = 0;
+  std::fill(h->stage_ms, h->stage_ms + 5, 0.f);
+  try {
+    GTK_CUDA(cudaSetDevice(h->device));
+    const int64_t n_bytes = n_texts ? text_offsets[n_texts] : 0;
+    h->h_text_id_off.reserve(size_t(n_texts + 1) * 8);
+    if (n_bytes == 0) {  // empty batch or only empty texts: ([], 0.0) in the reference
+      std::memset(h->h_text_id_off.p, 0, size_t(n_texts + 1) * 8);
+      h->h_chunk_id_off.reserve(8);
+      h->h_chunk_id_off.as<int64_t>()[0] = 0;
+      return GTK_OK;
+    }
+    if (!bytes) return h->fail(GTK_ERR_INVALID_ARG, "bytes is null");
+    cudaStream_t s = h->stream;
+    h->d_bytes.reserve(size_t(n_bytes) + 32);
+    h->d_text_off.reserve(size_t(n_texts + 1) * 8);
+    GTK_CUDA(cudaMemcpyAsync(h->d_bytes.p, bytes, size_t(n_bytes), cudaMemcpyHostToDevice, s));
+    GTK_CUDA(cudaMemcpyAsync(h->d_text_off.p, text_offsets, size_t(n_texts + 1) * 8, cudaMemcpyHostToDevice, s));
+    Plan p = plan_batch(h, h->d_bytes.as<uint8_t>(), n_bytes, h->d_text_off.as<int64_t>(), n_texts, nullptr, 0,
+                        nullptr, true);
+    int launches = 0;
+    run_front(h, p.b, mode, &launches);
+    GTK_CUDA(cudaStreamSynchronize(s));
+    const int64_t* ht = h->h_totals.as<int64_t>();
+    const int64_t C = ht[0], N = ht[1];
+    const int status = reinterpret_cast<const int32_t*>(ht + 2)[1];
+    if (status != gtk::kStatusOk) return h->fail(GTK_ERR_KERNEL, status_text(status));
+    h->d_out_ids.reserve(size_t(N + 1) * 4);
+    p.b.out_ids = h->d_out_ids.as<int32_t>();
+    p.b.out_capacity = N;
+    run_pack(h, p.b, mode, &launches);
+    h->h_ids.reserve(size_t(N + 1) * 4);
+    h->h_chunk_id_off.reserve(size_t(C + 1) * 8);
+    GTK_CUDA(cudaMemcpyAsync(h->h_ids.p, p.b.out_ids, size_t(N) * 4, cudaMemcpyDeviceToHost, s));
+    GTK_CUDA(cudaMemcpyAsync(h->h_chunk_id_off.p, p.b.chunk_id_off, size_t(C + 1) * 8, cudaMemcpyDeviceToHost, s));
+    GTK_CUDA(cudaMemcpyAsync(h->h_text_id_off.p, p.b.text_id_off, size_t(n_texts + 1) * 8, cudaMemcpyDeviceToHost, s));
+    GTK_CUDA(cudaStreamSynchronize(s));
+    collect_stage_times(h);
+    h->last_launches = launches;
+    h->res_n_ids = N;
+    h->res_n_chunks = C;
+    if (kernel_ms) *kernel_ms = h->stage_ms[4];
+    return GTK_OK;
+  } catch (const CudaFail& f) {
+    return h->fail(GTK_ERR_CUDA, f.what);
+  }
+}
+
+GTK_API int gtk_encode_cpu(gtk_tokenizer* h, int rule, const uint8_t* bytes, const int64_t* text_offsets,
+                           int64_t n_texts)
+{
+  if (!h) return GTK_ERR_INVALID_ARG;
+  std::lock_guard<std::mutex> lock(h->mu);
+  if (rule != GTK_RULE_GREEDY && rule != GTK_RULE_LOCALMIN) return h->fail(GTK_ERR_INVALID_ARG, "unknown rule");
+  if (int rc = validate_offsets(h, text_offsets, n_texts)) return rc;
+  if (n_texts > 0 && text_offsets[n_texts] > 0 && !bytes) return h->fail(GTK_ERR_INVALID_ARG, "bytes is null");
+  h->cpu_ids.clear();
+  h->cpu_text_off.assign(1, 0);
+  h->cpu_chunk_off.assign(1, 0);
+  for (int64_t t = 0; t < n_texts; ++t) {
+    const int64_t s = text_offsets[t], e = text_offsets[t + 1];
+    if (rule == GTK_RULE_LOCALMIN) {
+      if (e > s) {
+        h->table->localmin_text(bytes + s, e - s, h->max_iters, h->cpu_ids);
+        h->cpu_chunk_off.push_back(int64_t(h->cpu_ids.size()));
+      }
+    } else {
+      for (int64_t pos = s; pos < e; pos += h->chunk_tokens) {
+        const int64_t len = std::min<int64_t>(h->chunk_tokens, e - pos);
+        h->table->greedy_chunk(bytes + pos, len, h->cpu_ids);
+        h->cpu_chunk_off.push_back(int64_t(h->cpu_ids.size()));
+      }
+    }
+    h->cpu_text_off.push_back(int64_t(h->cpu_ids.size()));
+  }
+  h->result_is_cpu = true;
+  h->res_n_ids = int64_t(h->cpu_ids.size());
+  h->res_n_chunks = int64_t(h->cpu_chunk_off.size()) - 1;
+  h->res_n_texts = n_texts;
+  return GTK_OK;
+}
+
+GTK_API int gtk_result_sizes(const gtk_tokenizer* h, int64_t* n_ids, int64_t* n_chunks, int64_t* n_texts)
+{
+  if (!h) return GTK_ERR_INVALID_ARG;
+  if (n_ids) *n_ids = h->res_n_ids;
+  if (n_chunks) *n_chunks = h->res_n_chunks;
+  if (n_texts) *n_texts = h->res_n_texts;
+  return GTK_OK;
+}
+
+GTK_API int gtk_result_view(const gtk_tokenizer* h, const int32_t** ids, const int64_t** text_id_offsets,
+                            const int64_t** chunk_id_offsets)
+{
+  if (!h) return GTK_ERR_INVALID_ARG;
+  if (h->result_is_cpu) {
+    if (ids) *ids = h->cpu_ids.data();
+    if (text_id_offsets) *text_id_offsets = h->cpu_text_off.data();
+    if (chunk_id_offsets) *chunk_id_offsets = h->cpu_chunk_off.data();
+  } else {
+    if (ids) *ids = h->h_ids.as<int32_t>();
+    if (text_id_offsets) *text_id_offsets = h->h_text_id_off.as<int64_t>();
+    if (chunk_id_offsets) *chunk_id_offsets = h->h_chunk_id_off.as<int64_t>();
+  }
+  return GTK_OK;
+}
+
+GTK_API int gtk_result_copy(const gtk_tokenizer* h, int32_t* ids, int64_t ids_capacity, int64_t* text_id_offsets,
+                            int64_t* chunk_id_offsets, int64_t chunk_capacity)
+{
+  if (!h) return GTK_ERR_INVALID_ARG;
+  const int32_t* src_ids;
+  const int64_t *src_text, *src_chunk;
+  gtk_result_view(h, &src_ids, &src_text, &src_chunk);
+  if (ids) {
+    if (ids_capacity < h->res_n_ids) return h->fail(GTK_ERR_CAPACITY, "ids buffer too small");
+    if (h->res_n_ids) std::memcpy(ids, src_ids, size_t(h->res_n_ids) * 4);
+  }
+  if (text_id_offsets && src_text) std::memcpy(text_id_offsets, src_text, size_t(h->res_n_texts + 1) * 8);
+  if (chunk_id_offsets) {
+    if (chunk_capacity < h->res_n_chunks + 1) return h->fail(GTK_ERR_CAPACITY, "chunk offset buffer too small");
+    if (src_chunk) std::memcpy(chunk_id_offsets, src_chunk, size_t(h->res_n_chunks + 1) * 8);
+  }
+  return GTK_OK;
+}
+
+GTK_API int gtk_last_stage_ms(const gtk_tokenizer* h, float stage_ms[5], int32_t* kernel_launches)
+{
+  if (!h) return GTK_ERR_INVALID_ARG;
+  if (stage_ms) std::memcpy(stage_ms, h->stage_ms, sizeof(h->stage_ms));
+  if (kernel_launches) *kernel_launches = h->last_launches;
+  return GTK_OK;
+}
+
+GTK_API int gtk_decode(const gtk_tokenizer* h, const int32_t* ids, int64_t n_ids, uint8_t* out, int64_t out_capacity,
+                       int64_t* n_out)
+{
+  if (!h || (n_ids > 0 && !ids)) return GTK_ERR_INVALID_ARG;
+  const gtk::HostTable& t = *h->table;
+  int64_t k = 0;
+  for (int64_t i = 0; i < n_ids; ++i) {
+    const int32_t id = ids[i];
+    if (id < 0 || size_t(id) >= t.id_to_bytes.size() || !t.decodable[size_t(id)])
+      return h->fail(GTK_ERR_INVALID_ARG, "id " + std::to_string(id) + " has no byte string");
+    const std::string& s = t.id_to_bytes[size_t(id)];
+    if (out) {
+      if (k + int64_t(s.size()) > out_capacity) return h->fail(GTK_ERR_CAPACITY, "decode buffer too small");
+      std::memcpy(out + k, s.data(), s.size());
+    }
+    k += int64_t(s.size());
+  }
+  if (n_out) *n_out = k;
+  return GTK_OK;
+}
+
+GTK_API int32_t gtk_token_symbols(const gtk_tokenizer* h, int32_t id, char* buf, int32_t capacity)
+{
+  if (!h || id < 0 || size_t(id) >= h->table->id_to_symbols.size()) return -1;
+  const std::string& s = h->table->id_to_symbols[size_t(id)];
+  if (buf && capacity >= int32_t(s.size())) std::memcpy(buf, s.data(), s.size());
+  return int32_t(s.size());
+}
+
+GTK_API void* gtk_pinned_alloc(size_t bytes)
+{
+  void* p = nullptr;
+  if (cudaHostAlloc(&p, bytes ? bytes : 1, cudaHostAllocDefault) != cudaSuccess) return nullptr;
+  return p;
+}
+
+GTK_API void gtk_pinned_free(void* p)
+{
+  if (p) cudaFreeHost(p);
+}
+
+}  // extern "C"

@@ -1,0 +1,82 @@
+// gtk_device.cuh -- device-side view of the merge table and the launchers the
+// host API calls.  Kernels live in gtk_kernels.cu.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace gtk {
+
+// Tile geometry of the segment-parallel kernel: a CTA owns the segments that
+// start inside TILE consecutive bytes and sees HALO more bytes so that the
+// last owned segment can finish inside shared memory.
+constexpr int kTile = 4096;
+constexpr int kHalo = 512;
+constexpr int kWindow = kTile + kHalo;
+constexpr int kOptThreads = 256;
+constexpr int kBaseThreads = 512;
+constexpr int kBaseSmemTokens = 8192;  // chunks up to this length stay in shared memory in the base kernel
+constexpr int kThreadSegMax = 64;      // longest segment a single thread merges on its own
+
+// Pointers into HBM, passed by value to every kernel.
+struct DeviceTable {
+  const uint4* slots;              // HashSlot[capacity]: {right, left, rank, merged}
+  const uint16_t* byte_pair_rank;  // [65536]
+  const uint32_t* merged_of_rank;  // [max_rank+1]
+  const uint8_t* same_of_rank;     // [max_rank+1]
+  const uint32_t* adj;             // [2048]
+  const uint16_t* byte_to_id;      // [256]
+  uint32_t log2_capacity;
+  uint32_t max_probe;
+  int monotone;
+  int merged_is_256_plus_rank;
+};
+
+// Status word written by kernels instead of trapping: 0 = fine.
+enum : int {
+  kStatusOk = 0,
+  kStatusLongQueueOverflow = 1,
+  kStatusScratchTooSmall = 2,
+  kStatusBadSegment = 3,
+};
+
+struct EncodeBuffers {
+  const uint8_t* bytes;      // input text, n_bytes
+  int64_t n_bytes;
+  const int64_t* text_off;   // [n_texts+1]
+  int64_t n_texts;
+  int chunk_bytes;
+  // chunker outputs
+  int64_t* text_chunk_base;  // [n_texts+1] exclusive scan of chunks per text
+  int64_t* chunk_off;        // [chunk_cap+1] start byte of each chunk, chunk_off[C] = n_bytes
+  int64_t chunk_cap;         // upper bound on the number of chunks
+  int32_t* tile_chunk0;      // [n_tiles] chunk that contains the first byte of the tile
+  int64_t n_tiles;
+  // merge outputs
+  uint16_t* staging;         // [n_bytes] tokens of a unit, compacted at the unit's first byte
+  int64_t* unit_first;       // [n_tiles] byte position where the unit's tokens start in staging (opt mode)
+  int32_t* unit_cnt;         // [n_tiles] tokens produced by the unit (opt mode)
+  int32_t* chunk_cnt;        // [chunk_cap] tokens per chunk
+  // scan outputs
+  int64_t* unit_base;        // [n_tiles+1]
+  int64_t* chunk_id_off;     // [chunk_cap+1] packed id offset of each chunk (caller visible)
+  int64_t* text_id_off;      // [n_texts+1] or nullptr
+  int32_t* out_ids;
+  int64_t out_capacity;
+  // scratch
+  uint16_t* seg_scratch;     // per-CTA workspace for segments that do not fit in shared memory
+  int64_t seg_scratch_tokens;  // tokens per CTA (two arrays of this length per CTA)
+  int64_t* scan_block_sums;  // workspace of the multi-block scan
+  int32_t* counters;         // [0] tile ticket, [1] status word, [2] base-mode chunk ticket
+  int64_t* totals;           // device: [0] n_chunks, [1] n_ids
+};
+
+// Launchers (all asynchronous on `stream`; return the number of kernels launched).
+int launch_chunker(const EncodeBuffers& b, cudaStream_t stream);
+int launch_merge_opt(const EncodeBuffers& b, const DeviceTable& t, int grid, cudaStream_t stream);
+int launch_merge_base(const EncodeBuffers& b, const DeviceTable& t, int grid, cudaStream_t stream);
+int launch_output_scans(const EncodeBuffers& b, int mode_base, cudaStream_t stream);
+int launch_pack(const EncodeBuffers& b, int mode_base, int grid, cudaStream_t stream);
+int opt_kernel_max_blocks_per_sm();
+int base_kernel_max_blocks_per_sm();
+
+}  // namespace gtk

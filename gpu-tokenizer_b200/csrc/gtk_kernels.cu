@@ -1,0 +1,914 @@
+// gtk_kernels.cu -- sm_100a kernels of the greedy byte-level BPE path.
+//
+//   chunker      text lengths -> chunk counts -> exclusive scan -> chunk start
+//                offsets (replaces the host chunk/flatten loops of the
+//                reference, gputok_binding.cu:718-752)
+//   merge (opt)  persistent CTAs walk the byte stream in tiles; a tile is cut
+//                into never-merge segments, short segments are merged by one
+//                thread each, long ones by a warp, oversize ones by the CTA
+//                in an HBM workspace (replaces bpe_merge_kernel_optimized's
+//                role as the fast entry point, gputok_binding.cu:704-846, with
+//                the greedy rule of gputok_blockbpe.cu:248-300)
+//   merge (base) one CTA per chunk runs Algorithm 1 pass by pass on the whole
+//                chunk (replaces bpe_merge_kernel_blockbpe,
+//                gputok_blockbpe.cu:328-538)
+//   output       exclusive scans over per-unit and per-chunk token counts and
+//                a pack kernel that writes int32 ids back to back (replaces
+//                the padded D2H + host unflatten, gputok_binding.cu:807-836)
+//
+// Nothing here is a dense contraction: the kernels are integer/byte work bound
+// by shared-memory and issue throughput, so there is no tensor-core code.
+#include "gtk_device.cuh"
+
+namespace gtk {
+namespace {
+
+constexpr uint32_t NONE = 0xFFFFu;  // pair not mergeable
+constexpr uint32_t SEL  = 0xFFFEu;  // pair selected for the current pass
+constexpr uint32_t DEAD = 0xFFFFu;  // token slot holds nothing
+
+// ------------------------------------------------------------------------------------------------
+// merge table probes
+// ------------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t probe_rank(const DeviceTable& T, uint32_t left, uint32_t right)
+{
+  const uint64_t key  = (uint64_t(left) << 32) | uint64_t(right);
+  const uint32_t mask = (1u << T.log2_capacity) - 1u;
+  uint32_t h          = uint32_t((key * 0x9E3779B97F4A7C15ull) >> (64 - T.log2_capacity));
+  for (uint32_t d = 0; d <= T.max_probe; ++d) {
+    const uint4 s = __ldg(T.slots + h);
+    if (s.x == right && s.y == left) return s.z;
+    if ((s.x & s.y) == 0xFFFFFFFFu) return NONE;
+    h = (h + 1u) & mask;
+  }
+  return NONE;
+}
+
+__device__ __forceinline__ uint32_t merged_id(const DeviceTable& T, uint32_t rank)
+{
+  return T.merged_is_256_plus_rank ? 256u + rank : __ldg(T.merged_of_rank + rank);
+}
+
+__device__ __forceinline__ bool adj_bit(const uint32_t* adj, uint32_t u, uint32_t v)
+{
+  const uint32_t bit = (u << 8) | v;
+  return (adj[bit >> 5] >> (bit & 31u)) & 1u;
+}
+
+__device__ __forceinline__ uint32_t lanemask_lt()
+{
+  uint32_t m;
+  asm("mov.u32 %0, %%lanemask_lt;" : "=r"(m));
+  return m;
+}
+
+// ------------------------------------------------------------------------------------------------
+// One thread merges one short segment (<= 64 tokens) in place.
+//
+// tok[0..L) / rk[0..L) live in shared memory; rk[i] is the rank of the pair
+// (token i, next live token), NONE for the last one.  Dead slots become DEAD
+// tombstones and stay where they are; the alive set is a 64-bit register
+// mask.  Every step merges the left-most pair of lowest rank -- Algorithm 1
+// restricted to the segment -- and re-probes the two pairs next to it.
+// ------------------------------------------------------------------------------------------------
+__device__ void thread_merge(uint16_t* tok, uint16_t* rk, int L, const DeviceTable& T)
+{
+  uint64_t alive = (L >= 64) ? ~0ull : ((1ull << L) - 1ull);
+  for (int step = 0; step < L; ++step) {
+    uint32_t best = 0xFFFFFFFFu;
+    uint64_t m    = alive & ~(1ull << (63 - __clzll((long long)alive)));  // every live slot but the last
+    while (m) {
+      const int j = __ffsll((long long)m) - 1;
+      m &= m - 1;
+      const uint32_t v = (uint32_t(rk[j]) << 16) | uint32_t(j);
+      best             = min(best, v);
+    }
+    const uint32_t r = best >> 16;
+    if (r >= SEL) break;
+    const int j = int(best & 0xFFFFu);
+    const int q = j + __ffsll((long long)(alive >> (j + 1)));  // next live slot after j
+    const uint32_t c = merged_id(T, r);
+    tok[j] = uint16_t(c);
+    tok[q] = uint16_t(DEAD);
+    alive &= ~(1ull << q);
+    const uint64_t right = (q >= 63) ? 0ull : (alive >> (q + 1));
+    uint32_t rr          = NONE;
+    if (right) rr = probe_rank(T, c, tok[q + __ffsll((long long)right)]);
+    rk[j] = uint16_t(rr);
+    const uint64_t left = alive & ((1ull << j) - 1ull);
+    if (left) {
+      const int p = 63 - __clzll((long long)left);
+      rk[p]       = uint16_t(probe_rank(T, tok[p], c));
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// A group of NW warps (one warp, or the whole CTA) merges one sequence pass by
+// pass.  tok/rk may point to shared memory or to an HBM workspace.
+//
+// Pass = (1) group-wide minimum of the cached ranks, (2) select occurrences of
+// that pair, (3) write the merged id / a tombstone, (4) compact tokens and
+// ranks in place -- each thread keeps its elements in registers between the
+// read and the write, offsets come from warp ballots and popc plus a cross-warp
+// sum, (5) re-probe only the pairs that touch a new token.
+//
+// With a monotone table all non-overlapping occurrences of the winning pair,
+// taken left to right, are merged in one pass; this is what Algorithm 1 does
+// over consecutive passes because no merge at the minimum rank can expose a
+// lower rank.  Otherwise only the left-most occurrence is merged.
+// ------------------------------------------------------------------------------------------------
+struct GroupScratch {
+  uint32_t red[2][32];
+  uint32_t wsum[32];
+};
+
+template <int NW>
+__device__ __forceinline__ void gsync()
+{
+  if (NW == 1) __syncwarp();
+  else __syncthreads();
+}
+
+template <int NW>
+__device__ __forceinline__ uint32_t group_min(uint32_t v, GroupScratch* gs, int& parity, int lane, int warp)
+{
+  v = __reduce_min_sync(0xFFFFFFFFu, v);
+  if (NW > 1) {
+    if (lane == 0) gs->red[parity][warp] = v;
+    __syncthreads();
+    uint32_t x = (lane < NW) ? gs->red[parity][lane] : 0xFFFFFFFFu;
+    v          = __reduce_min_sync(0xFFFFFFFFu, x);
+    parity ^= 1;
+  }
+  return v;
+}
+
+template <int NW>
+__device__ int group_merge(uint16_t* tok, uint16_t* rk, int L, const DeviceTable& T, GroupScratch* gs,
+                           int* status)
+{
+  constexpr int G = NW * 32;
+  constexpr int E = 4;
+  const int lane  = threadIdx.x & 31;
+  const int warp  = (NW == 1) ? 0 : (threadIdx.x >> 5);
+  const int tid   = (NW == 1) ? lane : int(threadIdx.x);
+  const uint32_t lt = lanemask_lt();
+  int parity = 0;
+  int len    = L;
+  for (int pass = 0; pass < L && len >= 2; ++pass) {
+    // (1) lowest cached rank
+    uint32_t m = NONE;
+    for (int i = tid; i < len - 1; i += G) m = min(m, uint32_t(rk[i]));
+    m = group_min<NW>(m, gs, parity, lane, warp);
+    if (m >= SEL) break;
+    const uint32_t r = m;
+    const uint32_t c = merged_id(T, r);
+    const bool batch = T.monotone != 0;
+    const bool same  = batch && (__ldg(T.same_of_rank + r) != 0);
+    // (2) selection
+    if (!batch) {
+      uint32_t p = 0xFFFFFFFFu;
+      for (int i = tid; i < len - 1; i += G)
+        if (rk[i] == r) { p = uint32_t(i); break; }
+      p = group_min<NW>(p, gs, parity, lane, warp);
+      gsync<NW>();
+      if (tid == 0) rk[p] = uint16_t(SEL);
+      gsync<NW>();
+    } else if (same) {
+      // occurrences of (a,a) overlap inside a run a a a ...; left to right
+      // selection keeps the even offsets of every maximal run of matches
+      for (int i = tid; i < len - 1; i += G) {
+        if (rk[i] != r) continue;
+        if (i > 0) {
+          const uint32_t pv = rk[i - 1];
+          if (pv == r || pv == SEL) continue;  // not the first match of its run
+        }
+        int j = i;
+        for (;;) {
+          rk[j] = uint16_t(SEL);
+          if (j + 2 < len - 1 && rk[j + 1] == r && rk[j + 2] == r) j += 2;
+          else break;
+        }
+      }
+      gsync<NW>();
+    }
+    const uint32_t pick = (!batch || same) ? SEL : r;
+    // (3) apply
+    for (int i = tid; i < len - 1; i += G) {
+      if (rk[i] == pick) {
+        tok[i]     = uint16_t(c);
+        tok[i + 1] = uint16_t(DEAD);
+      }
+    }
+    gsync<NW>();
+    // (4) in-place compaction, batch by batch, registers as the second buffer
+    int out = 0;
+    for (int base = 0; base < len; base += G * E) {
+      uint16_t t[E], q[E];
+      uint32_t bal[E];
+      int wt = 0;
+#pragma unroll
+      for (int k = 0; k < E; ++k) {
+        const int i = base + warp * 32 * E + k * 32 + lane;
+        const bool v = i < len;
+        t[k]   = v ? tok[i] : uint16_t(DEAD);
+        q[k]   = v ? rk[i] : uint16_t(NONE);
+        bal[k] = __ballot_sync(0xFFFFFFFFu, t[k] != DEAD);
+        wt += __popc(bal[k]);
+      }
+      int pre = 0, tot = wt;
+      if (NW > 1) {
+        if (lane == 0) gs->wsum[warp] = uint32_t(wt);
+        __syncthreads();  // all loads of the batch are done, warp totals visible
+        tot = 0;
+        for (int w = 0; w < NW; ++w) {
+          const int x = int(gs->wsum[w]);
+          if (w < warp) pre += x;
+          tot += x;
+        }
+      } else {
+        __syncwarp();
+      }
+      int o = out + pre;
+#pragma unroll
+      for (int k = 0; k < E; ++k) {
+        if (t[k] != DEAD) {
+          const int d = o + __popc(bal[k] & lt);
+          tok[d] = t[k];
+          rk[d]  = q[k];
+        }
+        o += __popc(bal[k]);
+      }
+      out += tot;
+      gsync<NW>();
+    }
+    if (out >= len) {  // a pass must remove at least one token
+      if (tid == 0 && status) atomicMax(status, int(kStatusBadSegment));
+      break;
+    }
+    len = out;
+    // (5) refresh ranks next to new tokens
+    for (int d = tid; d < len; d += G) {
+      if (tok[d] == c) {
+        rk[d] = uint16_t((d + 1 < len) ? probe_rank(T, c, tok[d + 1]) : NONE);
+        if (d > 0) rk[d - 1] = uint16_t(probe_rank(T, tok[d - 1], c));
+      }
+    }
+    gsync<NW>();
+  }
+  return len;
+}
+
+// ------------------------------------------------------------------------------------------------
+// block-wide helpers
+// ------------------------------------------------------------------------------------------------
+
+// exclusive scan of one int per thread over the CTA; *total receives the sum.
+// `buf` must hold 33 ints of shared memory; contains two barriers.
+__device__ __forceinline__ int block_exclusive_scan(int v, int* buf, int* total)
+{
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  int inc = v;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int y = __shfl_up_sync(0xFFFFFFFFu, inc, d);
+    if (lane >= d) inc += y;
+  }
+  if (lane == 31) buf[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    int w = (lane < nw) ? buf[lane] : 0;
+    int winc = w;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int y = __shfl_up_sync(0xFFFFFFFFu, winc, d);
+      if (lane >= d) winc += y;
+    }
+    buf[lane] = winc - w;
+    if (lane == 31) buf[32] = winc;
+  }
+  __syncthreads();
+  *total = buf[32];
+  return buf[warp] + inc - v;
+}
+
+// ------------------------------------------------------------------------------------------------
+// multi-block exclusive scan: counts (int32 array, or chunks-per-text computed
+// on the fly) -> int64 offsets[n+1].  Three kernels: per-block sums, scan of
+// the block sums by one CTA, final pass.  n may live on the device.
+// ------------------------------------------------------------------------------------------------
+constexpr int kScanThreads = 256;
+constexpr int kScanItems   = 16;
+constexpr int kScanBlock   = kScanThreads * kScanItems;
+
+struct CountsI32 {
+  const int32_t* p;
+  __device__ int64_t operator()(int64_t i) const { return p[i]; }
+};
+struct ChunksPerText {
+  const int64_t* off;
+  int chunk;
+  __device__ int64_t operator()(int64_t i) const
+  {
+    const int64_t len = off[i + 1] - off[i];
+    return len <= 0 ? 0 : (len + chunk - 1) / chunk;
+  }
+};
+
+__device__ __forceinline__ int64_t block_sum_i64(int64_t v, int64_t* buf)
+{
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, d);
+  if (lane == 0) buf[warp] = v;
+  __syncthreads();
+  int64_t s = 0;
+  for (int w = 0; w < kScanThreads / 32; ++w) s += buf[w];
+  __syncthreads();
+  return s;
+}
+
+template <class In>
+__global__ void __launch_bounds__(kScanThreads) k_scan_partial(In in, int64_t n_imm, const int64_t* n_ptr,
+                                                               int64_t* block_sums)
+{
+  __shared__ int64_t buf[kScanThreads / 32];
+  const int64_t n    = n_ptr ? *n_ptr : n_imm;
+  const int64_t base = int64_t(blockIdx.x) * kScanBlock;
+  int64_t s          = 0;
+  for (int e = 0; e < kScanItems; ++e) {
+    const int64_t i = base + int64_t(e) * kScanThreads + threadIdx.x;
+    if (i < n) s += in(i);
+  }
+  s = block_sum_i64(s, buf);
+  if (threadIdx.x == 0) block_sums[blockIdx.x] = s;
+}
+
+// one CTA: exclusive scan of block_sums[0..nb) in place
+__global__ void __launch_bounds__(kScanThreads) k_scan_block_sums(int64_t* block_sums, int64_t nb)
+{
+  __shared__ int64_t wtot[kScanThreads / 32];
+  __shared__ int64_t carry_s;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) carry_s = 0;
+  __syncthreads();
+  for (int64_t base = 0; base < nb; base += kScanThreads) {
+    const int64_t i = base + threadIdx.x;
+    const int64_t v = (i < nb) ? block_sums[i] : 0;
+    int64_t inc     = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int64_t y = __shfl_up_sync(0xFFFFFFFFu, inc, d);
+      if (lane >= d) inc += y;
+    }
+    if (lane == 31) wtot[warp] = inc;
+    __syncthreads();
+    int64_t pre = carry_s;
+    for (int w = 0; w < warp; ++w) pre += wtot[w];
+    if (i < nb) block_sums[i] = pre + inc - v;
+    __syncthreads();
+    if (threadIdx.x == kScanThreads - 1) carry_s = pre + inc;
+    __syncthreads();
+  }
+}
+
+template <class In>
+__global__ void __launch_bounds__(kScanThreads) k_scan_final(In in, int64_t n_imm, const int64_t* n_ptr,
+                                                             const int64_t* block_sums, int64_t* out,
+                                                             int64_t* total_out)
+{
+  __shared__ int64_t wtot[kScanThreads / 32];
+  const int64_t n = n_ptr ? *n_ptr : n_imm;
+  if (n == 0) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+      out[0] = 0;
+      if (total_out) *total_out = 0;
+    }
+    return;
+  }
+  const int64_t base = int64_t(blockIdx.x) * kScanBlock;
+  if (base >= n) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // blocked layout: thread t owns items base + t*kScanItems .. +kScanItems
+  int64_t v[kScanItems];
+  int64_t s = 0;
+  const int64_t first = base + int64_t(threadIdx.x) * kScanItems;
+#pragma unroll
+  for (int e = 0; e < kScanItems; ++e) {
+    const int64_t i = first + e;
+    v[e] = (i < n) ? in(i) : 0;
+    s += v[e];
+  }
+  int64_t inc = s;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int64_t y = __shfl_up_sync(0xFFFFFFFFu, inc, d);
+    if (lane >= d) inc += y;
+  }
+  if (lane == 31) wtot[warp] = inc;
+  __syncthreads();
+  int64_t pre = block_sums[blockIdx.x];
+  for (int w = 0; w < warp; ++w) pre += wtot[w];
+  int64_t run = pre + inc - s;
+#pragma unroll
+  for (int e = 0; e < kScanItems; ++e) {
+    const int64_t i = first + e;
+    if (i < n) {
+      out[i] = run;
+      run += v[e];
+      if (i == n - 1) {
+        out[n] = run;
+        if (total_out) *total_out = run;
+      }
+    }
+  }
+}
+
+template <class In>
+int run_scan(In in, int64_t n_upper, int64_t n_imm, const int64_t* n_ptr, int64_t* block_sums, int64_t* out,
+             int64_t* total_out, cudaStream_t stream)
+{
+  int64_t nb = (n_upper + kScanBlock - 1) / kScanBlock;
+  if (nb < 1) nb = 1;
+  k_scan_partial<In><<<unsigned(nb), kScanThreads, 0, stream>>>(in, n_imm, n_ptr, block_sums);
+  k_scan_block_sums<<<1, kScanThreads, 0, stream>>>(block_sums, nb);
+  k_scan_final<In><<<unsigned(nb), kScanThreads, 0, stream>>>(in, n_imm, n_ptr, block_sums, out, total_out);
+  return 3;
+}
+
+// ------------------------------------------------------------------------------------------------
+// chunker
+// ------------------------------------------------------------------------------------------------
+
+// chunk c -> owning text by binary search over the scanned chunk counts, then
+// its start byte.  Empty texts own no chunk and are skipped by the search.
+__global__ void k_chunk_fill(const int64_t* __restrict__ text_off, const int64_t* __restrict__ text_chunk_base,
+                             int64_t n_texts, int chunk_bytes, int64_t* __restrict__ chunk_off)
+{
+  const int64_t C = text_chunk_base[n_texts];
+  for (int64_t c = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; c <= C; c += int64_t(gridDim.x) * blockDim.x) {
+    if (c == C) {
+      chunk_off[c] = text_off[n_texts];
+      continue;
+    }
+    int64_t lo = 0, hi = n_texts;  // last t with text_chunk_base[t] <= c
+    while (hi - lo > 1) {
+      const int64_t mid = (lo + hi) >> 1;
+      if (text_chunk_base[mid] <= c) lo = mid; else hi = mid;
+    }
+    chunk_off[c] = text_off[lo] + (c - text_chunk_base[lo]) * int64_t(chunk_bytes);
+  }
+}
+
+// tile k -> chunk that contains byte k*kTile
+__global__ void k_tile_chunk0(const int64_t* __restrict__ chunk_off, const int64_t* __restrict__ n_chunks_ptr,
+                              int64_t n_tiles, int32_t* __restrict__ tile_chunk0)
+{
+  const int64_t C = *n_chunks_ptr;
+  for (int64_t k = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; k < n_tiles; k += int64_t(gridDim.x) * blockDim.x) {
+    const int64_t pos = k * kTile;
+    int64_t lo = 0, hi = C;  // last c with chunk_off[c] <= pos (chunk_off[0] == 0)
+    while (hi - lo > 1) {
+      const int64_t mid = (lo + hi) >> 1;
+      if (chunk_off[mid] <= pos) lo = mid; else hi = mid;
+    }
+    tile_chunk0[k] = int32_t(lo);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// merge kernel, segment-parallel ("opt")
+// ------------------------------------------------------------------------------------------------
+
+constexpr int kCutWords = kWindow / 32;  // 144
+constexpr int kSegCap   = kTile / 2 + 8;
+constexpr int kLongCap  = 128;
+
+struct OptSmem {
+  alignas(16) uint8_t bytes[kWindow + 32];  // [15] = byte before the window, [16+i] = window position i
+  uint32_t adj[2048];
+  uint16_t tok[kWindow];
+  uint16_t rk[kWindow];  // reused as the compacted output buffer after merging
+  uint16_t seg[kSegCap];
+  uint32_t cut[kCutWords + 2];  // segment-start bits; reused as the alive bitmap
+  uint16_t woff[kCutWords + 2];
+  uint16_t longq[kLongCap];
+  GroupScratch gs;
+  int scanbuf[33];
+  int ticket;
+  int nseg, nlong;
+  int first_start, last_start, over_start;
+  int over_len;
+  long long over_end;
+  int over_chunk;
+};
+
+// first segment start strictly after window position s (words past the window are all ones)
+__device__ __forceinline__ int next_cut(const uint32_t* cut, int s)
+{
+  int w      = (s + 1) >> 5;
+  uint32_t x = cut[w] & (0xFFFFFFFFu << ((s + 1) & 31));
+  while (!x) x = cut[++w];
+  return w * 32 + __ffs(int(x)) - 1;
+}
+
+__global__ void __launch_bounds__(kOptThreads) k_merge_opt(EncodeBuffers b, DeviceTable T)
+{
+  __shared__ OptSmem S;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t lt = lanemask_lt();
+  const int64_t n   = b.n_bytes;
+  const int64_t C   = b.totals[0];
+  int* status       = b.counters + 1;
+
+  for (int i = tid; i < 2048; i += kOptThreads) S.adj[i] = T.adj[i];
+  if (tid < 2) S.cut[kCutWords + tid] = 0xFFFFFFFFu;
+  const bool aligned = (reinterpret_cast<uintptr_t>(b.bytes) & 15u) == 0;
+
+  for (;;) {
+    __syncthreads();
+    if (tid == 0) {
+      S.ticket      = atomicAdd(b.counters + 0, 1);
+      S.nlong       = 0;
+      S.first_start = kWindow;
+      S.last_start  = -1;
+      S.over_start  = -1;
+      S.over_len    = 0;
+    }
+    __syncthreads();
+    const int64_t k = S.ticket;
+    if (k >= b.n_tiles) break;
+    const int64_t lo = k * kTile;
+    const int wlen   = int(min(int64_t(kWindow), n - lo));
+    const int own    = int(min(int64_t(kTile), n - lo));
+
+    // ---- A. stage the window ----
+    if (aligned) {
+      for (int v = tid; v < kWindow / 16; v += kOptThreads) {
+        const int64_t pos = lo + int64_t(v) * 16;
+        uint4 x = make_uint4(0, 0, 0, 0);
+        if (pos + 16 <= n) {
+          x = __ldg(reinterpret_cast<const uint4*>(b.bytes + pos));
+        } else if (pos < n) {
+          uint8_t tmp[16];
+          for (int j = 0; j < 16; ++j) tmp[j] = (pos + j < n) ? b.bytes[pos + j] : uint8_t(0);
+          x = *reinterpret_cast<uint4*>(tmp);
+        }
+        *reinterpret_cast<uint4*>(&S.bytes[16 + v * 16]) = x;
+      }
+    } else {
+      for (int i = tid; i < kWindow; i += kOptThreads) S.bytes[16 + i] = (lo + i < n) ? b.bytes[lo + i] : uint8_t(0);
+    }
+    if (tid == 0) S.bytes[15] = (lo > 0) ? b.bytes[lo - 1] : uint8_t(0);
+    __syncthreads();
+
+    // ---- B. segment starts from the never-merge bitmap, initial ids and byte-pair ranks ----
+    for (int i = tid; i < kWindow; i += kOptThreads) {
+      const uint32_t cur = S.bytes[16 + i], prv = S.bytes[15 + i], nxt = S.bytes[17 + i];
+      const bool start   = (i >= wlen) || (lo + i == 0) || !adj_bit(S.adj, prv, cur);
+      const uint32_t bal = __ballot_sync(0xFFFFFFFFu, start);
+      if (lane == 0) S.cut[i >> 5] = bal;
+      S.tok[i] = (i < wlen) ? __ldg(T.byte_to_id + cur) : uint16_t(DEAD);
+      S.rk[i]  = (i + 1 < wlen) ? __ldg(T.byte_pair_rank + ((cur << 8) | nxt)) : uint16_t(NONE);
+    }
+    __syncthreads();
+
+    // ---- C. chunk boundaries are segment starts too ----
+    {
+      const int64_t c0 = b.tile_chunk0[k];
+      for (int64_t c = c0 + tid; c <= C; c += kOptThreads) {
+        const int64_t p = b.chunk_off[c] - lo;
+        if (p >= wlen) break;
+        if (p >= 0) {
+          atomicOr(&S.cut[p >> 5], 1u << (p & 31));
+          if (p > 0) S.rk[p - 1] = uint16_t(NONE);
+        }
+      }
+    }
+    __syncthreads();
+
+    // ---- D. list the owned segments that have at least two bytes ----
+    {
+      uint32_t m = 0;
+      if (tid < kTile / 32) {
+        const int w0        = tid * 32;
+        const uint32_t word = S.cut[tid], nextw = S.cut[tid + 1];
+        const uint32_t ownmask = (w0 + 32 <= own) ? 0xFFFFFFFFu : (w0 >= own ? 0u : ((1u << (own - w0)) - 1u));
+        const uint32_t starts  = word & ownmask;
+        if (starts) {
+          atomicMin(&S.first_start, w0 + __ffs(int(starts)) - 1);
+          atomicMax(&S.last_start, w0 + 31 - __clz(int(starts)));
+        }
+        m = starts & ~((word >> 1) | (nextw << 31));
+      }
+      int total;
+      int off = block_exclusive_scan(__popc(m), S.scanbuf, &total);
+      while (m) {
+        const int j = __ffs(int(m)) - 1;
+        m &= m - 1;
+        S.seg[off++] = uint16_t(tid * 32 + j);
+      }
+      if (tid == 0) S.nseg = total;
+    }
+    __syncthreads();
+
+    // ---- E. one thread per short segment ----
+    {
+      const int nseg = S.nseg;
+      for (int j = tid; j < nseg; j += kOptThreads) {
+        const int s = S.seg[j];
+        const int e = next_cut(S.cut, s);
+        const int L = e - s;
+        if (e >= kWindow && wlen == kWindow) {
+          S.over_start = s;  // runs past the window: finished in the HBM workspace below
+        } else if (L <= kThreadSegMax) {
+          thread_merge(S.tok + s, S.rk + s, L, T);
+        } else {
+          const int q = atomicAdd(&S.nlong, 1);
+          if (q < kLongCap) S.longq[q] = uint16_t(s);
+          else atomicMax(status, int(kStatusLongQueueOverflow));
+        }
+      }
+    }
+    __syncthreads();
+
+    // ---- F. one warp per long segment ----
+    {
+      const int nl = min(S.nlong, kLongCap);
+      for (int q = warp; q < nl; q += kOptThreads / 32) {
+        const int s   = S.longq[q];
+        const int L   = next_cut(S.cut, s) - s;
+        const int len = group_merge<1>(S.tok + s, S.rk + s, L, T, nullptr, status);
+        for (int i = len + lane; i < L; i += 32) S.tok[s + i] = uint16_t(DEAD);
+        __syncwarp();
+      }
+    }
+    __syncthreads();
+
+    // ---- G/H. compact the owned region [first, end) into S.rk, then to staging ----
+    const int first = S.first_start;
+    int end_owned   = 0;
+    if (S.last_start >= 0) end_owned = (S.over_start >= 0) ? S.over_start : next_cut(S.cut, S.last_start);
+    if (end_owned > wlen) end_owned = wlen;
+    __syncthreads();  // every thread has read cut[] before it becomes the alive bitmap
+    for (int w = warp; w < kCutWords; w += kOptThreads / 32) {
+      const int i       = w * 32 + lane;
+      const bool alive  = (i >= first) && (i < end_owned) && (S.tok[i] != DEAD);
+      const uint32_t bal = __ballot_sync(0xFFFFFFFFu, alive);
+      if (lane == 0) S.cut[w] = bal;
+    }
+    __syncthreads();
+    int total;
+    {
+      const int cnt = (tid < kCutWords) ? __popc(S.cut[tid]) : 0;
+      const int off = block_exclusive_scan(cnt, S.scanbuf, &total);
+      if (tid < kCutWords) S.woff[tid] = uint16_t(off);
+    }
+    __syncthreads();
+    for (int w = warp; w < kCutWords; w += kOptThreads / 32) {
+      const uint32_t bal = S.cut[w];
+      if ((bal >> lane) & 1u) S.rk[S.woff[w] + __popc(bal & lt)] = S.tok[w * 32 + lane];
+    }
+    __syncthreads();
+    const int64_t region_start = lo + ((first < kWindow) ? first : 0);
+    for (int j = tid; j < total; j += kOptThreads) b.staging[region_start + j] = S.rk[j];
+
+    // ---- I. per-chunk token counts from the alive bitmap ----
+    {
+      const int64_t region_end = lo + end_owned;
+      for (int64_t c = b.tile_chunk0[k] + warp; c < C; c += kOptThreads / 32) {
+        const int64_t cs_g = b.chunk_off[c];
+        if (cs_g >= region_end) break;
+        const int64_t ce_g = b.chunk_off[c + 1];
+        const int cs = int(max(cs_g, region_start) - lo);
+        const int ce = int(min(ce_g, region_end) - lo);
+        if (ce <= cs) continue;
+        int cnt = 0;
+        for (int w = (cs >> 5) + lane; w <= ((ce - 1) >> 5); w += 32) {
+          uint32_t x = S.cut[w];
+          if (w == (cs >> 5)) x &= 0xFFFFFFFFu << (cs & 31);
+          if (w == ((ce - 1) >> 5)) x &= 0xFFFFFFFFu >> (31 - ((ce - 1) & 31));
+          cnt += __popc(x);
+        }
+        cnt = __reduce_add_sync(0xFFFFFFFFu, cnt);
+        if (lane == 0 && cnt) atomicAdd(b.chunk_cnt + c, cnt);
+      }
+    }
+
+    // ---- J. a segment that runs past the window (rare): whole CTA, HBM workspace ----
+    if (S.over_start >= 0) {  // CTA-uniform
+      const int64_t gs0 = lo + S.over_start;
+      if (tid == 0) {
+        int64_t c = b.tile_chunk0[k];
+        while (c + 1 < C && b.chunk_off[c + 1] <= gs0) ++c;
+        S.over_chunk = int(c);
+        S.over_end   = b.chunk_off[c + 1];
+      }
+      __syncthreads();
+      // first never-merge boundary after the window, at most the chunk end
+      const int64_t cend = S.over_end;
+      int64_t ge         = cend;
+      for (int64_t pos = lo + kWindow; pos < cend; pos += kOptThreads) {
+        const int64_t p = pos + tid;
+        const bool cutp = (p < cend) && !adj_bit(S.adj, b.bytes[p - 1], b.bytes[p]);
+        if (__syncthreads_or(cutp)) {
+          if (cutp) atomicMin(reinterpret_cast<unsigned long long*>(&S.over_end), (unsigned long long)p);
+          __syncthreads();
+          ge = S.over_end;
+          break;
+        }
+      }
+      const int64_t L64 = ge - gs0;
+      if (L64 > b.seg_scratch_tokens || b.seg_scratch == nullptr) {
+        if (tid == 0) atomicMax(status, int(kStatusScratchTooSmall));
+      } else {
+        const int L    = int(L64);
+        uint16_t* wtok = b.seg_scratch + int64_t(blockIdx.x) * 2 * b.seg_scratch_tokens;
+        uint16_t* wrk  = wtok + b.seg_scratch_tokens;
+        for (int i = tid; i < L; i += kOptThreads) {
+          const uint32_t cur = b.bytes[gs0 + i];
+          wtok[i] = __ldg(T.byte_to_id + cur);
+          wrk[i]  = (i + 1 < L) ? __ldg(T.byte_pair_rank + ((cur << 8) | b.bytes[gs0 + i + 1])) : uint16_t(NONE);
+        }
+        __syncthreads();
+        const int len = group_merge<kOptThreads / 32>(wtok, wrk, L, T, &S.gs, status);
+        for (int j = tid; j < len; j += kOptThreads) b.staging[region_start + total + j] = wtok[j];
+        if (tid == 0) {
+          atomicAdd(b.chunk_cnt + S.over_chunk, len);
+          S.over_len = len;
+        }
+      }
+      __syncthreads();
+    }
+
+    // ---- K. unit record ----
+    if (tid == 0) {
+      b.unit_first[k] = region_start;
+      b.unit_cnt[k]   = total + S.over_len;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// merge kernel, one CTA per chunk ("base")
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kBaseThreads) k_merge_base(EncodeBuffers b, DeviceTable T)
+{
+  __shared__ uint16_t s_tok[kBaseSmemTokens];
+  __shared__ uint16_t s_rk[kBaseSmemTokens];
+  __shared__ GroupScratch gs;
+  __shared__ int ticket;
+  const int tid   = threadIdx.x;
+  const int64_t C = b.totals[0];
+  int* status     = b.counters + 1;
+  for (;;) {
+    __syncthreads();
+    if (tid == 0) ticket = atomicAdd(b.counters + 2, 1);
+    __syncthreads();
+    const int64_t c = ticket;
+    if (c >= C) break;
+    const int64_t cs  = b.chunk_off[c];
+    const int64_t L64 = b.chunk_off[c + 1] - cs;
+    uint16_t *tok = s_tok, *rk = s_rk;
+    if (L64 > kBaseSmemTokens) {
+      if (L64 > b.seg_scratch_tokens || b.seg_scratch == nullptr) {
+        if (tid == 0) {
+          atomicMax(status, int(kStatusScratchTooSmall));
+          b.chunk_cnt[c] = 0;
+        }
+        continue;
+      }
+      tok = b.seg_scratch + int64_t(blockIdx.x) * 2 * b.seg_scratch_tokens;
+      rk  = tok + b.seg_scratch_tokens;
+    }
+    const int L = int(L64);
+    for (int i = tid; i < L; i += kBaseThreads) {
+      const uint32_t cur = b.bytes[cs + i];
+      tok[i] = __ldg(T.byte_to_id + cur);
+      rk[i]  = (i + 1 < L) ? __ldg(T.byte_pair_rank + ((cur << 8) | b.bytes[cs + i + 1])) : uint16_t(NONE);
+    }
+    __syncthreads();
+    const int len = group_merge<kBaseThreads / 32>(tok, rk, L, T, &gs, status);
+    for (int j = tid; j < len; j += kBaseThreads) b.staging[cs + j] = tok[j];
+    if (tid == 0) b.chunk_cnt[c] = len;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// output: pack staged 16-bit tokens of every unit into the int32 id buffer
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_pack(const uint16_t* __restrict__ staging, const int64_t* __restrict__ first,
+                                              const int32_t* __restrict__ cnt, const int64_t* __restrict__ base,
+                                              int64_t n_units_imm, const int64_t* n_units_ptr,
+                                              int32_t* __restrict__ out, int64_t capacity)
+{
+  const int64_t U = n_units_ptr ? *n_units_ptr : n_units_imm;
+  for (int64_t u = blockIdx.x; u < U; u += gridDim.x) {
+    const int64_t src = first[u], dst = base[u];
+    const int m = cnt[u];
+    for (int j = threadIdx.x; j < m; j += blockDim.x)
+      if (dst + j < capacity) out[dst + j] = int32_t(staging[src + j]);
+  }
+}
+
+__global__ void k_text_id_off(const int64_t* __restrict__ text_chunk_base, const int64_t* __restrict__ chunk_id_off,
+                              int64_t n_texts, int64_t* __restrict__ text_id_off)
+{
+  for (int64_t t = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; t <= n_texts; t += int64_t(gridDim.x) * blockDim.x)
+    text_id_off[t] = chunk_id_off[text_chunk_base[t]];
+}
+
+inline unsigned grid_for(int64_t items, int threads, int64_t cap = 65535)
+{
+  int64_t g = (items + threads - 1) / threads;
+  if (g < 1) g = 1;
+  if (g > cap) g = cap;
+  return unsigned(g);
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------------
+// launchers
+// ------------------------------------------------------------------------------------------------
+
+int launch_chunker(const EncodeBuffers& b, cudaStream_t stream)
+{
+  int launches = run_scan(ChunksPerText{b.text_off, b.chunk_bytes}, b.n_texts, b.n_texts, nullptr,
+                          b.scan_block_sums, b.text_chunk_base, b.totals + 0, stream);
+  k_chunk_fill<<<grid_for(b.chunk_cap + 1, 256, 2048), 256, 0, stream>>>(b.text_off, b.text_chunk_base, b.n_texts,
+                                                                         b.chunk_bytes, b.chunk_off);
+  ++launches;
+  if (b.n_tiles > 0) {
+    k_tile_chunk0<<<grid_for(b.n_tiles, 256, 2048), 256, 0, stream>>>(b.chunk_off, b.totals + 0, b.n_tiles,
+                                                                      b.tile_chunk0);
+    ++launches;
+  }
+  return launches;
+}
+
+int launch_merge_opt(const EncodeBuffers& b, const DeviceTable& t, int grid, cudaStream_t stream)
+{
+  if (b.n_tiles <= 0) return 0;
+  if (grid > b.n_tiles) grid = int(b.n_tiles);
+  k_merge_opt<<<grid, kOptThreads, 0, stream>>>(b, t);
+  return 1;
+}
+
+int launch_merge_base(const EncodeBuffers& b, const DeviceTable& t, int grid, cudaStream_t stream)
+{
+  if (b.n_bytes <= 0) return 0;
+  if (grid > b.chunk_cap) grid = int(b.chunk_cap);
+  if (grid < 1) grid = 1;
+  k_merge_base<<<grid, kBaseThreads, 0, stream>>>(b, t);
+  return 1;
+}
+
+int launch_output_scans(const EncodeBuffers& b, int mode_base, cudaStream_t stream)
+{
+  int launches = 0;
+  // per-chunk counts -> packed id offset of every chunk (+ total id count)
+  launches += run_scan(CountsI32{b.chunk_cnt}, b.chunk_cap, 0, b.totals + 0, b.scan_block_sums, b.chunk_id_off,
+                       b.totals + 1, stream);
+  if (!mode_base && b.n_tiles > 0) {
+    launches += run_scan(CountsI32{b.unit_cnt}, b.n_tiles, b.n_tiles, nullptr, b.scan_block_sums, b.unit_base,
+                         nullptr, stream);
+  }
+  if (b.text_id_off) {
+    k_text_id_off<<<grid_for(b.n_texts + 1, 256, 2048), 256, 0, stream>>>(b.text_chunk_base, b.chunk_id_off,
+                                                                          b.n_texts, b.text_id_off);
+    ++launches;
+  }
+  return launches;
+}
+
+int launch_pack(const EncodeBuffers& b, int mode_base, int grid, cudaStream_t stream)
+{
+  if (b.n_bytes <= 0) return 0;
+  if (mode_base) {
+    k_pack<<<grid, 256, 0, stream>>>(b.staging, b.chunk_off, b.chunk_cnt, b.chunk_id_off, 0, b.totals + 0, b.out_ids,
+                                     b.out_capacity);
+  } else {
+    k_pack<<<grid, 256, 0, stream>>>(b.staging, b.unit_first, b.unit_cnt, b.unit_base, b.n_tiles, nullptr, b.out_ids,
+                                     b.out_capacity);
+  }
+  return 1;
+}
+
+int opt_kernel_max_blocks_per_sm()
+{
+  int nb = 0;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, k_merge_opt, kOptThreads, 0);
+  return nb;
+}
+
+int base_kernel_max_blocks_per_sm()
+{
+  int nb = 0;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, k_merge_base, kBaseThreads, 0);
+  return nb;
+}
+
+}  // namespace gtk

@@ -1,0 +1,97 @@
+// gtk_table.hpp -- host side of the merge table: byte encoder, merges.txt
+// parser, vocabulary, and the flat arrays the kernels read from HBM.
+//
+// Behaviour follows the reference's ByteEncoder / BPEVocab /
+// build_vocab_and_merges (gputok_blockbpe.cu:64-236); the data layout is new:
+// an open-addressing hash table with 16-byte slots, a dense 256x256 rank table
+// for byte pairs, per-rank merged ids and a never-merge bigram bitmap.
+#pragma once
+#include <cstdint>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+namespace gtk {
+
+constexpr uint32_t kNoRank16 = 0xFFFFu;  // "pair not mergeable" in the 16-bit rank arrays
+constexpr uint32_t kSelRank16 = 0xFFFEu; // transient "selected for this pass" marker
+constexpr uint32_t kDeadTok16 = 0xFFFFu; // tombstone in the 16-bit token arrays
+constexpr uint64_t kEmptyKey = 0xFFFFFFFFFFFFFFFFull;
+
+// One slot of the device hash table: 64-bit (left,right) key, 32-bit rank,
+// 32-bit merged id.  16 bytes so a probe is a single 128-bit load.
+struct alignas(16) HashSlot {
+  uint32_t key_lo;  // right id
+  uint32_t key_hi;  // left id
+  uint32_t rank;
+  uint32_t merged;
+};
+
+struct MergeRow {
+  int32_t  left, right;
+  uint32_t rank;
+  int32_t  merged;
+};
+
+inline uint64_t pair_key(uint32_t left, uint32_t right) { return (uint64_t(left) << 32) | uint64_t(right); }
+
+// Multiplicative hash shared by host and device (same constant in gtk_device.cuh).
+inline uint32_t pair_hash(uint64_t key, uint32_t log2_capacity)
+{
+  return uint32_t((key * 0x9E3779B97F4A7C15ull) >> (64 - log2_capacity));
+}
+
+class HostTable {
+ public:
+  // Throws std::runtime_error for an unreadable / empty file (as the reference does).
+  explicit HostTable(const std::string& merges_path);
+
+  // vocabulary
+  std::vector<std::string> id_to_symbols;               // token id -> GPT-2 symbol string
+  std::unordered_map<std::string, int32_t> symbols_to_id;
+  std::vector<std::string> id_to_bytes;                 // token id -> raw bytes ("" + !decodable if impossible)
+  std::vector<uint8_t> decodable;
+  uint16_t byte_to_id[256];
+
+  // merges, unique pairs in rank order
+  std::vector<MergeRow> rows;
+  uint32_t max_rank = 0;
+
+  // flat arrays for the device
+  std::vector<HashSlot> slots;
+  uint32_t log2_capacity = 0;
+  uint32_t max_probe = 0;                  // longest displacement of a stored key
+  std::vector<uint16_t> byte_pair_rank;    // [256*256], index (u<<8|v) on raw bytes, kNoRank16 if none
+  std::vector<uint32_t> merged_of_rank;    // [max_rank+1]
+  std::vector<uint8_t> same_of_rank;       // [max_rank+1]: 1 if left == right
+  uint32_t adj[2048];                      // bit (u<<8|v): bigram occurs inside a merge result
+  int adj_count = 0;
+
+  // properties the kernels rely on
+  bool monotone = false;        // rank(m) > rank of every merge producing one of m's parts
+  bool merged_is_256_plus_rank = false;
+  bool byte_ids_identity = false;
+  bool fits_u16 = false;        // ids < 0xFFFF and ranks < 0xFFFE
+
+  // host lookup through the same hash layout the device uses
+  bool find(int32_t left, int32_t right, uint32_t* rank, int32_t* merged) const;
+
+  bool can_merge_across(uint8_t u, uint8_t v) const
+  {
+    uint32_t bit = (uint32_t(u) << 8) | v;
+    return (adj[bit >> 5] >> (bit & 31)) & 1u;
+  }
+
+  // Host reference tokenizers (serve GpuTokenizer.tokenize_batch_cpu; never a fallback).
+  // Greedy rule on one chunk of raw bytes; appends ids to out.
+  void greedy_chunk(const uint8_t* bytes, int64_t n, std::vector<int32_t>& out) const;
+  // The binding's local-minimum rule with a pass cap, on one text.
+  void localmin_text(const uint8_t* bytes, int64_t n, int max_iters, std::vector<int32_t>& out) const;
+
+ private:
+  int32_t add_token(const std::string& symbols);
+  void build_hash();
+  void build_derived();
+};
+
+}  // namespace gtk

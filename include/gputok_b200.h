@@ -1,0 +1,175 @@
+/*
+ * gputok_b200.h -- C ABI of the B200-native greedy byte-level BPE tokenizer.
+ *
+ * This is the drop-in boundary for the reference's `GpuTokenizer` class
+ * (gputok_binding.cu:650-1011, exported to Python at :1015-1065).  Every entry
+ * point is `extern "C"`, takes plain pointers and sizes, returns an `int`
+ * status (GTK_OK == 0) and never throws or exits; the message of the last
+ * failure is available from gtk_last_error() / gtk_global_error().
+ *
+ * Semantics shared by all encode entry points (reference:
+ * gputok_binding.cu:704-752, 823-836):
+ *   - a batch is `n_texts` byte strings laid back to back in one buffer;
+ *     text t is bytes[text_offsets[t] .. text_offsets[t+1]), text_offsets[0]
+ *     must be 0 and the array non-decreasing;
+ *   - every text is cut into chunks of `chunk_tokens` bytes (the last chunk of
+ *     a text may be shorter, an empty text has no chunk); chunks are tokenised
+ *     independently with the greedy rule (globally lowest merge rank, left-most
+ *     occurrence, one merge at a time until no adjacent pair is mergeable:
+ *     bpe_merge_cpu_greedy, gputok_blockbpe.cu:248-300);
+ *   - token ids live in the reference's id space: ids 0..255 are the byte
+ *     values, merge number r (0-based line of merges.txt after the header)
+ *     creates id 256+r for a well-formed table (build_vocab_and_merges,
+ *     gputok_blockbpe.cu:178-236);
+ *   - the result is packed: all ids of the batch back to back in chunk order,
+ *     int64 offsets per chunk and per text.
+ */
+#ifndef GPUTOK_B200_H
+#define GPUTOK_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define GTK_API __attribute__((visibility("default")))
+#else
+#define GTK_API
+#endif
+
+/* status codes */
+enum {
+  GTK_OK               = 0,
+  GTK_ERR_INVALID_ARG  = 1, /* e.g. chunk_tokens <= 0 (std::invalid_argument, gputok_binding.cu:661-663) */
+  GTK_ERR_IO           = 2, /* merges file unreadable or empty (std::runtime_error, :153-161) */
+  GTK_ERR_CUDA         = 3, /* a CUDA runtime call failed (the reference prints and exit()s, :24-30) */
+  GTK_ERR_CAPACITY     = 4, /* a caller-provided output buffer is too small */
+  GTK_ERR_TABLE        = 5, /* merge table outside what the 16-bit kernels support */
+  GTK_ERR_NO_DEVICE    = 6, /* GPU entry point called on a host-only handle */
+  GTK_ERR_KERNEL       = 7  /* a kernel reported an internal inconsistency through its status word */
+};
+
+/* which merge kernel serves the call */
+enum {
+  GTK_MODE_OPT  = 0, /* GpuTokenizer::tokenize_batch               (gputok_binding.cu:704-846) */
+  GTK_MODE_BASE = 1  /* GpuTokenizer::tokenize_batch_blockbpe_base (gputok_binding.cu:850-989) */
+};
+
+/* merge rule of the host reference entry point */
+enum {
+  GTK_RULE_GREEDY   = 0, /* bpe_merge_cpu_greedy, per chunk (gputok_blockbpe.cu:248-300) */
+  GTK_RULE_LOCALMIN = 1  /* bpe_merge_cpu, whole text, max_iters passes (gputok_binding.cu:200-270, 992-1003) */
+};
+
+typedef struct gtk_tokenizer gtk_tokenizer;
+
+typedef struct gtk_table_info {
+  int32_t  vocab_size;       /* number of token ids (50 256 for GPT-2 merges.txt) */
+  int32_t  num_merges;       /* distinct (left,right) pairs in the table */
+  uint32_t max_rank;         /* highest rank present */
+  uint32_t hash_capacity;    /* slots of the open-addressing table (power of two) */
+  uint32_t hash_max_probe;   /* longest probe sequence of any stored key */
+  uint32_t hash_bytes;       /* bytes of the slot array in HBM */
+  int32_t  monotone;         /* 1: every merge has a higher rank than the merges that create its parts */
+  int32_t  merged_is_256_plus_rank; /* 1: merged id == 256 + rank for every merge */
+  int32_t  byte_ids_identity;       /* 1: id of byte b == b for all 256 bytes */
+  int32_t  adj_bigrams;      /* byte bigrams that occur inside at least one merge result */
+  int32_t  chunk_tokens;
+  int32_t  max_iters;
+  int32_t  device;           /* CUDA device ordinal, -1 for a host-only handle */
+  int32_t  sm_count;
+} gtk_table_info;
+
+/* Library version string. */
+GTK_API const char* gtk_version(void);
+
+/* Message of the last failure that had no handle to attach to (gtk_create). Thread-local. */
+GTK_API const char* gtk_global_error(void);
+
+/* Replaces GpuTokenizer::GpuTokenizer(merges_path, chunk_tokens, max_iters)
+ * (gputok_binding.cu:652-701): parses merges.txt, rebuilds the vocabulary,
+ * builds the merge-rank hash table, the byte-pair rank table and the
+ * never-merge bigram bitmap and uploads them to `device`.
+ * chunk_tokens <= 0 -> GTK_ERR_INVALID_ARG; max_iters <= 0 -> 50 (as :664-666).
+ * device == -1 builds a host-only handle: the GPU entry points then return
+ * GTK_ERR_NO_DEVICE (there is no CPU fallback); gtk_encode_cpu still works. */
+GTK_API int gtk_create(const char* merges_path, int chunk_tokens, int max_iters, int device,
+                       gtk_tokenizer** out);
+
+/* Replaces the destructor of GpuTokenizer (frees the table and all arenas). */
+GTK_API void gtk_destroy(gtk_tokenizer* h);
+
+GTK_API const char* gtk_last_error(const gtk_tokenizer* h);
+
+GTK_API int gtk_table_info_get(const gtk_tokenizer* h, gtk_table_info* out);
+
+/* Replaces tokenize_batch (mode GTK_MODE_OPT, gputok_binding.cu:704-846) and
+ * tokenize_batch_blockbpe_base (mode GTK_MODE_BASE, :850-989) for HOST input.
+ * Copies the batch to the device (fastest from pinned memory, see
+ * gtk_pinned_alloc), runs chunker -> merge kernel -> output scan/pack, copies
+ * ids and offsets back into pinned buffers owned by the handle.
+ * *kernel_ms (optional) receives the device time of the kernel pipeline
+ * (cudaEvent pair, as :790-805).  Results stay valid until the next call on
+ * the handle; read them with gtk_result_sizes/_view/_copy.
+ * An empty batch or a batch of empty texts is not an error: 0 ids, 0 chunks. */
+GTK_API int gtk_encode(gtk_tokenizer* h, int mode, const uint8_t* bytes, const int64_t* text_offsets,
+                       int64_t n_texts, float* kernel_ms);
+
+/* Replaces tokenize_batch_cpu (gputok_binding.cu:992-1003): host-only
+ * reference tokenizer.  GTK_RULE_GREEDY (default of the Python surface) runs
+ * the greedy rule per chunk; GTK_RULE_LOCALMIN reproduces the reference
+ * method's own rule on the un-chunked text.  Never used as a fallback. */
+GTK_API int gtk_encode_cpu(gtk_tokenizer* h, int rule, const uint8_t* bytes, const int64_t* text_offsets,
+                           int64_t n_texts);
+
+/* Sizes of the result of the last gtk_encode / gtk_encode_cpu. */
+GTK_API int gtk_result_sizes(const gtk_tokenizer* h, int64_t* n_ids, int64_t* n_chunks, int64_t* n_texts);
+
+/* Zero-copy view of the last result (replaces the unflatten loop,
+ * gputok_binding.cu:823-836): ids[n_ids], text_id_offsets[n_texts+1]
+ * (text t owns ids[text_id_offsets[t] .. text_id_offsets[t+1])),
+ * chunk_id_offsets[n_chunks+1].  Pointers are owned by the handle. */
+GTK_API int gtk_result_view(const gtk_tokenizer* h, const int32_t** ids, const int64_t** text_id_offsets,
+                            const int64_t** chunk_id_offsets);
+
+/* Copy of the last result into caller buffers (any of them may be NULL). */
+GTK_API int gtk_result_copy(const gtk_tokenizer* h, int32_t* ids, int64_t ids_capacity,
+                            int64_t* text_id_offsets, int64_t* chunk_id_offsets, int64_t chunk_capacity);
+
+/* Device-resident variant of gtk_encode for callers that keep text and ids in
+ * HBM (replaces the kernel launch section, gputok_binding.cu:790-805, together
+ * with the host chunk/flatten loops :718-752 that now run on the device).
+ * d_bytes (16-byte aligned for full speed), d_text_offsets[n_texts+1] (int64),
+ * d_out_ids[out_capacity] and d_out_chunk_offsets[chunk_capacity] (>= number
+ * of chunks + 1, may be NULL) are device pointers on the handle's device.
+ * *n_ids / *n_chunks are host outputs.  Synchronous on return. */
+GTK_API int gtk_encode_device(gtk_tokenizer* h, int mode, const uint8_t* d_bytes, int64_t n_bytes,
+                              const int64_t* d_text_offsets, int64_t n_texts, int32_t* d_out_ids,
+                              int64_t out_capacity, int64_t* d_out_chunk_offsets, int64_t chunk_capacity,
+                              int64_t* n_ids, int64_t* n_chunks, float* kernel_ms);
+
+/* Device time of the stages of the last GPU encode, in milliseconds:
+ * [0] chunker, [1] merge kernel, [2] output scans, [3] pack, [4] whole pipeline.
+ * Also the number of kernels launched by that call (for launch accounting). */
+GTK_API int gtk_last_stage_ms(const gtk_tokenizer* h, float stage_ms[5], int32_t* kernel_launches);
+
+/* ids -> bytes (inverse of the byte encoder + merges); the token-string writer
+ * of gputok_blockbpe.cu:841-865 builds on this.  *n_out receives the byte count. */
+GTK_API int gtk_decode(const gtk_tokenizer* h, const int32_t* ids, int64_t n_ids, uint8_t* out,
+                       int64_t out_capacity, int64_t* n_out);
+
+/* The symbol string the reference prints for a token (id_to_token,
+ * gputok_blockbpe.cu:857).  Returns the length, -1 for an unknown id. */
+GTK_API int32_t gtk_token_symbols(const gtk_tokenizer* h, int32_t id, char* buf, int32_t capacity);
+
+/* Page-locked host memory for inputs (cudaHostAlloc / cudaFreeHost). */
+GTK_API void* gtk_pinned_alloc(size_t bytes);
+GTK_API void  gtk_pinned_free(void* p);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GPUTOK_B200_H */
