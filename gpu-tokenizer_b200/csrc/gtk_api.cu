@@ -94,7 +94,8 @@ struct gtk_tokenizer {
   int device = -1;
   int sm_count = 0;
   int opt_grid = 0, base_grid = 0;
-  cudaStream_t stream = nullptr;
+  cudaStream_t stream = nullptr;      // stream in use
+  cudaStream_t own_stream = nullptr;  // created by gtk_create
   cudaEvent_t ev[6] = {};
   std::mutex mu;
   mutable std::string last_error;
@@ -344,7 +345,8 @@ GTK_API int gtk_create(const char* merges_path, int chunk_tokens, int max_iters,
       }
       GTK_CUDA(cudaSetDevice(device));
       GTK_CUDA(cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, device));
-      GTK_CUDA(cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking));
+      GTK_CUDA(cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking));
+      h->stream = h->own_stream;
       for (auto& ev : h->ev) GTK_CUDA(cudaEventCreate(&ev));
       upload_table(h);
       h->opt_grid = h->sm_count * std::max(1, gtk::opt_kernel_max_blocks_per_sm());
@@ -378,7 +380,7 @@ GTK_API void gtk_destroy(gtk_tokenizer* h)
     for (PinBuf* b : {&h->h_ids, &h->h_text_id_off, &h->h_chunk_id_off, &h->h_totals}) b->release();
     for (auto& ev : h->ev)
       if (ev) cudaEventDestroy(ev);
-    if (h->stream) cudaStreamDestroy(h->stream);
+    if (h->own_stream) cudaStreamDestroy(h->own_stream);
   }
   delete h;
 }
@@ -629,6 +631,17 @@ GTK_API int32_t gtk_token_symbols(const gtk_tokenizer* h, int32_t id, char* buf,
   const std::string& s = h->table->id_to_symbols[size_t(id)];
   if (buf && capacity >= int32_t(s.size())) std::memcpy(buf, s.data(), s.size());
   return int32_t(s.size());
+}
+
+GTK_API int gtk_set_stream(gtk_tokenizer* h, void* cuda_stream)
+{
+  if (!h) return GTK_ERR_INVALID_ARG;
+  std::lock_guard<std::mutex> lock(h->mu);
+  if (h->device < 0) return h->fail(GTK_ERR_NO_DEVICE, "host-only handle: no GPU entry points");
+  cudaSetDevice(h->device);
+  cudaStreamSynchronize(h->stream);
+  h->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : h->own_stream;
+  return GTK_OK;
 }
 
 GTK_API void* gtk_pinned_alloc(size_t bytes)

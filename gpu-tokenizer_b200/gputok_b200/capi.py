@@ -63,6 +63,7 @@ def load_library() -> C.CDLL:
     lib.gtk_decode.argtypes = [vp, vp, i64, vp, i64, C.POINTER(i64)]
     lib.gtk_token_symbols.argtypes = [vp, i32, C.c_char_p, i32]
     lib.gtk_token_symbols.restype = i32
+    lib.gtk_set_stream.argtypes = [vp, vp]
     lib.gtk_pinned_alloc.argtypes = [C.c_size_t]
     lib.gtk_pinned_alloc.restype = vp
     lib.gtk_pinned_free.argtypes = [vp]
@@ -143,6 +144,10 @@ class Tokenizer:
         self._check(self._lib.gtk_last_stage_ms(self._h, C.byref(ms), C.byref(n)))
         return {"chunker": ms[0], "merge": ms[1], "scan": ms[2], "pack": ms[3], "pipeline": ms[4],
                 "kernel_launches": n.value}
+
+    def set_stream(self, cuda_stream: int | None) -> None:
+        """Run later GPU work on the caller's stream (e.g. ``torch.cuda.current_stream().cuda_stream``)."""
+        self._check(self._lib.gtk_set_stream(self._h, cuda_stream or None))
 
     # ------------------------------------------------------------------ host buffers
     def _result(self, copy: bool = True):

@@ -165,6 +165,12 @@ GTK_API int gtk_decode(const gtk_tokenizer* h, const int32_t* ids, int64_t n_ids
  * gputok_blockbpe.cu:857).  Returns the length, -1 for an unknown id. */
 GTK_API int32_t gtk_token_symbols(const gtk_tokenizer* h, int32_t id, char* buf, int32_t capacity);
 
+/* Run all later GPU work of this handle on the caller's CUDA stream (a cudaStream_t passed as
+ * void*; NULL restores the handle's own stream).  The reference always uses the default stream
+ * (gputok_binding.cu:794-799); this lets a caller order the tokenizer against its own kernels and
+ * time it with its own events.  The entry points stay synchronous on return. */
+GTK_API int gtk_set_stream(gtk_tokenizer* h, void* cuda_stream);
+
 /* Page-locked host memory for inputs (cudaHostAlloc / cudaFreeHost). */
 GTK_API void* gtk_pinned_alloc(size_t bytes);
 GTK_API void  gtk_pinned_free(void* p);

@@ -1,0 +1,238 @@
+"""Parity of the CUDA path with the oracle, through the C ABI, on a B200.
+
+Every comparison is bit-exact (integer ids and offsets).  Small inputs are checked against the
+literal Algorithm 1 oracle, full-size configurations against the segmented oracle on every chunk,
+the literal oracle on a seeded sample of chunks, and the decode round trip.
+"""
+from __future__ import annotations
+
+import os
+
+import numpy as np
+import pytest
+
+from conftest import first_mismatch, fixed_chunk_offsets
+from oracle.loader import MODE_GREEDY, MODE_SEGMENTED
+
+pytestmark = pytest.mark.gpu
+
+NCPU = os.cpu_count() or 1
+
+
+@pytest.fixture(scope="module")
+def lib(native_built):
+    import gputok_b200
+
+    # fail loudly if the CUDA library is absent: nothing else can serve these tests
+    assert os.path.exists(gputok_b200.library_path())
+    return gputok_b200
+
+
+def make_tok(lib, merges_path, chunk):
+    return lib.Tokenizer(merges_path, chunk, 50, device=0)
+
+
+def check_chunks(ids, coff, want, woff, what):
+    assert len(coff) == len(woff), f"{what}: {len(coff) - 1} chunks vs {len(woff) - 1}"
+    if not np.array_equal(coff, woff):
+        c = int(np.flatnonzero(coff != woff)[0]) - 1
+        a, b = ids[coff[c]:coff[c + 1]], want[woff[c]:woff[c + 1]]
+        raise AssertionError(f"{what}: chunk {c} differs: {first_mismatch(a, b)}")
+    assert np.array_equal(ids, want), f"{what}: {first_mismatch(ids, want)}"
+
+
+@pytest.mark.parametrize("mode", ["opt", "base"])
+def test_golden_novel_2048(lib, merges_path, novel, golden_2048, mode):
+    """The reference's committed output for its sample input (348 chunks of 2048 bytes)."""
+    gold_ids, gold_off = golden_2048
+    t = make_tok(lib, merges_path, 2048)
+    m = lib.GTK_MODE_OPT if mode == "opt" else lib.GTK_MODE_BASE
+    ids, toff, coff, ms = t.encode(novel, mode=m)
+    check_chunks(ids, coff, gold_ids, gold_off, f"golden/{mode}")
+    assert toff.tolist() == [0, len(gold_ids)] and ms > 0
+    assert t.decode(ids) == novel
+    ids2, _, coff2, _ = t.encode(novel, mode=m)           # same handle, second call: identical
+    assert np.array_equal(ids, ids2) and np.array_equal(coff, coff2)
+
+
+@pytest.mark.parametrize("mode", ["opt", "base"])
+def test_reference_function_cases(lib, merges_path, ref_cases, mode):
+    """Adversarial strings (runs, tiny alphabets, random bytes, UTF-8, empty): one text each."""
+    t = make_tok(lib, merges_path, 4096)
+    m = lib.GTK_MODE_OPT if mode == "opt" else lib.GTK_MODE_BASE
+    blob, case_off = ref_cases["bytes"], ref_cases["case_offsets"]
+    ids, toff, coff, _ = t.encode(blob, case_off, mode=m)
+    assert np.array_equal(toff, ref_cases["greedy_offsets"]), "per-text offsets"
+    assert np.array_equal(ids, ref_cases["greedy_ids"]), first_mismatch(ids, ref_cases["greedy_ids"])
+    nonempty = np.flatnonzero(np.diff(case_off) > 0)
+    assert len(coff) - 1 == len(nonempty)                 # an empty text owns no chunk
+
+
+def test_empty_inputs(lib, merges_path):
+    t = make_tok(lib, merges_path, 2048)
+    ids, toff, coff, ms = t.encode(b"", np.zeros(1, np.int64))
+    assert len(ids) == 0 and toff.tolist() == [0] and ms == 0.0
+    ids, toff, coff, ms = t.encode(b"", np.zeros(4, np.int64))
+    assert len(ids) == 0 and toff.tolist() == [0, 0, 0, 0] and len(coff) == 1
+    ids, toff, coff, _ = t.encode_texts([b"", b"a", b"", b" the", b""])
+    assert toff.tolist() == [0, 0, 1, 1, 2, 2] and ids[0] == ord("a")
+
+
+@pytest.mark.parametrize("chunk", [1, 2, 3, 7, 33, 64, 65, 511, 512, 1024, 4095, 4096, 4097, 8192, 32768, 65536])
+def test_chunk_sizes_on_novel(lib, merges_path, oracle, novel, chunk):
+    t = make_tok(lib, merges_path, chunk)
+    data = novel[:40_000] if chunk < 64 else novel[:300_000]
+    want, woff = oracle.encode_fixed(data, chunk, mode=MODE_SEGMENTED, threads=NCPU)
+    for m in (lib.GTK_MODE_OPT, lib.GTK_MODE_BASE):
+        ids, _, coff, _ = t.encode(data, mode=m)
+        check_chunks(ids, coff, want, woff, f"chunk {chunk} mode {m}")
+
+
+def test_config1_correctness_case(lib, merges_path, oracle):
+    """1 MiB of seeded text (seed 0), 1024-byte chunks, literal Algorithm 1 on every chunk."""
+    data = lib.TextGen(0).text(1 << 20)
+    want, woff = oracle.encode_fixed(data, 1024, mode=MODE_GREEDY, threads=NCPU)
+    t = make_tok(lib, merges_path, 1024)
+    for m in (lib.GTK_MODE_OPT, lib.GTK_MODE_BASE):
+        ids, _, coff, _ = t.encode(data, mode=m)
+        assert len(coff) - 1 == 1024
+        check_chunks(ids, coff, want, woff, f"config1 mode {m}")
+
+
+def test_config2_full_size(lib, merges_path, oracle):
+    """256 MiB (seed 1), 4096-byte chunks: segmented oracle on every chunk, literal oracle on a
+    seeded 1 % sample, decode round trip, int64 offsets."""
+    n = 256 << 20
+    data = lib.TextGen(1).text(n)
+    t = make_tok(lib, merges_path, 4096)
+    ids, toff, coff, ms = t.encode(data)
+    assert len(coff) - 1 == 65536 and coff.dtype == np.int64 and ids.dtype == np.int32
+    off = fixed_chunk_offsets(n, 4096)
+    want, woff = oracle.encode_chunks(data, off, mode=MODE_SEGMENTED, threads=NCPU)
+    check_chunks(ids, coff, want, woff, "config2/all")
+    sample = np.sort(np.random.default_rng(1).choice(65536, size=655, replace=False))
+    for c in sample[:: max(1, len(sample) // 200)]:   # literal rule is ~40 ms per 4 KiB chunk on one core
+        lit, _ = oracle.encode_chunks(data, off[c:c + 2], mode=MODE_GREEDY)
+        got = ids[coff[c]:coff[c + 1]]
+        assert np.array_equal(got, lit), f"config2 chunk {c}: {first_mismatch(got, lit)}"
+    assert t.decode(ids[:coff[256]]) == data[:256 * 4096].tobytes()
+    lens = np.array([len(oracle.token_bytes(i)) for i in range(oracle.vocab_size)], dtype=np.int64)
+    per_chunk = np.add.reduceat(lens[ids], coff[:-1])
+    assert np.array_equal(per_chunk, np.diff(off))        # every chunk decodes to exactly its own bytes
+
+
+def test_config4_long_chunks_unicode_runs(lib, merges_path, oracle):
+    """Stress mix (seed 3), 32 KiB chunks: literal oracle on a sample, segmented oracle on all."""
+    n = 16 << 20
+    data = lib.TextGen(3).text(n, mix=lib.MIX_STRESS)
+    off = fixed_chunk_offsets(n, 32768)
+    want, woff = oracle.encode_chunks(data, off, mode=MODE_SEGMENTED, threads=NCPU)
+    t = make_tok(lib, merges_path, 32768)
+    ids, _, coff, _ = t.encode(data)
+    check_chunks(ids, coff, want, woff, "config4/opt")
+    ids_b, _, coff_b, _ = t.encode(data[:2 << 20], mode=lib.GTK_MODE_BASE)
+    check_chunks(ids_b, coff_b, want[:woff[64]], woff[:65], "config4/base")
+    for c in (0, 7, 100, 511):
+        lit, _ = oracle.encode_chunks(data, off[c:c + 2], mode=MODE_SEGMENTED)
+        assert np.array_equal(ids[coff[c]:coff[c + 1]], lit)
+    assert t.decode(ids[:coff[8]]) == data[:8 * 32768].tobytes()
+
+
+def test_config5_lognormal_chunks(lib, merges_path, oracle):
+    """Variable-length texts (log-normal, 64 B .. 64 KiB), one chunk each."""
+    n = 64 << 20
+    data = lib.TextGen(4).text(n, mix=lib.MIX_STRESS)
+    toff_in = lib.TextGen.lognormal_offsets(4, n)
+    want, woff = oracle.encode_chunks(data, toff_in, mode=MODE_SEGMENTED, threads=NCPU)
+    t = make_tok(lib, merges_path, 65536)
+    ids, toff, coff, _ = t.encode(data, toff_in)
+    check_chunks(ids, coff, want, woff, "config5")
+    assert np.array_equal(toff, coff)                     # one chunk per text
+
+
+def test_adversarial_long_segments(lib, merges_path, oracle):
+    """Segments far longer than a tile: the whole-CTA path in the HBM workspace."""
+    rng = np.random.default_rng(7)
+    texts = [b"a" * 65536, b"ab" * 20000, b"e" * 5000 + b" " + b"l" * 9000, ("😀" * 3000).encode(),
+             bytes(rng.choice(np.frombuffer(b"ae", np.uint8), size=30000)), b"x" * 4608, b"y" * 4609, b"z" * 4607,
+             b"q" * 4096 + b" " + b"w" * 513]
+    blob = b"".join(texts)
+    toff_in = np.concatenate([[0], np.cumsum([len(x) for x in texts])]).astype(np.int64)
+    t = make_tok(lib, merges_path, 65536)
+    want, woff = oracle.encode_chunks(blob, toff_in, mode=MODE_SEGMENTED, threads=NCPU)
+    for m in (lib.GTK_MODE_OPT, lib.GTK_MODE_BASE):
+        ids, toff, coff, _ = t.encode(blob, toff_in, mode=m)
+        check_chunks(ids, coff, want, woff, f"long segments mode {m}")
+    lit, _ = oracle.encode_chunks(blob, toff_in[:2], mode=MODE_GREEDY)
+    assert np.array_equal(want[:woff[1]], lit)            # 64 Ki of 'a': the literal rule agrees
+
+
+def test_random_small_batches(lib, merges_path, oracle):
+    """Many short texts of assorted lengths in one batch (latency-mode strings, ragged)."""
+    rng = np.random.default_rng(11)
+    src = lib.TextGen(2).text(4 << 20, mix=lib.MIX_STRESS)
+    lens = rng.integers(0, 1500, size=3000)
+    lens[::97] = 0
+    toff_in = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    data = src[:toff_in[-1]]
+    t = make_tok(lib, merges_path, 512)
+    ids, toff, coff, _ = t.encode(data, toff_in)
+    chunk_off = [0]
+    for s, e in zip(toff_in[:-1], toff_in[1:]):
+        chunk_off.extend(list(range(int(s) + 512, int(e), 512)) + ([int(e)] if e > s else []))
+    want, woff = oracle.encode_chunks(data, np.array(chunk_off, np.int64), mode=MODE_SEGMENTED, threads=NCPU)
+    check_chunks(ids, coff, want, woff, "ragged batch")
+    starts = np.searchsorted(np.array(chunk_off), toff_in, side="left")
+    assert np.array_equal(toff, woff[starts])
+
+
+def test_latency_strings_one_call_each(lib, merges_path, oracle):
+    """Config 3 in miniature: independent 512-byte strings, batch size 1, every string checked."""
+    gen = lib.TextGen(2)
+    t = make_tok(lib, merges_path, 2048)
+    for i in range(200):
+        s = gen.blocks(1, 512, first_block=i)
+        ids, _, _, _ = t.encode(s)
+        want, _ = oracle.encode_chunks(s, np.array([0, 512]), mode=MODE_GREEDY)
+        assert np.array_equal(ids, want), f"string {i}: {first_mismatch(ids, want)}"
+
+
+def test_device_resident_entry_point(lib, merges_path, oracle):
+    import torch
+
+    data = lib.TextGen(1).text(8 << 20)
+    n = len(data)
+    d_bytes = torch.from_numpy(data.copy()).cuda()
+    d_toff = torch.tensor([0, n], dtype=torch.int64, device="cuda")
+    d_ids = torch.empty(n, dtype=torch.int32, device="cuda")
+    d_coff = torch.empty(n // 4096 + 8, dtype=torch.int64, device="cuda")
+    t = make_tok(lib, merges_path, 4096)
+    n_ids, n_chunks, ms = t.encode_device(d_bytes.data_ptr(), n, d_toff.data_ptr(), 1, d_ids.data_ptr(), n,
+                                          d_coff.data_ptr(), d_coff.numel())
+    want, woff = oracle.encode_fixed(data, 4096, mode=MODE_SEGMENTED, threads=NCPU)
+    assert n_chunks == 2048 and n_ids == len(want) and ms > 0
+    assert np.array_equal(d_ids[:n_ids].cpu().numpy(), want)
+    assert np.array_equal(d_coff[:n_chunks + 1].cpu().numpy(), woff)
+    st = t.stage_ms()
+    assert st["kernel_launches"] >= 5 and st["merge"] > 0
+    with pytest.raises(lib.GtkError) as e:                # too small an id buffer is reported, not overrun
+        t.encode_device(d_bytes.data_ptr(), n, d_toff.data_ptr(), 1, d_ids.data_ptr(), 1000)
+    assert e.value.code == 4
+
+
+def test_pybind_methods_on_gpu(lib, merges_path, oracle):
+    import gputok_gpu
+
+    tok = gputok_gpu.GpuTokenizer(merges_path, 2048, 50)
+    texts = ["Hello world!", "", "The weather today is", "naïve café 日本 " * 300]
+    for method in (tok.tokenize_batch, tok.tokenize_batch_blockbpe_base):
+        batch, ms = method(texts)
+        assert len(batch) == 4 and batch[1] == [] and ms > 0
+        for text, ids in zip(texts, batch):
+            want, _ = oracle.encode_fixed(text.encode(), 2048, mode=MODE_GREEDY)
+            assert ids == want.tolist()
+    assert tok.tokenize_batch([]) == ([], 0.0)
+    assert tok.tokenize_batch(["", ""]) == ([], 0.0)     # all-empty batch, as the reference
+    assert tok.tokenize_batch_cpu(texts) == tok.tokenize_batch(texts)[0]
+    ids, toff, coff, ms = tok.encode_packed(texts)
+    assert ids.dtype == np.int32 and toff.dtype == np.int64 and toff[-1] == len(ids)
