@@ -290,6 +290,20 @@ int validate_offsets(gtk_tokenizer* h, const int64_t* text_offsets, int64_t n_te
 
 }  // namespace
 
+namespace gtk {
+bool handle_view(gtk_tokenizer* h, HandleView* out)
+{
+  if (!h || !out) return false;
+  out->device = h->device;
+  out->stream = h->stream;
+  out->table = h->dtab;
+  out->pinned_words = h->device >= 0 ? h->h_totals.as<int32_t>() + 8 : nullptr;
+  out->mu = &h->mu;
+  out->last_error = &h->last_error;
+  return true;
+}
+}  // namespace gtk
+
 // ------------------------------------------------------------------------------------------------
 // C ABI
 // ------------------------------------------------------------------------------------------------

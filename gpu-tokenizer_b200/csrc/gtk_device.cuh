@@ -3,6 +3,10 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <cstdint>
+#include <mutex>
+#include <string>
+
+struct gtk_tokenizer;
 
 namespace gtk {
 
@@ -76,6 +80,17 @@ int launch_merge_opt(const EncodeBuffers& b, const DeviceTable& t, int grid, cud
 int launch_merge_base(const EncodeBuffers& b, const DeviceTable& t, int grid, cudaStream_t stream);
 int launch_output_scans(const EncodeBuffers& b, int mode_base, cudaStream_t stream);
 int launch_pack(const EncodeBuffers& b, int mode_base, int grid, cudaStream_t stream);
+// What the allocation-free entry point needs from a handle (defined in gtk_api.cu).
+struct HandleView {
+  int device;
+  cudaStream_t stream;
+  DeviceTable table;
+  int32_t* pinned_words;  // 8 ints of page-locked host memory owned by the handle
+  std::mutex* mu;
+  std::string* last_error;
+};
+bool handle_view(gtk_tokenizer* h, HandleView* out);
+
 int opt_kernel_max_blocks_per_sm();
 int base_kernel_max_blocks_per_sm();
 

@@ -912,3 +912,128 @@ int base_kernel_max_blocks_per_sm()
 }
 
 }  // namespace gtk
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free entry point (declared in include/gputok_b200.h): the one-CTA-per-chunk merge
+// kernel with its ticket counter, status word and long-chunk workspace in a fixed device array
+// instead of buffers from cudaMalloc.
+// ------------------------------------------------------------------------------------------------
+#include "../../include/gputok_b200.h"
+
+namespace {
+
+constexpr int kNoAllocCtas        = 128;                          // persistent CTAs of the kernel
+constexpr int kNoAllocMaxTokens   = GTK_NOALLOC_MAX_CHUNK_BYTES;  // longest chunk (one token per byte at most)
+constexpr size_t kNoAllocHeader   = 256;                          // [0] chunk ticket, [1] status word
+constexpr size_t kNoAllocPerCta   = size_t(2) * kNoAllocMaxTokens * sizeof(uint16_t);  // tokens + ranks
+constexpr size_t kNoAllocBytes    = kNoAllocHeader + size_t(kNoAllocCtas) * kNoAllocPerCta;  // 8 MiB + 256 B
+constexpr int kMaxDevices         = 64;
+
+// Lives in the library image on every GPU that loads it.  In host code this name is only a
+// stand-in for the symbol; the device address comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+__global__ void __launch_bounds__(gtk::kBaseThreads)
+k_merge_chunks_noalloc(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ chunk_off, int64_t n_chunks,
+                       int max_chunk, int32_t* __restrict__ out_ids, int32_t* __restrict__ out_counts,
+                       gtk::DeviceTable T, unsigned char* scratch)
+{
+  using namespace gtk;
+  __shared__ uint16_t s_tok[kBaseSmemTokens];
+  __shared__ uint16_t s_rk[kBaseSmemTokens];
+  __shared__ GroupScratch gs;
+  __shared__ int ticket;
+  const int tid   = threadIdx.x;
+  int* counter    = reinterpret_cast<int*>(scratch);
+  int* status     = counter + 1;
+  uint16_t* w_tok = reinterpret_cast<uint16_t*>(scratch + kNoAllocHeader + size_t(blockIdx.x) * kNoAllocPerCta);
+  uint16_t* w_rk  = w_tok + kNoAllocMaxTokens;
+  for (;;) {
+    __syncthreads();
+    if (tid == 0) ticket = atomicAdd(counter, 1);
+    __syncthreads();
+    const int64_t c = ticket;
+    if (c >= n_chunks) break;
+    const int64_t cs  = chunk_off[c];
+    const int64_t L64 = chunk_off[c + 1] - cs;
+    if (L64 <= 0 || L64 > max_chunk) {
+      if (tid == 0) {
+        out_counts[c] = 0;
+        if (L64 != 0) atomicMax(status, int(kStatusScratchTooSmall));
+      }
+      continue;
+    }
+    const int L   = int(L64);
+    uint16_t* tok = (L <= kBaseSmemTokens) ? s_tok : w_tok;
+    uint16_t* rk  = (L <= kBaseSmemTokens) ? s_rk : w_rk;
+    for (int i = tid; i < L; i += kBaseThreads) {
+      const uint32_t cur = bytes[cs + i];
+      tok[i] = __ldg(T.byte_to_id + cur);
+      rk[i]  = (i + 1 < L) ? __ldg(T.byte_pair_rank + ((cur << 8) | bytes[cs + i + 1])) : uint16_t(NONE);
+    }
+    __syncthreads();
+    const int len = group_merge<kBaseThreads / 32>(tok, rk, L, T, &gs, status);
+    for (int j = tid; j < len; j += kBaseThreads) out_ids[cs + j] = int32_t(tok[j]);
+    if (tid == 0) out_counts[c] = len;
+  }
+}
+
+// Device address of the fixed array, looked up once per device with that device current.
+std::mutex g_noalloc_mu;
+unsigned char* g_noalloc_ptr[kMaxDevices] = {};
+
+cudaError_t noalloc_scratch_for(int device, unsigned char** out)
+{
+  std::lock_guard<std::mutex> lock(g_noalloc_mu);
+  if (!g_noalloc_ptr[device]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return e;
+    g_noalloc_ptr[device] = static_cast<unsigned char*>(p);
+  }
+  *out = g_noalloc_ptr[device];
+  return cudaSuccess;
+}
+
+}  // namespace
+
+extern "C" GTK_API int gtk_encode_chunks_noalloc(gtk_tokenizer* h, const uint8_t* d_bytes, int64_t n_bytes,
+                                                 const int64_t* d_chunk_offsets, int64_t n_chunks,
+                                                 int32_t max_chunk_bytes, int32_t* d_out_ids, int32_t* d_out_counts)
+{
+  gtk::HandleView v;
+  if (!gtk::handle_view(h, &v)) return GTK_ERR_INVALID_ARG;
+  std::lock_guard<std::mutex> lock(*v.mu);
+  auto fail = [&](int code, const std::string& msg) {
+    *v.last_error = msg;
+    return code;
+  };
+  if (v.device < 0) return fail(GTK_ERR_NO_DEVICE, "host-only handle: no GPU entry points");
+  if (v.device >= kMaxDevices) return fail(GTK_ERR_INVALID_ARG, "device ordinal beyond the supported range");
+  if (n_chunks < 0 || n_bytes < 0 || max_chunk_bytes <= 0) return fail(GTK_ERR_INVALID_ARG, "negative or zero size");
+  if (max_chunk_bytes > GTK_NOALLOC_MAX_CHUNK_BYTES)
+    return fail(GTK_ERR_CAPACITY, "max_chunk_bytes " + std::to_string(max_chunk_bytes) +
+                                      " exceeds the allocation-free limit of " +
+                                      std::to_string(GTK_NOALLOC_MAX_CHUNK_BYTES) + " bytes per chunk");
+  if (n_chunks == 0) return GTK_OK;
+  if (!d_bytes || !d_chunk_offsets || !d_out_ids || !d_out_counts) return fail(GTK_ERR_INVALID_ARG, "null device pointer");
+  cudaError_t e = cudaSetDevice(v.device);
+  unsigned char* scratch = nullptr;
+  if (e == cudaSuccess) e = noalloc_scratch_for(v.device, &scratch);
+  if (e != cudaSuccess) return fail(GTK_ERR_CUDA, std::string("fixed workspace lookup: ") + cudaGetErrorString(e));
+  // the previous call's ticket and status words must start at zero
+  e = cudaMemsetAsync(scratch, 0, kNoAllocHeader, v.stream);
+  if (e != cudaSuccess) return fail(GTK_ERR_CUDA, std::string("cudaMemsetAsync: ") + cudaGetErrorString(e));
+  const int grid = int(n_chunks < kNoAllocCtas ? n_chunks : kNoAllocCtas);
+  k_merge_chunks_noalloc<<<grid, gtk::kBaseThreads, 0, v.stream>>>(d_bytes, d_chunk_offsets, n_chunks, max_chunk_bytes,
+                                                                   d_out_ids, d_out_counts, v.table, scratch);
+  e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaMemcpyAsync(v.pinned_words, scratch, 8, cudaMemcpyDeviceToHost, v.stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(v.stream);
+  if (e != cudaSuccess) return fail(GTK_ERR_CUDA, std::string("allocation-free merge kernel: ") + cudaGetErrorString(e));
+  const int status = v.pinned_words[1];
+  if (status == gtk::kStatusScratchTooSmall)
+    return fail(GTK_ERR_CAPACITY, "a chunk is longer than max_chunk_bytes (" + std::to_string(max_chunk_bytes) + ")");
+  if (status != gtk::kStatusOk) return fail(GTK_ERR_KERNEL, "merge pass made no progress");
+  return GTK_OK;
+}

@@ -10,6 +10,7 @@ GTK_MODE_OPT = 0
 GTK_MODE_BASE = 1
 GTK_RULE_GREEDY = 0
 GTK_RULE_LOCALMIN = 1
+NOALLOC_MAX_CHUNK_BYTES = 16384
 
 _PKG_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 _LIB = None
@@ -64,6 +65,7 @@ def load_library() -> C.CDLL:
     lib.gtk_token_symbols.argtypes = [vp, i32, C.c_char_p, i32]
     lib.gtk_token_symbols.restype = i32
     lib.gtk_set_stream.argtypes = [vp, vp]
+    lib.gtk_encode_chunks_noalloc.argtypes = [vp, vp, i64, vp, i64, i32, vp, vp]
     lib.gtk_pinned_alloc.argtypes = [C.c_size_t]
     lib.gtk_pinned_alloc.restype = vp
     lib.gtk_pinned_free.argtypes = [vp]
@@ -207,6 +209,15 @@ class Tokenizer:
                                                 d_out_chunk_offsets or None, int(chunk_capacity),
                                                 C.byref(n_ids), C.byref(n_chunks), C.byref(ms)))
         return n_ids.value, n_chunks.value, ms.value
+
+    def encode_chunks_noalloc(self, d_bytes: int, n_bytes: int, d_chunk_offsets: int, n_chunks: int,
+                              max_chunk_bytes: int, d_out_ids: int, d_out_counts: int) -> None:
+        """Allocation-free variant for callers that may not allocate while tokenising (raw device
+        pointers).  Ids of chunk c land at ``d_out_ids[chunk_offsets[c]:]``, their number in
+        ``d_out_counts[c]``.  At most ``NOALLOC_MAX_CHUNK_BYTES`` bytes per chunk."""
+        self._check(self._lib.gtk_encode_chunks_noalloc(self._h, d_bytes, int(n_bytes), d_chunk_offsets,
+                                                        int(n_chunks), int(max_chunk_bytes), d_out_ids,
+                                                        d_out_counts))
 
     # ------------------------------------------------------------------ decode
     def decode(self, ids) -> bytes:

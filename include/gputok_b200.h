@@ -171,6 +171,41 @@ GTK_API int32_t gtk_token_symbols(const gtk_tokenizer* h, int32_t id, char* buf,
  * time it with its own events.  The entry points stay synchronous on return. */
 GTK_API int gtk_set_stream(gtk_tokenizer* h, void* cuda_stream);
 
+/* Longest chunk, in bytes, that gtk_encode_chunks_noalloc accepts. */
+#define GTK_NOALLOC_MAX_CHUNK_BYTES 16384
+
+/* No counterpart in the reference (which allocates five device buffers inside every call).
+ *
+ * For callers that must not allocate while they tokenise: code running inside a serving loop
+ * with a frozen memory budget, under a framework whose caching allocator owns all of HBM, or
+ * anywhere a cudaMalloc -- which synchronises the whole device -- would stall other streams.
+ * Once the handle exists this call performs no cudaMalloc/cudaFree and calls no allocating
+ * library routine: one kernel (the one-CTA-per-chunk greedy merge kernel) runs with its work
+ * queue, status word and long-chunk workspace in a fixed array that is part of the library
+ * image (8 MiB + 256 B of device memory on every GPU that loads the library, held until the
+ * process exits).
+ *
+ *   d_bytes[n_bytes]              text on the handle's device
+ *   d_chunk_offsets[n_chunks+1]   int64, on the device: chunk c is bytes[off[c] .. off[c+1]);
+ *                                 non-decreasing, off[n_chunks] <= n_bytes
+ *   max_chunk_bytes               the caller's bound on off[c+1]-off[c]; values above
+ *                                 GTK_NOALLOC_MAX_CHUNK_BYTES are rejected with GTK_ERR_CAPACITY
+ *                                 before anything is launched; a chunk that breaks the bound is
+ *                                 reported as GTK_ERR_CAPACITY after the kernel (its count is 0)
+ *   d_out_ids[n_bytes]            int32; the ids of chunk c start at d_out_ids[off[c]] (the layout
+ *                                 of the reference kernel's d_tokens_out, gputok_blockbpe.cu:530-537)
+ *   d_out_counts[n_chunks]        int32 ids produced per chunk
+ *
+ * The first call on a device looks up the device address of the fixed array
+ * (cudaGetSymbolAddress); make that first call before any stream capture.  All calls on a
+ * device share the array, which keeps the previous call's contents: the queue and status words
+ * are cleared at the start of every call, the workspace is fully rewritten per chunk.  Two calls
+ * that overlap on the same GPU (different handles or streams) race on it -- serialise them.
+ * Synchronous on return. */
+GTK_API int gtk_encode_chunks_noalloc(gtk_tokenizer* h, const uint8_t* d_bytes, int64_t n_bytes,
+                                      const int64_t* d_chunk_offsets, int64_t n_chunks, int32_t max_chunk_bytes,
+                                      int32_t* d_out_ids, int32_t* d_out_counts);
+
 /* Page-locked host memory for inputs (cudaHostAlloc / cudaFreeHost). */
 GTK_API void* gtk_pinned_alloc(size_t bytes);
 GTK_API void  gtk_pinned_free(void* p);
