@@ -19,7 +19,7 @@ constexpr int kWindow = kTile + kHalo;
 constexpr int kOptThreads = 256;
 constexpr int kBaseThreads = 512;
 constexpr int kBaseSmemTokens = 8192;  // chunks up to this length stay in shared memory in the base kernel
-constexpr int kThreadSegMax = 64;      // longest segment a single thread merges on its own
+constexpr int kThreadSegMax = 32;      // longest segment a single thread merges on its own
 
 // Pointers into HBM, passed by value to every kernel.
 struct DeviceTable {

@@ -33,14 +33,16 @@ constexpr uint32_t DEAD = 0xFFFFu;  // token slot holds nothing
 
 __device__ __forceinline__ uint32_t probe_rank(const DeviceTable& T, uint32_t left, uint32_t right)
 {
-  const uint64_t key  = (uint64_t(left) << 32) | uint64_t(right);
   const uint32_t mask = (1u << T.log2_capacity) - 1u;
-  uint32_t h          = uint32_t((key * 0x9E3779B97F4A7C15ull) >> (64 - T.log2_capacity));
-  for (uint32_t d = 0; d <= T.max_probe; ++d) {
-    const uint4 s = __ldg(T.slots + h);
+  uint32_t h          = (((left << 16) ^ right) * 0x9E3779B1u) >> (32 - T.log2_capacity);
+  uint4 s             = __ldg(T.slots + h);
+  if (s.x == right && s.y == left) return s.z;  // load factor 0.38: the first slot answers most probes
+  if ((s.x & s.y) == 0xFFFFFFFFu) return NONE;
+  for (uint32_t d = 1; d <= T.max_probe; ++d) {
+    h = (h + 1u) & mask;
+    s = __ldg(T.slots + h);
     if (s.x == right && s.y == left) return s.z;
     if ((s.x & s.y) == 0xFFFFFFFFu) return NONE;
-    h = (h + 1u) & mask;
   }
   return NONE;
 }
@@ -64,44 +66,40 @@ __device__ __forceinline__ uint32_t lanemask_lt()
 }
 
 // ------------------------------------------------------------------------------------------------
-// One thread merges one short segment (<= 64 tokens) in place.
+// One merge step of one short segment (<= 32 tokens), executed by a single thread.
 //
 // tok[0..L) / rk[0..L) live in shared memory; rk[i] is the rank of the pair
-// (token i, next live token), NONE for the last one.  Dead slots become DEAD
-// tombstones and stay where they are; the alive set is a 64-bit register
-// mask.  Every step merges the left-most pair of lowest rank -- Algorithm 1
-// restricted to the segment -- and re-probes the two pairs next to it.
+// (token i, next live token), NONE for dead slots and for the last live one.
+// Dead slots become DEAD tombstones and stay where they are; the alive set is
+// a 32-bit register mask.  A step merges the left-most pair of lowest rank --
+// Algorithm 1 restricted to the segment -- and re-probes the two pairs next
+// to it.  Returns false when no pair of the segment is mergeable any more.
 // ------------------------------------------------------------------------------------------------
-__device__ void thread_merge(uint16_t* tok, uint16_t* rk, int L, const DeviceTable& T)
+__device__ __forceinline__ bool thread_merge_step(uint16_t* tok, uint16_t* rk, int L, uint32_t& alive,
+                                                  const DeviceTable& T)
 {
-  uint64_t alive = (L >= 64) ? ~0ull : ((1ull << L) - 1ull);
-  for (int step = 0; step < L; ++step) {
-    uint32_t best = 0xFFFFFFFFu;
-    uint64_t m    = alive & ~(1ull << (63 - __clzll((long long)alive)));  // every live slot but the last
-    while (m) {
-      const int j = __ffsll((long long)m) - 1;
-      m &= m - 1;
-      const uint32_t v = (uint32_t(rk[j]) << 16) | uint32_t(j);
-      best             = min(best, v);
-    }
-    const uint32_t r = best >> 16;
-    if (r >= SEL) break;
-    const int j = int(best & 0xFFFFu);
-    const int q = j + __ffsll((long long)(alive >> (j + 1)));  // next live slot after j
-    const uint32_t c = merged_id(T, r);
-    tok[j] = uint16_t(c);
-    tok[q] = uint16_t(DEAD);
-    alive &= ~(1ull << q);
-    const uint64_t right = (q >= 63) ? 0ull : (alive >> (q + 1));
-    uint32_t rr          = NONE;
-    if (right) rr = probe_rank(T, c, tok[q + __ffsll((long long)right)]);
-    rk[j] = uint16_t(rr);
-    const uint64_t left = alive & ((1ull << j) - 1ull);
-    if (left) {
-      const int p = 63 - __clzll((long long)left);
-      rk[p]       = uint16_t(probe_rank(T, tok[p], c));
-    }
+  if ((alive & (alive - 1u)) == 0u) return false;  // one token left
+  uint32_t best = 0xFFFFFFFFu;
+  for (int i = 0; i < L - 1; ++i) best = min(best, (uint32_t(rk[i]) << 16) | uint32_t(i));
+  const uint32_t r = best >> 16;
+  if (r >= SEL) return false;
+  const int j = int(best & 0xFFFFu);
+  const int q = j + __ffs(int(alive >> (j + 1)));  // next live slot after j (j <= 30)
+  const uint32_t c = merged_id(T, r);
+  tok[j] = uint16_t(c);
+  tok[q] = uint16_t(DEAD);
+  rk[q]  = uint16_t(NONE);
+  alive &= ~(1u << q);
+  const uint32_t right = (q >= 31) ? 0u : (alive >> (q + 1));
+  uint32_t rr          = NONE;
+  if (right) rr = probe_rank(T, c, tok[q + __ffs(int(right))]);
+  rk[j] = uint16_t(rr);
+  const uint32_t left = alive & ((1u << j) - 1u);
+  if (left) {
+    const int p = 31 - __clz(int(left));
+    rk[p]       = uint16_t(probe_rank(T, tok[p], c));
   }
+  return true;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -498,7 +496,7 @@ struct OptSmem {
   GroupScratch gs;
   int scanbuf[33];
   int ticket;
-  int nseg, nlong;
+  int nseg, nlong, seg_next;
   int first_start, last_start, over_start;
   int over_len;
   long long over_end;
@@ -532,6 +530,7 @@ __global__ void __launch_bounds__(kOptThreads) k_merge_opt(EncodeBuffers b, Devi
     if (tid == 0) {
       S.ticket      = atomicAdd(b.counters + 0, 1);
       S.nlong       = 0;
+      S.seg_next    = 0;
       S.first_start = kWindow;
       S.last_start  = -1;
       S.over_start  = -1;
@@ -614,22 +613,48 @@ __global__ void __launch_bounds__(kOptThreads) k_merge_opt(EncodeBuffers b, Devi
     }
     __syncthreads();
 
-    // ---- E. one thread per short segment ----
+    // ---- E. short segments: every lane pulls segments from a CTA-wide queue and does one merge
+    //         step per loop trip, so a lane that finishes early takes new work instead of idling ----
     {
-      const int nseg = S.nseg;
-      for (int j = tid; j < nseg; j += kOptThreads) {
-        const int s = S.seg[j];
-        const int e = next_cut(S.cut, s);
-        const int L = e - s;
-        if (e >= kWindow && wlen == kWindow) {
-          S.over_start = s;  // runs past the window: finished in the HBM workspace below
-        } else if (L <= kThreadSegMax) {
-          thread_merge(S.tok + s, S.rk + s, L, T);
-        } else {
-          const int q = atomicAdd(&S.nlong, 1);
-          if (q < kLongCap) S.longq[q] = uint16_t(s);
-          else atomicMax(status, int(kStatusLongQueueOverflow));
+      const int nseg   = S.nseg;
+      int s            = -1, L = 0;
+      uint32_t alive   = 0;
+      bool drained     = false;
+      for (;;) {
+        const bool need   = (s < 0) && !drained;
+        const uint32_t nb = __ballot_sync(0xFFFFFFFFu, need);
+        if (nb) {
+          const int leader = __ffs(int(nb)) - 1;
+          int base         = 0;
+          if (lane == leader) base = atomicAdd(&S.seg_next, __popc(nb));
+          base = __shfl_sync(0xFFFFFFFFu, base, leader);
+          if (need) {
+            const int j = base + __popc(nb & lt);
+            if (j >= nseg) {
+              drained = true;
+            } else {
+              const int ss = S.seg[j];
+              const int e  = next_cut(S.cut, ss);
+              const int LL = e - ss;
+              if (e >= kWindow && wlen == kWindow) {
+                S.over_start = ss;  // runs past the window: finished in the HBM workspace below
+              } else if (LL <= kThreadSegMax) {
+                s     = ss;
+                L     = LL;
+                alive = (LL >= 32) ? 0xFFFFFFFFu : ((1u << LL) - 1u);
+              } else {
+                const int q = atomicAdd(&S.nlong, 1);
+                if (q < kLongCap) S.longq[q] = uint16_t(ss);
+                else atomicMax(status, int(kStatusLongQueueOverflow));
+              }
+            }
+          }
         }
+        if (!__any_sync(0xFFFFFFFFu, s >= 0)) {
+          if (__all_sync(0xFFFFFFFFu, drained)) break;
+          continue;
+        }
+        if (s >= 0 && !thread_merge_step(S.tok + s, S.rk + s, L, alive, T)) s = -1;
       }
     }
     __syncthreads();

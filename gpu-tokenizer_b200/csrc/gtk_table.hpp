@@ -35,10 +35,12 @@ struct MergeRow {
 
 inline uint64_t pair_key(uint32_t left, uint32_t right) { return (uint64_t(left) << 32) | uint64_t(right); }
 
-// Multiplicative hash shared by host and device (same constant in gtk_device.cuh).
+// Hash shared by host and device (probe_rank in gtk_kernels.cu): the pair folded into 32 bits
+// (exact for 16-bit ids), one 32-bit multiply, top bits.  Three integer instructions on the GPU.
 inline uint32_t pair_hash(uint64_t key, uint32_t log2_capacity)
 {
-  return uint32_t((key * 0x9E3779B97F4A7C15ull) >> (64 - log2_capacity));
+  const uint32_t left = uint32_t(key >> 32), right = uint32_t(key);
+  return (((left << 16) ^ right) * 0x9E3779B1u) >> (32 - log2_capacity);
 }
 
 class HostTable {
