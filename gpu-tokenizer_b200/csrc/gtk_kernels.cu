@@ -489,7 +489,8 @@ struct OptSmem {
   uint32_t adj[2048];
   uint16_t tok[kWindow];
   uint16_t rk[kWindow];  // reused as the compacted output buffer after merging
-  uint16_t seg[kSegCap];
+  uint32_t seg[kSegCap];  // (start | length << 16) of owned short segments, longest first
+  int hist[34];
   uint32_t cut[kCutWords + 2];  // segment-start bits; reused as the alive bitmap
   uint16_t woff[kCutWords + 2];
   uint16_t longq[kLongCap];
@@ -588,9 +589,11 @@ __global__ void __launch_bounds__(kOptThreads) k_merge_opt(EncodeBuffers b, Devi
     }
     __syncthreads();
 
-    // ---- D. list the owned segments that have at least two bytes ----
+    // ---- D. owned segments of at least two bytes, sorted by length (longest first) so that the
+    //         lanes of a warp work on segments of similar length in step E ----
     {
       uint32_t m = 0;
+      if (tid < 33) S.hist[tid] = 0;
       if (tid < kTile / 32) {
         const int w0        = tid * 32;
         const uint32_t word = S.cut[tid], nextw = S.cut[tid + 1];
@@ -602,14 +605,46 @@ __global__ void __launch_bounds__(kOptThreads) k_merge_opt(EncodeBuffers b, Devi
         }
         m = starts & ~((word >> 1) | (nextw << 31));
       }
-      int total;
-      int off = block_exclusive_scan(__popc(m), S.scanbuf, &total);
-      while (m) {
-        const int j = __ffs(int(m)) - 1;
-        m &= m - 1;
-        S.seg[off++] = uint16_t(tid * 32 + j);
+      __syncthreads();
+      for (uint32_t mm = m; mm;) {  // pass 1: length histogram, long and oversize segments set aside
+        const int ss = tid * 32 + __ffs(int(mm)) - 1;
+        mm &= mm - 1;
+        const int e  = next_cut(S.cut, ss);
+        const int LL = e - ss;
+        if (e >= kWindow && wlen == kWindow) {
+          S.over_start = ss;  // runs past the window: finished in the HBM workspace below
+        } else if (LL <= kThreadSegMax) {
+          atomicAdd(&S.hist[LL], 1);
+        } else {
+          const int q = atomicAdd(&S.nlong, 1);
+          if (q < kLongCap) S.longq[q] = uint16_t(ss);
+          else atomicMax(status, int(kStatusLongQueueOverflow));
+        }
       }
-      if (tid == 0) S.nseg = total;
+      __syncthreads();
+      if (warp == 0) {  // exclusive prefix over lengths 32, 31, ... 2
+        const int len = 32 - lane;
+        const int v   = S.hist[len];
+        int inc       = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int y = __shfl_up_sync(0xFFFFFFFFu, inc, d);
+          if (lane >= d) inc += y;
+        }
+        S.hist[len] = inc - v;
+        if (lane == 31) S.nseg = inc;
+      }
+      __syncthreads();
+      for (uint32_t mm = m; mm;) {  // pass 2: scatter (start, length) into the sorted list
+        const int ss = tid * 32 + __ffs(int(mm)) - 1;
+        mm &= mm - 1;
+        const int e  = next_cut(S.cut, ss);
+        const int LL = e - ss;
+        if (LL <= kThreadSegMax && !(e >= kWindow && wlen == kWindow)) {
+          const int pos = atomicAdd(&S.hist[LL], 1);
+          S.seg[pos]    = uint32_t(ss) | (uint32_t(LL) << 16);
+        }
+      }
     }
     __syncthreads();
 
@@ -633,27 +668,14 @@ __global__ void __launch_bounds__(kOptThreads) k_merge_opt(EncodeBuffers b, Devi
             if (j >= nseg) {
               drained = true;
             } else {
-              const int ss = S.seg[j];
-              const int e  = next_cut(S.cut, ss);
-              const int LL = e - ss;
-              if (e >= kWindow && wlen == kWindow) {
-                S.over_start = ss;  // runs past the window: finished in the HBM workspace below
-              } else if (LL <= kThreadSegMax) {
-                s     = ss;
-                L     = LL;
-                alive = (LL >= 32) ? 0xFFFFFFFFu : ((1u << LL) - 1u);
-              } else {
-                const int q = atomicAdd(&S.nlong, 1);
-                if (q < kLongCap) S.longq[q] = uint16_t(ss);
-                else atomicMax(status, int(kStatusLongQueueOverflow));
-              }
+              const uint32_t ent = S.seg[j];
+              s     = int(ent & 0xFFFFu);
+              L     = int(ent >> 16);
+              alive = (L >= 32) ? 0xFFFFFFFFu : ((1u << L) - 1u);
             }
           }
         }
-        if (!__any_sync(0xFFFFFFFFu, s >= 0)) {
-          if (__all_sync(0xFFFFFFFFu, drained)) break;
-          continue;
-        }
+        if (!__any_sync(0xFFFFFFFFu, s >= 0)) break;  // a lane without work here is drained
         if (s >= 0 && !thread_merge_step(S.tok + s, S.rk + s, L, alive, T)) s = -1;
       }
     }
