@@ -182,6 +182,8 @@ class GpuTokenizer {
     d["max_iters"] = ti.max_iters;
     d["device"] = ti.device;
     d["sm_count"] = ti.sm_count;
+    d["whole_segment_entries"] = ti.whole_segment_entries;
+    d["whole_segment_max_probe"] = ti.whole_segment_max_probe;
     return d;
   }
 

@@ -101,7 +101,7 @@ struct gtk_tokenizer {
   mutable std::string last_error;
 
   // table in HBM
-  DevBuf d_slots, d_bpr, d_mor, d_sor, d_adj, d_b2i;
+  DevBuf d_slots, d_bpr, d_mor, d_sor, d_adj, d_b2i, d_words;
   gtk::DeviceTable dtab{};
 
   // arenas
@@ -141,6 +141,7 @@ void upload_table(gtk_tokenizer* h)
   upload(h->d_sor, t.same_of_rank.data(), t.same_of_rank.size(), h->stream);
   upload(h->d_adj, t.adj, sizeof(t.adj), h->stream);
   upload(h->d_b2i, t.byte_to_id, sizeof(t.byte_to_id), h->stream);
+  upload(h->d_words, t.word_slots.data(), t.word_slots.size() * sizeof(gtk::WordSlot), h->stream);
   GTK_CUDA(cudaStreamSynchronize(h->stream));
   h->dtab.slots = h->d_slots.as<uint4>();
   h->dtab.byte_pair_rank = h->d_bpr.as<uint16_t>();
@@ -148,10 +149,14 @@ void upload_table(gtk_tokenizer* h)
   h->dtab.same_of_rank = h->d_sor.as<uint8_t>();
   h->dtab.adj = h->d_adj.as<uint32_t>();
   h->dtab.byte_to_id = h->d_b2i.as<uint16_t>();
+  h->dtab.word_slots = h->d_words.as<uint4>();
+  h->dtab.word_log2_capacity = t.word_log2_capacity;
+  h->dtab.word_max_probe = t.word_max_probe;
   h->dtab.log2_capacity = t.log2_capacity;
   h->dtab.max_probe = t.max_probe;
   h->dtab.monotone = t.monotone ? 1 : 0;
   h->dtab.merged_is_256_plus_rank = t.merged_is_256_plus_rank ? 1 : 0;
+  h->dtab.byte_ids_identity = t.byte_ids_identity ? 1 : 0;
 }
 
 // Upper bound on the number of chunks without touching the device: every text
@@ -386,7 +391,7 @@ GTK_API void gtk_destroy(gtk_tokenizer* h)
   if (h->device >= 0) {
     cudaSetDevice(h->device);
     if (h->stream) cudaStreamSynchronize(h->stream);
-    for (DevBuf* b : {&h->d_slots, &h->d_bpr, &h->d_mor, &h->d_sor, &h->d_adj, &h->d_b2i, &h->d_bytes, &h->d_text_off,
+    for (DevBuf* b : {&h->d_slots, &h->d_bpr, &h->d_mor, &h->d_sor, &h->d_adj, &h->d_b2i, &h->d_words, &h->d_bytes, &h->d_text_off,
                       &h->d_text_chunk_base, &h->d_chunk_off, &h->d_tile_chunk0, &h->d_staging, &h->d_unit_first,
                       &h->d_unit_cnt, &h->d_chunk_cnt, &h->d_unit_base, &h->d_chunk_id_off, &h->d_text_id_off,
                       &h->d_out_ids, &h->d_seg_scratch, &h->d_scan_sums, &h->d_counters, &h->d_totals})
@@ -419,6 +424,8 @@ GTK_API int gtk_table_info_get(const gtk_tokenizer* h, gtk_table_info* out)
   out->max_iters = h->max_iters;
   out->device = h->device;
   out->sm_count = h->sm_count;
+  out->whole_segment_entries = int32_t(t.word_count);
+  out->whole_segment_max_probe = t.word_max_probe;
   return GTK_OK;
 }
 

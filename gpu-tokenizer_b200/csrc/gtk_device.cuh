@@ -29,10 +29,14 @@ struct DeviceTable {
   const uint8_t* same_of_rank;     // [max_rank+1]
   const uint32_t* adj;             // [2048]
   const uint16_t* byte_to_id;      // [256]
+  const uint4* word_slots;         // WordSlot[word capacity]: {k0, k1, k2, length << 16 | id}
+  uint32_t word_log2_capacity;
+  uint32_t word_max_probe;
   uint32_t log2_capacity;
   uint32_t max_probe;
   int monotone;
   int merged_is_256_plus_rank;
+  int byte_ids_identity;
 };
 
 // Status word written by kernels instead of trapping: 0 = fine.

@@ -47,6 +47,25 @@ __device__ __forceinline__ uint32_t probe_rank(const DeviceTable& T, uint32_t le
   return NONE;
 }
 
+// Whole-segment table: id of the vocabulary string (k0,k1,k2 = bytes zero padded, L = length)
+// if the greedy rule turns exactly that string into one token, else 0xFFFFFFFF.
+__device__ __forceinline__ uint32_t word_lookup(const DeviceTable& T, uint32_t k0, uint32_t k1, uint32_t k2,
+                                                uint32_t L)
+{
+  const uint32_t mask = (1u << T.word_log2_capacity) - 1u;
+  uint32_t h          = (k0 * 0x9E3779B1u) ^ (k1 * 0x85EBCA77u) ^ (k2 * 0xC2B2AE3Du);
+  h ^= h >> 15;
+  h *= 0x2C1B3C6Du;
+  h >>= (32 - T.word_log2_capacity);
+  for (uint32_t d = 0; d <= T.word_max_probe; ++d) {
+    const uint4 s = __ldg(T.word_slots + h);
+    if (s.w == 0u) return 0xFFFFFFFFu;
+    if (s.x == k0 && s.y == k1 && s.z == k2 && (s.w >> 16) == L) return s.w & 0xFFFFu;
+    h = (h + 1u) & mask;
+  }
+  return 0xFFFFFFFFu;
+}
+
 __device__ __forceinline__ uint32_t merged_id(const DeviceTable& T, uint32_t rank)
 {
   return T.merged_is_256_plus_rank ? 256u + rank : __ldg(T.merged_of_rank + rank);
@@ -484,11 +503,27 @@ constexpr int kCutWords = kWindow / 32;  // 144
 constexpr int kSegCap   = kTile / 2 + 8;
 constexpr int kLongCap  = 128;
 
+// Optional per-phase cycle accounting of k_merge_opt (build with -DGTK_PHASE_TIMING): thread 0 of
+// every CTA accumulates clock64() deltas between phase boundaries; read with gtk_debug_phase_cycles.
+#ifdef GTK_PHASE_TIMING
+__device__ unsigned long long g_phase_cycles[16];
+#define GTK_PHASE(k)                                              \
+  do {                                                            \
+    if (tid == 0) {                                               \
+      const long long now__ = clock64();                          \
+      atomicAdd(&g_phase_cycles[k], (unsigned long long)(now__ - phase_t0)); \
+      phase_t0 = now__;                                           \
+    }                                                             \
+  } while (0)
+#else
+#define GTK_PHASE(k) do { } while (0)
+#endif
+
 struct OptSmem {
   alignas(16) uint8_t bytes[kWindow + 32];  // [15] = byte before the window, [16+i] = window position i
   uint32_t adj[2048];
-  uint16_t tok[kWindow];
-  uint16_t rk[kWindow];  // reused as the compacted output buffer after merging
+  alignas(8) uint16_t tok[kWindow];
+  alignas(8) uint16_t rk[kWindow];  // reused as the compacted output buffer after merging
   uint32_t seg[kSegCap];  // (start | length << 16) of owned short segments, longest first
   int hist[34];
   uint32_t cut[kCutWords + 2];  // segment-start bits; reused as the alive bitmap
@@ -497,7 +532,7 @@ struct OptSmem {
   GroupScratch gs;
   int scanbuf[33];
   int ticket;
-  int nseg, nlong, seg_next;
+  int nseg, nlong, seg_next, nmiss;
   int first_start, last_start, over_start;
   int over_len;
   long long over_end;
@@ -525,6 +560,7 @@ __global__ void __launch_bounds__(kOptThreads) k_merge_opt(EncodeBuffers b, Devi
   for (int i = tid; i < 2048; i += kOptThreads) S.adj[i] = T.adj[i];
   if (tid < 2) S.cut[kCutWords + tid] = 0xFFFFFFFFu;
   const bool aligned = (reinterpret_cast<uintptr_t>(b.bytes) & 15u) == 0;
+  const bool identity_ids = T.byte_ids_identity != 0;
 
   for (;;) {
     __syncthreads();
@@ -532,6 +568,7 @@ __global__ void __launch_bounds__(kOptThreads) k_merge_opt(EncodeBuffers b, Devi
       S.ticket      = atomicAdd(b.counters + 0, 1);
       S.nlong       = 0;
       S.seg_next    = 0;
+      S.nmiss       = 0;
       S.first_start = kWindow;
       S.last_start  = -1;
       S.over_start  = -1;
@@ -540,6 +577,9 @@ __global__ void __launch_bounds__(kOptThreads) k_merge_opt(EncodeBuffers b, Devi
     __syncthreads();
     const int64_t k = S.ticket;
     if (k >= b.n_tiles) break;
+#ifdef GTK_PHASE_TIMING
+    long long phase_t0 = clock64();
+#endif
     const int64_t lo = k * kTile;
     const int wlen   = int(min(int64_t(kWindow), n - lo));
     const int own    = int(min(int64_t(kTile), n - lo));
@@ -564,17 +604,41 @@ __global__ void __launch_bounds__(kOptThreads) k_merge_opt(EncodeBuffers b, Devi
     if (tid == 0) S.bytes[15] = (lo > 0) ? b.bytes[lo - 1] : uint8_t(0);
     __syncthreads();
 
-    // ---- B. segment starts from the never-merge bitmap, initial ids and byte-pair ranks ----
-    for (int i = tid; i < kWindow; i += kOptThreads) {
-      const uint32_t cur = S.bytes[16 + i], prv = S.bytes[15 + i], nxt = S.bytes[17 + i];
-      const bool start   = (i >= wlen) || (lo + i == 0) || !adj_bit(S.adj, prv, cur);
-      const uint32_t bal = __ballot_sync(0xFFFFFFFFu, start);
-      if (lane == 0) S.cut[i >> 5] = bal;
-      S.tok[i] = (i < wlen) ? __ldg(T.byte_to_id + cur) : uint16_t(DEAD);
-      S.rk[i]  = (i + 1 < wlen) ? __ldg(T.byte_pair_rank + ((cur << 8) | nxt)) : uint16_t(NONE);
+    GTK_PHASE(0);
+    // ---- B. segment starts from the never-merge bitmap, initial ids and byte-pair ranks.
+    //         Four consecutive positions per thread; eight lanes assemble one 32-bit bitmap word ----
+    for (int g = tid; g < kWindow / 4; g += kOptThreads) {
+      const int i0     = g * 4;
+      const uint32_t w = *reinterpret_cast<const uint32_t*>(&S.bytes[16 + i0]);
+      uint32_t by[6];
+      by[0] = S.bytes[15 + i0];
+      by[1] = w & 0xFFu;
+      by[2] = (w >> 8) & 0xFFu;
+      by[3] = (w >> 16) & 0xFFu;
+      by[4] = w >> 24;
+      by[5] = S.bytes[20 + i0];
+      uint32_t mergeable = 0;  // bit k: the pair (by[k], by[k+1]) occurs inside some merge result
+#pragma unroll
+      for (int k = 0; k < 5; ++k) mergeable |= uint32_t(adj_bit(S.adj, by[k], by[k + 1])) << k;
+      uint32_t nib = 0, t[4], r[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int i      = i0 + k;
+        const bool start = (i >= wlen) || (lo + i == 0) || !((mergeable >> k) & 1u);
+        nib |= uint32_t(start) << k;
+        t[k] = (i < wlen) ? (identity_ids ? by[k + 1] : uint32_t(__ldg(T.byte_to_id + by[k + 1]))) : DEAD;
+        r[k] = ((i + 1 < wlen) && ((mergeable >> (k + 1)) & 1u))
+                   ? uint32_t(__ldg(T.byte_pair_rank + ((by[k + 1] << 8) | by[k + 2])))
+                   : NONE;
+      }
+      const uint32_t word = __reduce_or_sync(0xFFu << (lane & 24), nib << (4 * (lane & 7)));
+      if ((lane & 7) == 0) S.cut[g >> 3] = word;
+      *reinterpret_cast<uint2*>(&S.tok[i0]) = make_uint2(t[0] | (t[1] << 16), t[2] | (t[3] << 16));
+      *reinterpret_cast<uint2*>(&S.rk[i0])  = make_uint2(r[0] | (r[1] << 16), r[2] | (r[3] << 16));
     }
     __syncthreads();
 
+    GTK_PHASE(1);
     // ---- C. chunk boundaries are segment starts too ----
     {
       const int64_t c0 = b.tile_chunk0[k];
@@ -589,6 +653,7 @@ __global__ void __launch_bounds__(kOptThreads) k_merge_opt(EncodeBuffers b, Devi
     }
     __syncthreads();
 
+    GTK_PHASE(2);
     // ---- D. owned segments of at least two bytes, sorted by length (longest first) so that the
     //         lanes of a warp work on segments of similar length in step E ----
     {
@@ -648,10 +713,60 @@ __global__ void __launch_bounds__(kOptThreads) k_merge_opt(EncodeBuffers b, Devi
     }
     __syncthreads();
 
+    GTK_PHASE(3);
+    // ---- E1. whole-segment lookup: a segment whose bytes are a vocabulary string that the greedy
+    //          rule collapses to one id is finished with a single table probe; the others are
+    //          compacted to the front of the list for the merge loop ----
+    GTK_PHASE(9);
+    {
+      const int nseg = S.nseg;
+      for (int r0 = 0; r0 < nseg; r0 += kOptThreads) {
+        const int j  = r0 + tid;
+        uint32_t ent = 0;
+        bool miss    = false;
+        if (j < nseg) {
+          ent          = S.seg[j];
+          const int ss = int(ent & 0xFFFFu);
+          const int LL = int(ent >> 16);
+          miss         = true;
+          if (LL <= 12) {
+            const int at       = 16 + ss;
+            const uint32_t* wp = reinterpret_cast<const uint32_t*>(&S.bytes[at & ~3]);
+            const uint32_t sh  = uint32_t(at & 3) * 8u;
+            const uint32_t a0 = wp[0], a1 = wp[1], a2 = wp[2], a3 = wp[3];
+            uint32_t k0 = __funnelshift_r(a0, a1, sh), k1 = __funnelshift_r(a1, a2, sh),
+                     k2 = __funnelshift_r(a2, a3, sh);
+            k0 &= (LL >= 4) ? 0xFFFFFFFFu : ((1u << (8 * LL)) - 1u);
+            k1 &= (LL >= 8) ? 0xFFFFFFFFu : ((LL <= 4) ? 0u : ((1u << (8 * (LL - 4))) - 1u));
+            k2 &= (LL >= 12) ? 0xFFFFFFFFu : ((LL <= 8) ? 0u : ((1u << (8 * (LL - 8))) - 1u));
+            const uint32_t id = word_lookup(T, k0, k1, k2, uint32_t(LL));
+            if (id != 0xFFFFFFFFu) {
+              miss      = false;
+              S.tok[ss] = uint16_t(id);
+              for (int i = 1; i < LL; ++i) S.tok[ss + i] = uint16_t(DEAD);
+            }
+          }
+        }
+        const uint32_t bal = __ballot_sync(0xFFFFFFFFu, miss);
+        int wbase          = 0;
+        if (lane == 0 && bal) wbase = atomicAdd(&S.nmiss, __popc(bal));
+        wbase = __shfl_sync(0xFFFFFFFFu, wbase, 0);
+        __syncthreads();  // every entry of this round has been read before the list is overwritten
+        if (miss) S.seg[wbase + __popc(bal & lt)] = ent;
+      }
+    }
+    __syncthreads();
+
+#ifdef GTK_PHASE_TIMING
+    if (tid == 0) {
+      atomicAdd(&g_phase_cycles[10], (unsigned long long)S.nmiss);
+      atomicAdd(&g_phase_cycles[11], (unsigned long long)S.nseg);
+    }
+#endif
     // ---- E. short segments: every lane pulls segments from a CTA-wide queue and does one merge
     //         step per loop trip, so a lane that finishes early takes new work instead of idling ----
     {
-      const int nseg   = S.nseg;
+      const int nseg   = S.nmiss;
       int s            = -1, L = 0;
       uint32_t alive   = 0;
       bool drained     = false;
@@ -681,6 +796,7 @@ __global__ void __launch_bounds__(kOptThreads) k_merge_opt(EncodeBuffers b, Devi
     }
     __syncthreads();
 
+    GTK_PHASE(4);
     // ---- F. one warp per long segment ----
     {
       const int nl = min(S.nlong, kLongCap);
@@ -694,17 +810,23 @@ __global__ void __launch_bounds__(kOptThreads) k_merge_opt(EncodeBuffers b, Devi
     }
     __syncthreads();
 
+    GTK_PHASE(5);
     // ---- G/H. compact the owned region [first, end) into S.rk, then to staging ----
     const int first = S.first_start;
     int end_owned   = 0;
     if (S.last_start >= 0) end_owned = (S.over_start >= 0) ? S.over_start : next_cut(S.cut, S.last_start);
     if (end_owned > wlen) end_owned = wlen;
     __syncthreads();  // every thread has read cut[] before it becomes the alive bitmap
-    for (int w = warp; w < kCutWords; w += kOptThreads / 32) {
-      const int i       = w * 32 + lane;
-      const bool alive  = (i >= first) && (i < end_owned) && (S.tok[i] != DEAD);
-      const uint32_t bal = __ballot_sync(0xFFFFFFFFu, alive);
-      if (lane == 0) S.cut[w] = bal;
+    for (int g = tid; g < kWindow / 4; g += kOptThreads) {
+      const int i0   = g * 4;
+      const uint2 tk = *reinterpret_cast<const uint2*>(&S.tok[i0]);
+      const uint32_t t[4] = {tk.x & 0xFFFFu, tk.x >> 16, tk.y & 0xFFFFu, tk.y >> 16};
+      uint32_t nib = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        nib |= uint32_t((i0 + k >= first) && (i0 + k < end_owned) && (t[k] != DEAD)) << k;
+      const uint32_t word = __reduce_or_sync(0xFFu << (lane & 24), nib << (4 * (lane & 7)));
+      if ((lane & 7) == 0) S.cut[g >> 3] = word;
     }
     __syncthreads();
     int total;
@@ -714,14 +836,25 @@ __global__ void __launch_bounds__(kOptThreads) k_merge_opt(EncodeBuffers b, Devi
       if (tid < kCutWords) S.woff[tid] = uint16_t(off);
     }
     __syncthreads();
-    for (int w = warp; w < kCutWords; w += kOptThreads / 32) {
-      const uint32_t bal = S.cut[w];
-      if ((bal >> lane) & 1u) S.rk[S.woff[w] + __popc(bal & lt)] = S.tok[w * 32 + lane];
+    for (int g = tid; g < kWindow / 4; g += kOptThreads) {
+      const int i0        = g * 4;
+      const int sh        = 4 * (lane & 7);
+      const uint32_t word = S.cut[g >> 3];
+      uint32_t nib        = (word >> sh) & 0xFu;
+      if (nib) {
+        int d          = S.woff[g >> 3] + __popc(word & ((1u << sh) - 1u));
+        const uint2 tk = *reinterpret_cast<const uint2*>(&S.tok[i0]);
+        const uint32_t t[4] = {tk.x & 0xFFFFu, tk.x >> 16, tk.y & 0xFFFFu, tk.y >> 16};
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if ((nib >> k) & 1u) S.rk[d++] = uint16_t(t[k]);
+      }
     }
     __syncthreads();
     const int64_t region_start = lo + ((first < kWindow) ? first : 0);
     for (int j = tid; j < total; j += kOptThreads) b.staging[region_start + j] = S.rk[j];
 
+    GTK_PHASE(6);
     // ---- I. per-chunk token counts from the alive bitmap ----
     {
       const int64_t region_end = lo + end_owned;
@@ -744,6 +877,7 @@ __global__ void __launch_bounds__(kOptThreads) k_merge_opt(EncodeBuffers b, Devi
       }
     }
 
+    GTK_PHASE(7);
     // ---- J. a segment that runs past the window (rare): whole CTA, HBM workspace ----
     if (S.over_start >= 0) {  // CTA-uniform
       const int64_t gs0 = lo + S.over_start;
@@ -790,6 +924,7 @@ __global__ void __launch_bounds__(kOptThreads) k_merge_opt(EncodeBuffers b, Devi
       __syncthreads();
     }
 
+    GTK_PHASE(8);
     // ---- K. unit record ----
     if (tid == 0) {
       b.unit_first[k] = region_start;
@@ -943,6 +1078,18 @@ int launch_pack(const EncodeBuffers& b, int mode_base, int grid, cudaStream_t st
   }
   return 1;
 }
+
+#ifdef GTK_PHASE_TIMING
+extern "C" __attribute__((visibility("default"))) void gtk_debug_phase_cycles(unsigned long long out[16], int reset)
+{
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out, g_phase_cycles, sizeof(unsigned long long) * 16);
+  if (reset) {
+    unsigned long long z[16] = {};
+    cudaMemcpyToSymbol(g_phase_cycles, z, sizeof(z));
+  }
+}
+#endif
 
 int opt_kernel_max_blocks_per_sm()
 {

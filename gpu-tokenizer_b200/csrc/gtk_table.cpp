@@ -137,6 +137,7 @@ HostTable::HostTable(const std::string& merges_path)
   }
   build_hash();
   build_derived();
+  build_words();
 }
 
 void HostTable::build_hash()
@@ -155,6 +156,36 @@ void HostTable::build_hash()
     slots[h] = {uint32_t(r.right), uint32_t(r.left), r.rank, uint32_t(r.merged)};
     max_probe = std::max(max_probe, d);
     max_rank = std::max(max_rank, r.rank);
+  }
+}
+
+// A segment whose bytes equal a vocabulary string that the greedy rule collapses to that one id
+// needs no merging at all.  The entries are checked here, one by one, with the same greedy routine
+// that defines the result, so the shortcut cannot change any output.
+void HostTable::build_words()
+{
+  std::vector<std::pair<std::string, int32_t>> words;
+  std::vector<int32_t> out;
+  for (size_t id = 0; id < id_to_bytes.size(); ++id) {
+    const std::string& bs = id_to_bytes[id];
+    if (!decodable[id] || bs.size() < 2 || bs.size() > size_t(kWordMaxBytes) || id >= 0xFFFFu) continue;
+    out.clear();
+    greedy_chunk(reinterpret_cast<const uint8_t*>(bs.data()), int64_t(bs.size()), out);
+    if (out.size() == 1 && out[0] == int32_t(id)) words.emplace_back(bs, int32_t(id));
+  }
+  word_count = uint32_t(words.size());
+  word_log2_capacity = 10;
+  while ((size_t(1) << word_log2_capacity) < words.size() * 2 + 1) ++word_log2_capacity;
+  const uint32_t cap = 1u << word_log2_capacity, mask = cap - 1;
+  word_slots.assign(cap, WordSlot{0, 0, 0, 0});
+  word_max_probe = 0;
+  for (auto& w : words) {
+    uint32_t k[3] = {0, 0, 0};
+    for (size_t i = 0; i < w.first.size(); ++i) k[i >> 2] |= uint32_t((unsigned char)w.first[i]) << (8 * (i & 3));
+    uint32_t h = word_hash(k[0], k[1], k[2], word_log2_capacity), d = 0;
+    while (word_slots[h].meta != 0) { h = (h + 1) & mask; ++d; }
+    word_slots[h] = {k[0], k[1], k[2], (uint32_t(w.first.size()) << 16) | uint32_t(w.second)};
+    word_max_probe = std::max(word_max_probe, d);
   }
 }
 

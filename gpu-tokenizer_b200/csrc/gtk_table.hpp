@@ -27,6 +27,22 @@ struct alignas(16) HashSlot {
   uint32_t merged;
 };
 
+// One slot of the whole-segment table: a byte string of 2..12 bytes (zero padded to three
+// words) whose greedy tokenisation is the single id in `meta` (length << 16 | id); meta 0 = empty.
+struct alignas(16) WordSlot {
+  uint32_t k0, k1, k2;
+  uint32_t meta;
+};
+constexpr int kWordMaxBytes = 12;
+
+inline uint32_t word_hash(uint32_t k0, uint32_t k1, uint32_t k2, uint32_t log2_capacity)
+{
+  uint32_t h = (k0 * 0x9E3779B1u) ^ (k1 * 0x85EBCA77u) ^ (k2 * 0xC2B2AE3Du);
+  h ^= h >> 15;
+  h *= 0x2C1B3C6Du;
+  return h >> (32 - log2_capacity);
+}
+
 struct MergeRow {
   int32_t  left, right;
   uint32_t rank;
@@ -69,6 +85,13 @@ class HostTable {
   uint32_t adj[2048];                      // bit (u<<8|v): bigram occurs inside a merge result
   int adj_count = 0;
 
+  // whole-segment fast path: every vocabulary string of 2..12 bytes that the greedy rule turns
+  // into exactly its own id (verified one by one with greedy_chunk at build time)
+  std::vector<WordSlot> word_slots;
+  uint32_t word_log2_capacity = 0;
+  uint32_t word_max_probe = 0;
+  uint32_t word_count = 0;
+
   // properties the kernels rely on
   bool monotone = false;        // rank(m) > rank of every merge producing one of m's parts
   bool merged_is_256_plus_rank = false;
@@ -94,6 +117,7 @@ class HostTable {
   int32_t add_token(const std::string& symbols);
   void build_hash();
   void build_derived();
+  void build_words();
 };
 
 }  // namespace gtk

@@ -81,6 +81,8 @@ typedef struct gtk_table_info {
   int32_t  max_iters;
   int32_t  device;           /* CUDA device ordinal, -1 for a host-only handle */
   int32_t  sm_count;
+  int32_t  whole_segment_entries;   /* vocabulary strings (2..12 bytes) answered by one table probe */
+  uint32_t whole_segment_max_probe; /* longest probe sequence in that table */
 } gtk_table_info;
 
 /* Library version string. */
