@@ -222,7 +222,7 @@ def run_reference_arm(args, rank: int, world: int):
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
@@ -295,9 +295,9 @@ def main() -> None:
         return tok.encode_device(d_bytes.data_ptr(), n_bytes, d_toff.data_ptr(), n_texts, d_ids.data_ptr(), cap,
                                  d_coff.data_ptr(), chunk_cap, mode=mode)
 
+    sampler = ClockSampler(local_rank) if rank == 0 else None  # samples through warm-up and both timed regions
     for _ in range(args.warmup):
         n_ids, n_chunks, _ = step_device()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
     merge_ms, stage_acc, launches = [], np.zeros(5), 0
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -313,7 +313,6 @@ def main() -> None:
     barrier()
     wall_ms = (time.perf_counter() - t0) * 1e3
     dev_ms = ev0.elapsed_time(ev1)  # CUDA events on the stream the kernels run on
-    clocks = sampler.stop() if sampler else None
     step_ms = allmax(dev_ms / args.steps)
     total_bytes = allsum(float(n_bytes))
     total_ids = allsum(float(n_ids))
@@ -335,6 +334,7 @@ def main() -> None:
     e2e_ms = allmax(max(ev0.elapsed_time(ev1), 0.0) / e2e_steps)
     e2e_wall_ms = allmax((time.perf_counter() - t0) * 1e3 / e2e_steps)
     e2e_value = total_bytes / (e2e_wall_ms * 1e-3) / 1e6
+    clocks = sampler.stop() if sampler else None
     h2d = n_bytes + 8 * (n_texts + 1)
     d2h = 4 * len(ids_h) + 8 * len(coff_h) + 8 * len(toff_h) + 32
 

@@ -87,6 +87,30 @@ struct PinBuf {
 
 }  // namespace
 
+// Buffers of one in-flight slice of a large host batch (kSliceArenas sets rotate).
+constexpr int kSliceArenas = 4;
+struct SliceArena {
+  DevBuf text_off, text_chunk_base, chunk_off, tile_chunk0, unit_first, unit_cnt, chunk_cnt, unit_base,
+      chunk_id_off, text_id_off, scan_sums, counters, totals;
+  PinBuf h_totals, h_piece_off, h_piece_id_off;
+  cudaEvent_t ev[6] = {};          // stage timing
+  cudaEvent_t ev_in = nullptr;     // slice text is in HBM
+  cudaEvent_t ev_front = nullptr;  // totals of the slice are on the host
+  cudaEvent_t ev_packed = nullptr; // ids of the slice are packed
+  cudaEvent_t ev_out = nullptr;    // results of the slice are on the host
+  void release()
+  {
+    for (DevBuf* b : {&text_off, &text_chunk_base, &chunk_off, &tile_chunk0, &unit_first, &unit_cnt, &chunk_cnt,
+                      &unit_base, &chunk_id_off, &text_id_off, &scan_sums, &counters, &totals})
+      b->release();
+    for (PinBuf* b : {&h_totals, &h_piece_off, &h_piece_id_off}) b->release();
+    for (auto& e : ev)
+      if (e) cudaEventDestroy(e);
+    for (cudaEvent_t* e : {&ev_in, &ev_front, &ev_packed, &ev_out})
+      if (*e) cudaEventDestroy(*e);
+  }
+};
+
 struct gtk_tokenizer {
   std::unique_ptr<gtk::HostTable> table;
   int chunk_tokens = 2048;
@@ -109,6 +133,9 @@ struct gtk_tokenizer {
       d_chunk_cnt, d_unit_base, d_chunk_id_off, d_text_id_off, d_out_ids, d_seg_scratch, d_scan_sums, d_counters,
       d_totals;
   PinBuf h_ids, h_text_id_off, h_chunk_id_off, h_totals;
+  // sliced host path: copy streams and two slice arenas
+  cudaStream_t in_stream = nullptr, out_stream = nullptr;
+  SliceArena slice[4];
   // host-side result of gtk_encode_cpu
   std::vector<int32_t> cpu_ids;
   std::vector<int64_t> cpu_text_off, cpu_chunk_off;
@@ -244,43 +271,284 @@ const char* status_text(int s)
 
 // Chunker -> merge -> scans.  Leaves totals (n_chunks, n_ids) and the status
 // word in the pinned totals buffer; the caller synchronises and then packs.
-void run_front(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* launches)
+void run_front(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* launches, cudaEvent_t* ev = nullptr,
+               int64_t* pinned_totals = nullptr)
 {
   cudaStream_t s = h->stream;
+  if (!ev) ev = h->ev;
   GTK_CUDA(cudaMemsetAsync(b.counters, 0, 64, s));
   GTK_CUDA(cudaMemsetAsync(b.chunk_cnt, 0, size_t(b.chunk_cap + 1) * 4, s));
-  GTK_CUDA(cudaEventRecord(h->ev[0], s));
+  GTK_CUDA(cudaEventRecord(ev[0], s));
   *launches += gtk::launch_chunker(b, s);
-  GTK_CUDA(cudaEventRecord(h->ev[1], s));
+  GTK_CUDA(cudaEventRecord(ev[1], s));
   if (mode == GTK_MODE_BASE) *launches += gtk::launch_merge_base(b, h->dtab, h->base_grid, s);
   else *launches += gtk::launch_merge_opt(b, h->dtab, h->opt_grid, s);
-  GTK_CUDA(cudaEventRecord(h->ev[2], s));
+  GTK_CUDA(cudaEventRecord(ev[2], s));
   *launches += gtk::launch_output_scans(b, mode == GTK_MODE_BASE, s);
-  GTK_CUDA(cudaEventRecord(h->ev[3], s));
+  GTK_CUDA(cudaEventRecord(ev[3], s));
   GTK_CUDA(cudaGetLastError());
-  int64_t* ht = h->h_totals.as<int64_t>();
+  int64_t* ht = pinned_totals ? pinned_totals : h->h_totals.as<int64_t>();
   GTK_CUDA(cudaMemcpyAsync(ht, b.totals, 16, cudaMemcpyDeviceToHost, s));
   GTK_CUDA(cudaMemcpyAsync(ht + 2, b.counters, 16, cudaMemcpyDeviceToHost, s));
 }
 
-void run_pack(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* launches)
+void run_pack(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* launches, cudaEvent_t* ev = nullptr)
 {
   cudaStream_t s = h->stream;
-  GTK_CUDA(cudaEventRecord(h->ev[5], s));
+  if (!ev) ev = h->ev;
+  GTK_CUDA(cudaEventRecord(ev[5], s));
   *launches += gtk::launch_pack(b, mode == GTK_MODE_BASE, h->sm_count * 8, s);
-  GTK_CUDA(cudaEventRecord(h->ev[4], s));
+  GTK_CUDA(cudaEventRecord(ev[4], s));
   GTK_CUDA(cudaGetLastError());
 }
 
-void collect_stage_times(gtk_tokenizer* h)
+// adds the stage times of one pipeline run (one batch, or one slice) to h->stage_ms
+void collect_stage_times(gtk_tokenizer* h, cudaEvent_t* ev = nullptr)
 {
+  if (!ev) ev = h->ev;
   float ms = 0;
   for (int i = 0; i < 3; ++i) {
-    if (cudaEventElapsedTime(&ms, h->ev[i], h->ev[i + 1]) == cudaSuccess) h->stage_ms[i] = ms;
+    if (cudaEventElapsedTime(&ms, ev[i], ev[i + 1]) == cudaSuccess) h->stage_ms[i] += ms;
   }
-  if (cudaEventElapsedTime(&ms, h->ev[5], h->ev[4]) == cudaSuccess) h->stage_ms[3] = ms;
+  if (cudaEventElapsedTime(&ms, ev[5], ev[4]) == cudaSuccess) h->stage_ms[3] += ms;
   // the pipeline time excludes the host round trip between scans and pack
   h->stage_ms[4] = h->stage_ms[0] + h->stage_ms[1] + h->stage_ms[2] + h->stage_ms[3];
+}
+
+
+// ------------------------------------------------------------------------------------------------
+// Large host batches: cut the batch into slices of whole chunks and overlap, per slice, the
+// host->device copy, the kernel pipeline and the device->host copy of the results on three
+// streams.  A slice is an independent sub-batch (its pieces are texts or chunk-aligned parts of a
+// text), so the per-chunk results are exactly those of the unsliced batch.
+// ------------------------------------------------------------------------------------------------
+constexpr int64_t kSliceThresholdBytes = int64_t(24) << 20;  // smaller batches take the single-shot path
+constexpr int64_t kSliceTargetBytes    = int64_t(16) << 20;
+
+struct SlicePlan {
+  int64_t byte_lo = 0, byte_hi = 0;
+  std::vector<int64_t> piece_off;    // [P+1], relative to byte_lo
+  std::vector<int64_t> first_text;   // [P]: text index if the piece starts a text, else -1
+};
+
+std::vector<SlicePlan> plan_slices(const int64_t* text_off, int64_t n_texts, int chunk, int64_t target)
+{
+  std::vector<SlicePlan> out;
+  SlicePlan cur;
+  cur.piece_off.push_back(0);
+  auto close = [&](int64_t at) {
+    cur.byte_hi = at;
+    out.push_back(std::move(cur));
+    cur = SlicePlan();
+    cur.byte_lo = at;
+    cur.piece_off.push_back(0);
+  };
+  for (int64_t t = 0; t < n_texts; ++t) {
+    int64_t pos = text_off[t];
+    const int64_t end = text_off[t + 1];
+    bool first = true;
+    do {
+      const int64_t used = pos - cur.byte_lo;
+      int64_t take = end - pos;
+      if (used + take > target && take > 0) {
+        const int64_t room_chunks = (target - used) / chunk;
+        if (room_chunks <= 0 && used > 0) {  // slice is full: start a new one and retry
+          close(pos);
+          continue;
+        }
+        take = std::min<int64_t>(take, std::max<int64_t>(room_chunks, 1) * chunk);
+      }
+      cur.piece_off.push_back(pos + take - cur.byte_lo);
+      cur.first_text.push_back(first ? t : -1);
+      first = false;
+      pos += take;
+      if (pos - cur.byte_lo >= target) close(pos);
+    } while (pos < end);
+  }
+  if (cur.piece_off.size() > 1) close(text_off[n_texts]);
+  return out;
+}
+
+void slice_arena_prepare(gtk_tokenizer* h, SliceArena& a, int64_t max_bytes, int64_t max_pieces)
+{
+  const int64_t chunk_cap = chunk_upper_bound(max_bytes, max_pieces, h->chunk_tokens);
+  const int64_t n_tiles   = (max_bytes + gtk::kTile - 1) / gtk::kTile;
+  a.text_off.reserve(size_t(max_pieces + 1) * 8);
+  a.text_chunk_base.reserve(size_t(max_pieces + 1) * 8);
+  a.chunk_off.reserve(size_t(chunk_cap + 1) * 8);
+  a.tile_chunk0.reserve(size_t(n_tiles + 1) * 4);
+  a.unit_first.reserve(size_t(n_tiles + 1) * 8);
+  a.unit_cnt.reserve(size_t(n_tiles + 1) * 4);
+  a.chunk_cnt.reserve(size_t(chunk_cap + 1) * 4);
+  a.unit_base.reserve(size_t(n_tiles + 2) * 8);
+  a.chunk_id_off.reserve(size_t(chunk_cap + 1) * 8);
+  a.text_id_off.reserve(size_t(max_pieces + 1) * 8);
+  a.scan_sums.reserve(size_t(std::max<int64_t>(std::max(chunk_cap, n_tiles), max_pieces) / 4096 + 2) * 8);
+  a.counters.reserve(64);
+  a.totals.reserve(64);
+  a.h_totals.reserve(64);
+  a.h_piece_off.reserve(size_t(max_pieces + 1) * 8);
+  a.h_piece_id_off.reserve(size_t(max_pieces + 1) * 8);
+  for (auto& e : a.ev)
+    if (!e) GTK_CUDA(cudaEventCreate(&e));
+  for (cudaEvent_t* e : {&a.ev_in, &a.ev_front, &a.ev_packed, &a.ev_out})
+    if (!*e) GTK_CUDA(cudaEventCreateWithFlags(e, cudaEventDisableTiming));
+}
+
+gtk::EncodeBuffers slice_buffers(gtk_tokenizer* h, SliceArena& a, const SlicePlan& sp)
+{
+  gtk::EncodeBuffers b{};
+  const int64_t n_bytes = sp.byte_hi - sp.byte_lo;
+  const int64_t pieces  = int64_t(sp.piece_off.size()) - 1;
+  b.bytes = h->d_bytes.as<uint8_t>() + sp.byte_lo;
+  b.n_bytes = n_bytes;
+  b.text_off = a.text_off.as<int64_t>();
+  b.n_texts = pieces;
+  b.chunk_bytes = h->chunk_tokens;
+  b.text_chunk_base = a.text_chunk_base.as<int64_t>();
+  b.chunk_off = a.chunk_off.as<int64_t>();
+  b.chunk_cap = chunk_upper_bound(n_bytes, pieces, h->chunk_tokens);
+  b.tile_chunk0 = a.tile_chunk0.as<int32_t>();
+  b.n_tiles = (n_bytes + gtk::kTile - 1) / gtk::kTile;
+  b.staging = h->d_staging.as<uint16_t>() + sp.byte_lo;
+  b.unit_first = a.unit_first.as<int64_t>();
+  b.unit_cnt = a.unit_cnt.as<int32_t>();
+  b.chunk_cnt = a.chunk_cnt.as<int32_t>();
+  b.unit_base = a.unit_base.as<int64_t>();
+  b.chunk_id_off = a.chunk_id_off.as<int64_t>();
+  b.text_id_off = a.text_id_off.as<int64_t>();
+  b.out_ids = h->d_out_ids.as<int32_t>() + sp.byte_lo;  // worst case one id per byte: slices never overlap
+  b.out_capacity = n_bytes;
+  const int64_t longest = std::min<int64_t>(h->chunk_tokens, n_bytes);
+  const int64_t scratch_tokens = longest > gtk::kHalo ? ((longest + 63) & ~int64_t(63)) : 0;
+  b.seg_scratch = scratch_tokens ? h->d_seg_scratch.as<uint16_t>() : nullptr;
+  b.seg_scratch_tokens = scratch_tokens;
+  b.scan_block_sums = a.scan_sums.as<int64_t>();
+  b.counters = a.counters.as<int32_t>();
+  b.totals = a.totals.as<int64_t>();
+  return b;
+}
+
+
+int encode_host_sliced(gtk_tokenizer* h, int mode, const uint8_t* bytes, const int64_t* text_offsets,
+                       int64_t n_texts, int64_t n_bytes, float* kernel_ms)
+{
+  const std::vector<SlicePlan> slices = plan_slices(text_offsets, n_texts, h->chunk_tokens, kSliceTargetBytes);
+  const int ns = int(slices.size());
+  int64_t max_bytes = 0, max_pieces = 0, total_pieces = 0;
+  for (const SlicePlan& sp : slices) {
+    max_bytes = std::max(max_bytes, sp.byte_hi - sp.byte_lo);
+    max_pieces = std::max<int64_t>(max_pieces, int64_t(sp.piece_off.size()) - 1);
+    total_pieces += int64_t(sp.piece_off.size()) - 1;
+  }
+  // everything is sized before the first copy is issued: nothing may be reallocated in flight
+  h->d_bytes.reserve(size_t(n_bytes) + 32);
+  h->d_staging.reserve(size_t(n_bytes + 16) * 2);
+  h->d_out_ids.reserve(size_t(n_bytes) * 4 + 64);
+  {
+    const int64_t longest = std::min<int64_t>(h->chunk_tokens, max_bytes);
+    if (longest > gtk::kHalo)
+      h->d_seg_scratch.reserve(size_t(std::max(h->opt_grid, h->base_grid)) * 2 * size_t((longest + 63) & ~int64_t(63)) * 2);
+  }
+  h->h_text_id_off.reserve(size_t(n_texts + 1) * 8);
+  h->h_chunk_id_off.reserve(size_t(chunk_upper_bound(n_bytes, total_pieces, h->chunk_tokens) + 2) * 8);
+  h->h_ids.reserve(size_t(n_bytes) * 2);  // grown below if the batch yields more than one id per two bytes
+  if (!h->in_stream) GTK_CUDA(cudaStreamCreateWithFlags(&h->in_stream, cudaStreamNonBlocking));
+  if (!h->out_stream) GTK_CUDA(cudaStreamCreateWithFlags(&h->out_stream, cudaStreamNonBlocking));
+  for (auto& a : h->slice) slice_arena_prepare(h, a, max_bytes, max_pieces);
+  GTK_CUDA(cudaStreamSynchronize(h->stream));
+
+  const size_t nsz = size_t(ns);
+  std::vector<gtk::EncodeBuffers> bufs(nsz);
+  std::vector<int64_t> sl_n(nsz), sl_c(nsz), sl_r(nsz), sl_cbase(nsz);
+  int launches = 0;
+  int64_t R = 0, Cbase = 0;
+  int64_t* h_text = h->h_text_id_off.as<int64_t>();
+
+  auto issue_front = [&](int i) {
+    SliceArena& a = h->slice[i % kSliceArenas];
+    const SlicePlan& sp = slices[size_t(i)];
+    const int64_t pieces = int64_t(sp.piece_off.size()) - 1;
+    std::memcpy(a.h_piece_off.p, sp.piece_off.data(), size_t(pieces + 1) * 8);
+    GTK_CUDA(cudaMemcpyAsync(h->d_bytes.as<uint8_t>() + sp.byte_lo, bytes + sp.byte_lo, size_t(sp.byte_hi - sp.byte_lo),
+                             cudaMemcpyHostToDevice, h->in_stream));
+    GTK_CUDA(cudaMemcpyAsync(a.text_off.p, a.h_piece_off.p, size_t(pieces + 1) * 8, cudaMemcpyHostToDevice,
+                             h->in_stream));
+    GTK_CUDA(cudaEventRecord(a.ev_in, h->in_stream));
+    GTK_CUDA(cudaStreamWaitEvent(h->stream, a.ev_in, 0));
+    if (i >= kSliceArenas) GTK_CUDA(cudaStreamWaitEvent(h->stream, a.ev_out, 0));  // its previous slice has left this arena
+    bufs[size_t(i)] = slice_buffers(h, a, sp);
+    run_front(h, bufs[size_t(i)], mode, &launches, a.ev, a.h_totals.as<int64_t>());
+    GTK_CUDA(cudaEventRecord(a.ev_front, h->stream));
+  };
+  auto finish = [&](int i) {  // results of slice i are on the host: stitch its text offsets
+    SliceArena& a = h->slice[i % kSliceArenas];
+    GTK_CUDA(cudaEventSynchronize(a.ev_out));
+    collect_stage_times(h, a.ev);
+    const SlicePlan& sp = slices[size_t(i)];
+    const int64_t* pid = a.h_piece_id_off.as<int64_t>();
+    for (size_t p = 0; p < sp.first_text.size(); ++p)
+      if (sp.first_text[p] >= 0) h_text[sp.first_text[p]] = sl_r[size_t(i)] + pid[p];
+  };
+
+  // a text that starts exactly where the previous slice ended is handled by whichever slice holds its first piece
+  constexpr int kAhead = kSliceArenas - 1;  // kernel pipelines queued ahead of the slice being packed
+  for (int i = 0; i < std::min(ns, kAhead); ++i) issue_front(i);
+  for (int i = 0; i < ns; ++i) {
+    SliceArena& a = h->slice[i % kSliceArenas];
+    if (i >= 2) finish(i - 2);
+    GTK_CUDA(cudaEventSynchronize(a.ev_front));
+    const int64_t* ht = a.h_totals.as<int64_t>();
+    const int64_t C = ht[0], N = ht[1];
+    const int status = reinterpret_cast<const int32_t*>(ht + 2)[1];
+    if (status != gtk::kStatusOk) {
+      cudaStreamSynchronize(h->stream);
+      cudaStreamSynchronize(h->out_stream);
+      return h->fail(GTK_ERR_KERNEL, status_text(status));
+    }
+    if (size_t(R + N + 1) * 4 > h->h_ids.cap) {  // grow the pinned id buffer, keeping what has arrived
+      GTK_CUDA(cudaStreamSynchronize(h->out_stream));
+      PinBuf bigger;
+      bigger.reserve(std::max(size_t(R + N + 1) * 4 * 2, h->h_ids.cap * 2));
+      std::memcpy(bigger.p, h->h_ids.p, size_t(R) * 4);
+      h->h_ids.release();
+      h->h_ids = bigger;
+    }
+    run_pack(h, bufs[size_t(i)], mode, &launches, a.ev);
+    GTK_CUDA(cudaEventRecord(a.ev_packed, h->stream));
+    GTK_CUDA(cudaStreamWaitEvent(h->out_stream, a.ev_packed, 0));
+    const gtk::EncodeBuffers& b = bufs[size_t(i)];
+    GTK_CUDA(cudaMemcpyAsync(h->h_ids.as<int32_t>() + R, b.out_ids, size_t(N) * 4, cudaMemcpyDeviceToHost,
+                             h->out_stream));
+    GTK_CUDA(cudaMemcpyAsync(h->h_chunk_id_off.as<int64_t>() + Cbase, b.chunk_id_off, size_t(C + 1) * 8,
+                             cudaMemcpyDeviceToHost, h->out_stream));
+    GTK_CUDA(cudaMemcpyAsync(a.h_piece_id_off.p, b.text_id_off, size_t(b.n_texts + 1) * 8, cudaMemcpyDeviceToHost,
+                             h->out_stream));
+    GTK_CUDA(cudaEventRecord(a.ev_out, h->out_stream));
+    sl_n[size_t(i)] = N;
+    sl_c[size_t(i)] = C;
+    sl_r[size_t(i)] = R;
+    sl_cbase[size_t(i)] = Cbase;
+    R += N;
+    Cbase += C;
+    if (i + kAhead < ns) issue_front(i + kAhead);
+  }
+  for (int i = std::max(0, ns - 2); i < ns; ++i) finish(i);
+  GTK_CUDA(cudaStreamSynchronize(h->stream));
+  // per-slice chunk offsets start at 0: add the ids that precede the slice
+  int64_t* h_chunk = h->h_chunk_id_off.as<int64_t>();
+  for (int i = 0; i < ns; ++i) {
+    const int64_t base = sl_r[size_t(i)];
+    if (base)
+      for (int64_t c = sl_cbase[size_t(i)]; c < sl_cbase[size_t(i)] + sl_c[size_t(i)]; ++c) h_chunk[c] += base;
+  }
+  h_chunk[Cbase] = R;
+  h_text[n_texts] = R;
+  h->last_launches = launches;
+  h->res_n_ids = R;
+  h->res_n_chunks = Cbase;
+  if (kernel_ms) *kernel_ms = h->stage_ms[4];
+  return GTK_OK;
 }
 
 int validate_offsets(gtk_tokenizer* h, const int64_t* text_offsets, int64_t n_texts)
@@ -397,6 +665,9 @@ GTK_API void gtk_destroy(gtk_tokenizer* h)
                       &h->d_out_ids, &h->d_seg_scratch, &h->d_scan_sums, &h->d_counters, &h->d_totals})
       b->release();
     for (PinBuf* b : {&h->h_ids, &h->h_text_id_off, &h->h_chunk_id_off, &h->h_totals}) b->release();
+    for (auto& sl : h->slice) sl.release();
+    if (h->in_stream) cudaStreamDestroy(h->in_stream);
+    if (h->out_stream) cudaStreamDestroy(h->out_stream);
     for (auto& ev : h->ev)
       if (ev) cudaEventDestroy(ev);
     if (h->own_stream) cudaStreamDestroy(h->own_stream);
@@ -504,6 +775,7 @@ GTK_API int gtk_encode(gtk_tokenizer* h, int mode, const uint8_t* bytes, const i
       return GTK_OK;
     }
     if (!bytes) return h->fail(GTK_ERR_INVALID_ARG, "bytes is null");
+    if (n_bytes >= kSliceThresholdBytes) return encode_host_sliced(h, mode, bytes, text_offsets, n_texts, n_bytes, kernel_ms);
     cudaStream_t s = h->stream;
     h->d_bytes.reserve(size_t(n_bytes) + 32);
     h->d_text_off.reserve(size_t(n_texts + 1) * 8);

@@ -150,6 +150,26 @@ def test_config5_lognormal_chunks(lib, merges_path, oracle):
     assert np.array_equal(toff, coff)                     # one chunk per text
 
 
+def test_sliced_host_path_boundaries(lib, merges_path, oracle):
+    """Host batches above 24 MiB are cut into overlapped slices: texts that span slices, empty texts
+    at slice edges and a chunk size that divides nothing must give the unsliced result."""
+    lens = [30 * (1 << 20) + 11, 0, 5 << 20, 100, 17 * (1 << 20) + 3, 0, 1, 0]
+    toff_in = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    data = lib.TextGen(9).text(int(toff_in[-1]), mix=lib.MIX_STRESS)
+    t = make_tok(lib, merges_path, 4097)
+    ids, toff, coff, ms = t.encode(data, toff_in)
+    chunk_off = [0]
+    for s, e in zip(toff_in[:-1], toff_in[1:]):
+        chunk_off.extend(list(range(int(s) + 4097, int(e), 4097)) + ([int(e)] if e > s else []))
+    chunk_off = np.array(chunk_off, np.int64)
+    want, woff = oracle.encode_chunks(data, chunk_off, mode=MODE_SEGMENTED, threads=NCPU)
+    check_chunks(ids, coff, want, woff, "sliced host path")
+    starts = np.searchsorted(chunk_off, toff_in, side="left")
+    assert np.array_equal(toff, woff[starts]) and ms > 0
+    ids2, toff2, coff2, _ = t.encode(data, toff_in)       # arenas reused: identical on the second call
+    assert np.array_equal(ids, ids2) and np.array_equal(coff, coff2) and np.array_equal(toff, toff2)
+
+
 def test_adversarial_long_segments(lib, merges_path, oracle):
     """Segments far longer than a tile: the whole-CTA path in the HBM workspace."""
     rng = np.random.default_rng(7)
