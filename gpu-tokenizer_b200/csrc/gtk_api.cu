@@ -133,6 +133,12 @@ struct gtk_tokenizer {
       d_chunk_cnt, d_unit_base, d_chunk_id_off, d_text_id_off, d_out_ids, d_seg_scratch, d_scan_sums, d_counters,
       d_totals;
   PinBuf h_ids, h_text_id_off, h_chunk_id_off, h_totals;
+  // small batches: input and results live in mapped page-locked memory, one kernel per call
+  uint8_t* small_in_h = nullptr;   // [text offsets | bytes]
+  uint8_t* small_in_d = nullptr;
+  uint8_t* small_out_h = nullptr;  // [totals | text id offsets | chunk id offsets | ids]
+  uint8_t* small_out_d = nullptr;
+  bool result_is_small = false;
   // sliced host path: copy streams and two slice arenas
   cudaStream_t in_stream = nullptr, out_stream = nullptr;
   SliceArena slice[4];
@@ -551,6 +557,64 @@ int encode_host_sliced(gtk_tokenizer* h, int mode, const uint8_t* bytes, const i
   return GTK_OK;
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Small host batches (latency mode): the text is copied into mapped page-locked memory, one
+// single-CTA kernel reads it over PCIe and writes ids and offsets straight back into mapped
+// memory; the call is one launch plus one stream synchronisation.
+// ------------------------------------------------------------------------------------------------
+constexpr size_t kSmallInOff    = 0;
+constexpr size_t kSmallInBytes  = ((size_t(gtk::kSmallMaxTexts) + 1) * 8 + 63) & ~size_t(63);
+constexpr size_t kSmallInSize   = kSmallInBytes + size_t(gtk::kSmallMaxBytes) + 64;
+constexpr int64_t kSmallChunkCap = gtk::kSmallMaxBytes + gtk::kSmallMaxTexts + 2;
+constexpr size_t kSmallOutTotals = 0;
+constexpr size_t kSmallOutText   = 64;
+constexpr size_t kSmallOutChunk  = kSmallOutText + (((size_t(gtk::kSmallMaxTexts) + 1) * 8 + 63) & ~size_t(63));
+constexpr size_t kSmallOutIds    = kSmallOutChunk + (((size_t(kSmallChunkCap) + 1) * 8 + 63) & ~size_t(63));
+constexpr size_t kSmallOutSize   = kSmallOutIds + size_t(gtk::kSmallMaxBytes) * 4 + 64;
+
+void small_path_init(gtk_tokenizer* h)
+{
+  void *ih = nullptr, *oh = nullptr, *id = nullptr, *od = nullptr;
+  GTK_CUDA(cudaHostAlloc(&ih, kSmallInSize, cudaHostAllocMapped));
+  GTK_CUDA(cudaHostAlloc(&oh, kSmallOutSize, cudaHostAllocMapped));
+  GTK_CUDA(cudaHostGetDevicePointer(&id, ih, 0));
+  GTK_CUDA(cudaHostGetDevicePointer(&od, oh, 0));
+  h->small_in_h = static_cast<uint8_t*>(ih);
+  h->small_out_h = static_cast<uint8_t*>(oh);
+  h->small_in_d = static_cast<uint8_t*>(id);
+  h->small_out_d = static_cast<uint8_t*>(od);
+}
+
+int encode_host_small(gtk_tokenizer* h, const uint8_t* bytes, const int64_t* text_offsets, int64_t n_texts,
+                      int64_t n_bytes, float* kernel_ms)
+{
+  std::memcpy(h->small_in_h + kSmallInOff, text_offsets, size_t(n_texts + 1) * 8);
+  std::memcpy(h->small_in_h + kSmallInBytes, bytes, size_t(n_bytes));
+  Plan p = plan_batch(h, h->small_in_d + kSmallInBytes, n_bytes,
+                      reinterpret_cast<const int64_t*>(h->small_in_d + kSmallInOff), n_texts,
+                      reinterpret_cast<int32_t*>(h->small_out_d + kSmallOutIds), gtk::kSmallMaxBytes,
+                      reinterpret_cast<int64_t*>(h->small_out_d + kSmallOutChunk), false);
+  p.b.text_id_off = reinterpret_cast<int64_t*>(h->small_out_d + kSmallOutText);
+  p.b.totals      = reinterpret_cast<int64_t*>(h->small_out_d + kSmallOutTotals);
+  cudaStream_t s = h->stream;
+  GTK_CUDA(cudaEventRecord(h->ev[1], s));
+  const int launches = gtk::launch_encode_small(p.b, h->dtab, s);
+  GTK_CUDA(cudaEventRecord(h->ev[2], s));
+  GTK_CUDA(cudaGetLastError());
+  GTK_CUDA(cudaStreamSynchronize(s));
+  const int64_t* tot = reinterpret_cast<const int64_t*>(h->small_out_h + kSmallOutTotals);
+  if (tot[2] != gtk::kStatusOk) return h->fail(GTK_ERR_KERNEL, status_text(int(tot[2])));
+  float ms = 0.f;
+  if (cudaEventElapsedTime(&ms, h->ev[1], h->ev[2]) == cudaSuccess) h->stage_ms[1] = h->stage_ms[4] = ms;
+  h->last_launches = launches;
+  h->result_is_small = true;
+  h->res_n_chunks = tot[0];
+  h->res_n_ids = tot[1];
+  if (kernel_ms) *kernel_ms = h->stage_ms[4];
+  return GTK_OK;
+}
+
 int validate_offsets(gtk_tokenizer* h, const int64_t* text_offsets, int64_t n_texts)
 {
   if (n_texts < 0) return h->fail(GTK_ERR_INVALID_ARG, "n_texts must be >= 0");
@@ -639,6 +703,7 @@ GTK_API int gtk_create(const char* merges_path, int chunk_tokens, int max_iters,
       h->opt_grid = h->sm_count * std::max(1, gtk::opt_kernel_max_blocks_per_sm());
       h->base_grid = h->sm_count * std::max(1, gtk::base_kernel_max_blocks_per_sm());
       h->h_totals.reserve(64);
+      small_path_init(h);
     }
     *out = h;
     return GTK_OK;
@@ -665,6 +730,8 @@ GTK_API void gtk_destroy(gtk_tokenizer* h)
                       &h->d_out_ids, &h->d_seg_scratch, &h->d_scan_sums, &h->d_counters, &h->d_totals})
       b->release();
     for (PinBuf* b : {&h->h_ids, &h->h_text_id_off, &h->h_chunk_id_off, &h->h_totals}) b->release();
+    if (h->small_in_h) cudaFreeHost(h->small_in_h);
+    if (h->small_out_h) cudaFreeHost(h->small_out_h);
     for (auto& sl : h->slice) sl.release();
     if (h->in_stream) cudaStreamDestroy(h->in_stream);
     if (h->out_stream) cudaStreamDestroy(h->out_stream);
@@ -760,6 +827,7 @@ GTK_API int gtk_encode(gtk_tokenizer* h, int mode, const uint8_t* bytes, const i
   if (int rc = validate_offsets(h, text_offsets, n_texts)) return rc;
   if (kernel_ms) *kernel_ms = 0.f;
   h->result_is_cpu = false;
+  h->result_is_small = false;
   h->res_n_ids = h->res_n_chunks = 0;
   h->res_n_texts = n_texts;
   h->last_launches = 0;
@@ -775,6 +843,8 @@ GTK_API int gtk_encode(gtk_tokenizer* h, int mode, const uint8_t* bytes, const i
       return GTK_OK;
     }
     if (!bytes) return h->fail(GTK_ERR_INVALID_ARG, "bytes is null");
+    if (mode == GTK_MODE_OPT && n_bytes <= gtk::kSmallMaxBytes && n_texts <= gtk::kSmallMaxTexts)
+      return encode_host_small(h, bytes, text_offsets, n_texts, n_bytes, kernel_ms);
     if (n_bytes >= kSliceThresholdBytes) return encode_host_sliced(h, mode, bytes, text_offsets, n_texts, n_bytes, kernel_ms);
     cudaStream_t s = h->stream;
     h->d_bytes.reserve(size_t(n_bytes) + 32);
@@ -839,6 +909,7 @@ GTK_API int gtk_encode_cpu(gtk_tokenizer* h, int rule, const uint8_t* bytes, con
     h->cpu_text_off.push_back(int64_t(h->cpu_ids.size()));
   }
   h->result_is_cpu = true;
+  h->result_is_small = false;
   h->res_n_ids = int64_t(h->cpu_ids.size());
   h->res_n_chunks = int64_t(h->cpu_chunk_off.size()) - 1;
   h->res_n_texts = n_texts;
@@ -862,6 +933,10 @@ GTK_API int gtk_result_view(const gtk_tokenizer* h, const int32_t** ids, const i
     if (ids) *ids = h->cpu_ids.data();
     if (text_id_offsets) *text_id_offsets = h->cpu_text_off.data();
     if (chunk_id_offsets) *chunk_id_offsets = h->cpu_chunk_off.data();
+  } else if (h->result_is_small) {
+    if (ids) *ids = reinterpret_cast<const int32_t*>(h->small_out_h + kSmallOutIds);
+    if (text_id_offsets) *text_id_offsets = reinterpret_cast<const int64_t*>(h->small_out_h + kSmallOutText);
+    if (chunk_id_offsets) *chunk_id_offsets = reinterpret_cast<const int64_t*>(h->small_out_h + kSmallOutChunk);
   } else {
     if (ids) *ids = h->h_ids.as<int32_t>();
     if (text_id_offsets) *text_id_offsets = h->h_text_id_off.as<int64_t>();

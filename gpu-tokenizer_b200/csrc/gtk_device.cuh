@@ -84,6 +84,10 @@ int launch_merge_opt(const EncodeBuffers& b, const DeviceTable& t, int grid, cud
 int launch_merge_base(const EncodeBuffers& b, const DeviceTable& t, int grid, cudaStream_t stream);
 int launch_output_scans(const EncodeBuffers& b, int mode_base, cudaStream_t stream);
 int launch_pack(const EncodeBuffers& b, int mode_base, int grid, cudaStream_t stream);
+// Whole pipeline in one single-CTA kernel for small batches; totals[0..2] receive n_chunks, n_ids, status.
+int launch_encode_small(const EncodeBuffers& b, const DeviceTable& t, cudaStream_t stream);
+constexpr int64_t kSmallMaxBytes = 32768;
+constexpr int64_t kSmallMaxTexts = 1024;
 // What the allocation-free entry point needs from a handle (defined in gtk_api.cu).
 struct HandleView {
   int device;

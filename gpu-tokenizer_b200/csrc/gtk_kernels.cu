@@ -548,38 +548,41 @@ __device__ __forceinline__ int next_cut(const uint32_t* cut, int s)
   return w * 32 + __ffs(int(x)) - 1;
 }
 
-__global__ void __launch_bounds__(kOptThreads) k_merge_opt(EncodeBuffers b, DeviceTable T)
+// Per-CTA set-up shared by the kernels that process tiles: never-merge bitmap into shared memory and
+// the all-ones sentinel words behind the segment-start bitmap.
+__device__ __forceinline__ void opt_tile_setup(OptSmem& S, const DeviceTable& T)
 {
-  __shared__ OptSmem S;
+  for (int i = threadIdx.x; i < 2048; i += kOptThreads) S.adj[i] = T.adj[i];
+  if (threadIdx.x < 2) S.cut[kCutWords + threadIdx.x] = 0xFFFFFFFFu;
+}
+
+// Reset of the per-tile words; call by one thread, then __syncthreads().
+__device__ __forceinline__ void opt_tile_reset(OptSmem& S)
+{
+  S.nlong       = 0;
+  S.seg_next    = 0;
+  S.nmiss       = 0;
+  S.first_start = kWindow;
+  S.last_start  = -1;
+  S.over_start  = -1;
+  S.over_len    = 0;
+}
+
+// One tile of the byte stream: tokenises every segment that starts in bytes [k*kTile, (k+1)*kTile),
+// writes the tokens compacted to staging, the unit record and the per-chunk counts.
+__device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, const DeviceTable& T, int64_t k,
+                                         int64_t C)
+{
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t lt = lanemask_lt();
   const int64_t n   = b.n_bytes;
-  const int64_t C   = b.totals[0];
   int* status       = b.counters + 1;
-
-  for (int i = tid; i < 2048; i += kOptThreads) S.adj[i] = T.adj[i];
-  if (tid < 2) S.cut[kCutWords + tid] = 0xFFFFFFFFu;
   const bool aligned = (reinterpret_cast<uintptr_t>(b.bytes) & 15u) == 0;
   const bool identity_ids = T.byte_ids_identity != 0;
-
-  for (;;) {
-    __syncthreads();
-    if (tid == 0) {
-      S.ticket      = atomicAdd(b.counters + 0, 1);
-      S.nlong       = 0;
-      S.seg_next    = 0;
-      S.nmiss       = 0;
-      S.first_start = kWindow;
-      S.last_start  = -1;
-      S.over_start  = -1;
-      S.over_len    = 0;
-    }
-    __syncthreads();
-    const int64_t k = S.ticket;
-    if (k >= b.n_tiles) break;
 #ifdef GTK_PHASE_TIMING
-    long long phase_t0 = clock64();
+  long long phase_t0 = clock64();
 #endif
+  {
     const int64_t lo = k * kTile;
     const int wlen   = int(min(int64_t(kWindow), n - lo));
     const int own    = int(min(int64_t(kTile), n - lo));
@@ -933,6 +936,112 @@ __global__ void __launch_bounds__(kOptThreads) k_merge_opt(EncodeBuffers b, Devi
   }
 }
 
+__global__ void __launch_bounds__(kOptThreads) k_merge_opt(EncodeBuffers b, DeviceTable T)
+{
+  __shared__ OptSmem S;
+  const int tid   = threadIdx.x;
+  const int64_t C = b.totals[0];
+  opt_tile_setup(S, T);
+  for (;;) {
+    __syncthreads();
+    if (tid == 0) {
+      S.ticket = atomicAdd(b.counters + 0, 1);
+      opt_tile_reset(S);
+    }
+    __syncthreads();
+    const int64_t k = S.ticket;
+    if (k >= b.n_tiles) break;
+    opt_tile(S, b, T, k, C);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// small batches (latency mode): ONE kernel, one CTA, does the chunker, every tile, the output
+// scans and the pack.  Input and output pointers may be mapped host memory, so a call is one
+// launch and one stream synchronisation.
+// ------------------------------------------------------------------------------------------------
+
+// single-CTA exclusive scan of f(0..n) into out[0..n] (int64); returns the total to every thread
+template <class F>
+__device__ int64_t cta_exclusive_scan(F f, int64_t n, int64_t* out, int* scanbuf, int64_t* carry_s)
+{
+  if (threadIdx.x == 0) *carry_s = 0;
+  __syncthreads();
+  for (int64_t base = 0; base < n; base += kOptThreads) {
+    const int64_t i = base + threadIdx.x;
+    const int v     = (i < n) ? int(f(i)) : 0;
+    int total;
+    const int off       = block_exclusive_scan(v, scanbuf, &total);
+    const int64_t carry = *carry_s;
+    if (i < n) out[i] = carry + off;
+    __syncthreads();
+    if (threadIdx.x == 0) *carry_s = carry + total;
+    __syncthreads();
+  }
+  const int64_t total = *carry_s;
+  if (threadIdx.x == 0) out[n] = total;
+  __syncthreads();
+  return total;
+}
+
+__global__ void __launch_bounds__(kOptThreads) k_encode_small(EncodeBuffers b, DeviceTable T)
+{
+  __shared__ OptSmem S;
+  __shared__ int64_t carry_s;
+  const int tid = threadIdx.x;
+  opt_tile_setup(S, T);
+  if (tid < 4) b.counters[tid] = 0;
+  // chunker: chunks per text -> offsets of every chunk -> first chunk of every tile
+  const int64_t C = cta_exclusive_scan(ChunksPerText{b.text_off, b.chunk_bytes}, b.n_texts, b.text_chunk_base,
+                                       S.scanbuf, &carry_s);
+  for (int64_t c = tid; c <= C; c += kOptThreads) {
+    if (c < C) b.chunk_cnt[c] = 0;
+    if (c == C) {
+      b.chunk_off[c] = b.text_off[b.n_texts];
+      continue;
+    }
+    int64_t lo = 0, hi = b.n_texts;
+    while (hi - lo > 1) {
+      const int64_t mid = (lo + hi) >> 1;
+      if (b.text_chunk_base[mid] <= c) lo = mid; else hi = mid;
+    }
+    b.chunk_off[c] = b.text_off[lo] + (c - b.text_chunk_base[lo]) * int64_t(b.chunk_bytes);
+  }
+  __syncthreads();
+  for (int64_t k = tid; k < b.n_tiles; k += kOptThreads) {
+    const int64_t pos = k * kTile;
+    int64_t lo = 0, hi = C;
+    while (hi - lo > 1) {
+      const int64_t mid = (lo + hi) >> 1;
+      if (b.chunk_off[mid] <= pos) lo = mid; else hi = mid;
+    }
+    b.tile_chunk0[k] = int32_t(lo);
+  }
+  // tiles, one after the other
+  for (int64_t k = 0; k < b.n_tiles; ++k) {
+    __syncthreads();
+    if (tid == 0) opt_tile_reset(S);
+    __syncthreads();
+    opt_tile(S, b, T, k, C);
+  }
+  __syncthreads();
+  // output: offsets of units, chunks and texts, then the packed ids
+  cta_exclusive_scan(CountsI32{b.unit_cnt}, b.n_tiles, b.unit_base, S.scanbuf, &carry_s);
+  const int64_t N = cta_exclusive_scan(CountsI32{b.chunk_cnt}, C, b.chunk_id_off, S.scanbuf, &carry_s);
+  for (int64_t t = tid; t <= b.n_texts; t += kOptThreads) b.text_id_off[t] = b.chunk_id_off[b.text_chunk_base[t]];
+  for (int64_t u = 0; u < b.n_tiles; ++u) {
+    const int64_t src = b.unit_first[u], dst = b.unit_base[u];
+    const int m       = b.unit_cnt[u];
+    for (int j = tid; j < m; j += kOptThreads)
+      if (dst + j < b.out_capacity) b.out_ids[dst + j] = int32_t(b.staging[src + j]);
+  }
+  if (tid == 0) {
+    b.totals[0] = C;
+    b.totals[1] = N;
+    b.totals[2] = int64_t(b.counters[1]);
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 // merge kernel, one CTA per chunk ("base")
 // ------------------------------------------------------------------------------------------------
@@ -1076,6 +1185,12 @@ int launch_pack(const EncodeBuffers& b, int mode_base, int grid, cudaStream_t st
     k_pack<<<grid, 256, 0, stream>>>(b.staging, b.unit_first, b.unit_cnt, b.unit_base, b.n_tiles, nullptr, b.out_ids,
                                      b.out_capacity);
   }
+  return 1;
+}
+
+int launch_encode_small(const EncodeBuffers& b, const DeviceTable& t, cudaStream_t stream)
+{
+  k_encode_small<<<1, kOptThreads, 0, stream>>>(b, t);
   return 1;
 }
 
