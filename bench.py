@@ -360,15 +360,25 @@ def main() -> None:
     # ---- latency mode (cfg3 only): one call per string, host in / host out ----
     latency = None
     if args.workload == "cfg3" and rank == 0:
-        lat = []
+        import ctypes
+        lat, kern, raw = [], [], []
+        one = np.array([0, 512], dtype=np.int64)
+        ms = ctypes.c_float()
         for i in range(min(args.latency_calls, n_texts)):
             s = pin.array[text_off[i]:text_off[i + 1]]
             t1 = time.perf_counter()
-            tok.encode(s, None, mode=mode, copy=False)
+            _, _, _, k_ms = tok.encode(s, None, mode=mode, copy=False)   # the Python call a user makes
             lat.append((time.perf_counter() - t1) * 1e6)
-        lat = np.array(lat[10:])
+            kern.append(k_ms * 1e3)
+            t1 = time.perf_counter()                                      # the C ABI call alone
+            tok._lib.gtk_encode(tok._h, int(mode), s.ctypes.data, one.ctypes.data, 1, ctypes.byref(ms))
+            raw.append((time.perf_counter() - t1) * 1e6)
+        lat, kern, raw = np.array(lat[10:]), np.array(kern[10:]), np.array(raw[10:])
         latency = {"p50_us": float(np.percentile(lat, 50)), "p99_us": float(np.percentile(lat, 99)),
-                   "calls": int(len(lat)), "bytes_per_call": 512}
+                   "c_abi_p50_us": float(np.percentile(raw, 50)), "c_abi_p99_us": float(np.percentile(raw, 99)),
+                   "kernel_p50_us": float(np.percentile(kern, 50)),
+                   "calls": int(len(lat)), "bytes_per_call": 512,
+                   "note": "host bytes in, ids on the host out; p50/p99 through Python ctypes, c_abi = gtk_encode alone"}
 
     if rank == 0:
         peak, peak_kind = measured_hbm_peak()

@@ -129,6 +129,7 @@ struct gtk_tokenizer {
   gtk::DeviceTable dtab{};
 
   // arenas
+  DevBuf d_q_short, d_q_long, d_q_huge;  // split pipeline queues (shared by all slices: kernels of one stream)
   DevBuf d_bytes, d_text_off, d_text_chunk_base, d_chunk_off, d_tile_chunk0, d_staging, d_unit_first, d_unit_cnt,
       d_chunk_cnt, d_unit_base, d_chunk_id_off, d_text_id_off, d_out_ids, d_seg_scratch, d_scan_sums, d_counters,
       d_totals;
@@ -199,6 +200,29 @@ int64_t chunk_upper_bound(int64_t n_bytes, int64_t n_texts, int chunk_tokens)
   return n_bytes / chunk_tokens + n_texts + 1;
 }
 
+// Batches of at least this many tiles take the split pipeline (queues + separate merge kernels);
+// smaller ones run the single tile kernel, whose per-tile barriers do not matter at that size.
+constexpr int64_t kSplitMinTiles = 1024;
+
+bool use_split(const gtk::EncodeBuffers& b, int mode) { return mode == GTK_MODE_OPT && b.q_short != nullptr; }
+
+void attach_queues(gtk_tokenizer* h, gtk::EncodeBuffers& b, int64_t reserve_bytes)
+{
+  if (b.n_tiles < kSplitMinTiles) return;
+  const int64_t n = std::max(reserve_bytes, b.n_bytes);
+  const int64_t cap_short = std::min<int64_t>(n / 8 + 4096, (int64_t(1) << 31) - (int64_t(1) << 24));
+  const int64_t cap_long = n / 33 + 1024, cap_huge = n / (gtk::kLongSegMax + 1) + 16;
+  h->d_q_short.reserve(size_t(cap_short) * 48);
+  h->d_q_long.reserve(size_t(cap_long) * 8);
+  h->d_q_huge.reserve(size_t(cap_huge) * 16);
+  b.q_short = h->d_q_short.as<uint4>();
+  b.q_long = h->d_q_long.as<unsigned long long>();
+  b.q_huge = h->d_q_huge.as<unsigned long long>();
+  b.q_short_cap = cap_short;
+  b.q_long_cap = cap_long;
+  b.q_huge_cap = cap_huge;
+}
+
 struct Plan {
   gtk::EncodeBuffers b{};
   int64_t chunk_cap = 0;
@@ -262,6 +286,7 @@ Plan plan_batch(gtk_tokenizer* h, const uint8_t* d_bytes, int64_t n_bytes, const
   b.scan_block_sums = h->d_scan_sums.as<int64_t>();
   b.counters = h->d_counters.as<int32_t>();
   b.totals = h->d_totals.as<int64_t>();
+  attach_queues(h, b, 0);
   return p;
 }
 
@@ -288,6 +313,7 @@ void run_front(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* lau
   *launches += gtk::launch_chunker(b, s);
   GTK_CUDA(cudaEventRecord(ev[1], s));
   if (mode == GTK_MODE_BASE) *launches += gtk::launch_merge_base(b, h->dtab, h->base_grid, s);
+  else if (use_split(b, mode)) *launches += gtk::launch_merge_split(b, h->dtab, h->sm_count, h->opt_grid, s);
   else *launches += gtk::launch_merge_opt(b, h->dtab, h->opt_grid, s);
   GTK_CUDA(cudaEventRecord(ev[2], s));
   *launches += gtk::launch_output_scans(b, mode == GTK_MODE_BASE, s);
@@ -303,7 +329,8 @@ void run_pack(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* laun
   cudaStream_t s = h->stream;
   if (!ev) ev = h->ev;
   GTK_CUDA(cudaEventRecord(ev[5], s));
-  *launches += gtk::launch_pack(b, mode == GTK_MODE_BASE, h->sm_count * 8, s);
+  if (use_split(b, mode)) *launches += gtk::launch_pack_split(b, h->sm_count * 8, s);
+  else *launches += gtk::launch_pack(b, mode == GTK_MODE_BASE, h->sm_count * 8, s);
   GTK_CUDA(cudaEventRecord(ev[4], s));
   GTK_CUDA(cudaGetLastError());
 }
@@ -401,12 +428,17 @@ void slice_arena_prepare(gtk_tokenizer* h, SliceArena& a, int64_t max_bytes, int
     if (!*e) GTK_CUDA(cudaEventCreateWithFlags(e, cudaEventDisableTiming));
 }
 
-gtk::EncodeBuffers slice_buffers(gtk_tokenizer* h, SliceArena& a, const SlicePlan& sp)
+// Device offset of slice i inside the batch-wide byte / staging / id buffers: 16-element aligned
+// (vector loads) and spaced so that neighbouring slices never share an element.
+inline int64_t slice_dev_offset(const SlicePlan& sp, int index) { return (sp.byte_lo + 16 * int64_t(index) + 15) & ~int64_t(15); }
+
+gtk::EncodeBuffers slice_buffers(gtk_tokenizer* h, SliceArena& a, const SlicePlan& sp, int index, int64_t max_bytes)
 {
   gtk::EncodeBuffers b{};
+  const int64_t dev_off = slice_dev_offset(sp, index);
   const int64_t n_bytes = sp.byte_hi - sp.byte_lo;
   const int64_t pieces  = int64_t(sp.piece_off.size()) - 1;
-  b.bytes = h->d_bytes.as<uint8_t>() + sp.byte_lo;
+  b.bytes = h->d_bytes.as<uint8_t>() + dev_off;
   b.n_bytes = n_bytes;
   b.text_off = a.text_off.as<int64_t>();
   b.n_texts = pieces;
@@ -416,14 +448,14 @@ gtk::EncodeBuffers slice_buffers(gtk_tokenizer* h, SliceArena& a, const SlicePla
   b.chunk_cap = chunk_upper_bound(n_bytes, pieces, h->chunk_tokens);
   b.tile_chunk0 = a.tile_chunk0.as<int32_t>();
   b.n_tiles = (n_bytes + gtk::kTile - 1) / gtk::kTile;
-  b.staging = h->d_staging.as<uint16_t>() + sp.byte_lo;
+  b.staging = h->d_staging.as<uint16_t>() + dev_off;
   b.unit_first = a.unit_first.as<int64_t>();
   b.unit_cnt = a.unit_cnt.as<int32_t>();
   b.chunk_cnt = a.chunk_cnt.as<int32_t>();
   b.unit_base = a.unit_base.as<int64_t>();
   b.chunk_id_off = a.chunk_id_off.as<int64_t>();
   b.text_id_off = a.text_id_off.as<int64_t>();
-  b.out_ids = h->d_out_ids.as<int32_t>() + sp.byte_lo;  // worst case one id per byte: slices never overlap
+  b.out_ids = h->d_out_ids.as<int32_t>() + dev_off;  // worst case one id per byte: slices never overlap
   b.out_capacity = n_bytes;
   const int64_t longest = std::min<int64_t>(h->chunk_tokens, n_bytes);
   const int64_t scratch_tokens = longest > gtk::kHalo ? ((longest + 63) & ~int64_t(63)) : 0;
@@ -432,6 +464,7 @@ gtk::EncodeBuffers slice_buffers(gtk_tokenizer* h, SliceArena& a, const SlicePla
   b.scan_block_sums = a.scan_sums.as<int64_t>();
   b.counters = a.counters.as<int32_t>();
   b.totals = a.totals.as<int64_t>();
+  attach_queues(h, b, max_bytes);
   return b;
 }
 
@@ -448,9 +481,10 @@ int encode_host_sliced(gtk_tokenizer* h, int mode, const uint8_t* bytes, const i
     total_pieces += int64_t(sp.piece_off.size()) - 1;
   }
   // everything is sized before the first copy is issued: nothing may be reallocated in flight
-  h->d_bytes.reserve(size_t(n_bytes) + 32);
-  h->d_staging.reserve(size_t(n_bytes + 16) * 2);
-  h->d_out_ids.reserve(size_t(n_bytes) * 4 + 64);
+  const size_t span = size_t(n_bytes) + 16 * size_t(ns) + 64;  // slices sit at 16-aligned, disjoint offsets
+  h->d_bytes.reserve(span);
+  h->d_staging.reserve(span * 2);
+  h->d_out_ids.reserve(span * 4);
   {
     const int64_t longest = std::min<int64_t>(h->chunk_tokens, max_bytes);
     if (longest > gtk::kHalo)
@@ -476,14 +510,14 @@ int encode_host_sliced(gtk_tokenizer* h, int mode, const uint8_t* bytes, const i
     const SlicePlan& sp = slices[size_t(i)];
     const int64_t pieces = int64_t(sp.piece_off.size()) - 1;
     std::memcpy(a.h_piece_off.p, sp.piece_off.data(), size_t(pieces + 1) * 8);
-    GTK_CUDA(cudaMemcpyAsync(h->d_bytes.as<uint8_t>() + sp.byte_lo, bytes + sp.byte_lo, size_t(sp.byte_hi - sp.byte_lo),
+    GTK_CUDA(cudaMemcpyAsync(h->d_bytes.as<uint8_t>() + slice_dev_offset(sp, i), bytes + sp.byte_lo, size_t(sp.byte_hi - sp.byte_lo),
                              cudaMemcpyHostToDevice, h->in_stream));
     GTK_CUDA(cudaMemcpyAsync(a.text_off.p, a.h_piece_off.p, size_t(pieces + 1) * 8, cudaMemcpyHostToDevice,
                              h->in_stream));
     GTK_CUDA(cudaEventRecord(a.ev_in, h->in_stream));
     GTK_CUDA(cudaStreamWaitEvent(h->stream, a.ev_in, 0));
     if (i >= kSliceArenas) GTK_CUDA(cudaStreamWaitEvent(h->stream, a.ev_out, 0));  // its previous slice has left this arena
-    bufs[size_t(i)] = slice_buffers(h, a, sp);
+    bufs[size_t(i)] = slice_buffers(h, a, sp, i, max_bytes);
     run_front(h, bufs[size_t(i)], mode, &launches, a.ev, a.h_totals.as<int64_t>());
     GTK_CUDA(cudaEventRecord(a.ev_front, h->stream));
   };
@@ -597,6 +631,8 @@ int encode_host_small(gtk_tokenizer* h, const uint8_t* bytes, const int64_t* tex
                       reinterpret_cast<int64_t*>(h->small_out_d + kSmallOutChunk), false);
   p.b.text_id_off = reinterpret_cast<int64_t*>(h->small_out_d + kSmallOutText);
   p.b.totals      = reinterpret_cast<int64_t*>(h->small_out_d + kSmallOutTotals);
+  h->d_text_off.reserve((size_t(gtk::kSmallMaxTexts) + 1) * 8);
+  p.b.text_off_copy = h->d_text_off.as<int64_t>();
   cudaStream_t s = h->stream;
   GTK_CUDA(cudaEventRecord(h->ev[1], s));
   const int launches = gtk::launch_encode_small(p.b, h->dtab, s);
@@ -724,7 +760,7 @@ GTK_API void gtk_destroy(gtk_tokenizer* h)
   if (h->device >= 0) {
     cudaSetDevice(h->device);
     if (h->stream) cudaStreamSynchronize(h->stream);
-    for (DevBuf* b : {&h->d_slots, &h->d_bpr, &h->d_mor, &h->d_sor, &h->d_adj, &h->d_b2i, &h->d_words, &h->d_bytes, &h->d_text_off,
+    for (DevBuf* b : {&h->d_slots, &h->d_bpr, &h->d_mor, &h->d_sor, &h->d_adj, &h->d_b2i, &h->d_words, &h->d_q_short, &h->d_q_long, &h->d_q_huge, &h->d_bytes, &h->d_text_off,
                       &h->d_text_chunk_base, &h->d_chunk_off, &h->d_tile_chunk0, &h->d_staging, &h->d_unit_first,
                       &h->d_unit_cnt, &h->d_chunk_cnt, &h->d_unit_base, &h->d_chunk_id_off, &h->d_text_id_off,
                       &h->d_out_ids, &h->d_seg_scratch, &h->d_scan_sums, &h->d_counters, &h->d_totals})

@@ -20,6 +20,8 @@
 // by shared-memory and issue throughput, so there is no tensor-core code.
 #include "gtk_device.cuh"
 
+#include <algorithm>
+
 namespace gtk {
 namespace {
 
@@ -532,7 +534,7 @@ struct OptSmem {
   GroupScratch gs;
   int scanbuf[33];
   int ticket;
-  int nseg, nlong, seg_next, nmiss;
+  int nseg, nlong, seg_next, nmiss, qbase;
   int first_start, last_start, over_start;
   int over_len;
   long long over_end;
@@ -570,6 +572,7 @@ __device__ __forceinline__ void opt_tile_reset(OptSmem& S)
 
 // One tile of the byte stream: tokenises every segment that starts in bytes [k*kTile, (k+1)*kTile),
 // writes the tokens compacted to staging, the unit record and the per-chunk counts.
+template <bool SPLIT>
 __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, const DeviceTable& T, int64_t k,
                                          int64_t C)
 {
@@ -766,9 +769,41 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
       atomicAdd(&g_phase_cycles[11], (unsigned long long)S.nseg);
     }
 #endif
-    // ---- E. short segments: every lane pulls segments from a CTA-wide queue and does one merge
-    //         step per loop trip, so a lane that finishes early takes new work instead of idling ----
-    {
+    // ---- E. short segments that missed the lookup.  Split mode: hand them to the batch-wide queue
+    //         (one reservation per tile).  Otherwise, or if the queue is full: every lane pulls
+    //         segments from a CTA-wide list and does one merge step per loop trip ----
+    bool queued = false;
+    if (SPLIT) {
+      const int nm = S.nmiss;
+      if (tid == 0) S.qbase = (nm > 0) ? atomicAdd(b.counters + 4, nm) : 0;
+      __syncthreads();
+      const int64_t qb = S.qbase;
+      queued           = qb + nm <= b.q_short_cap;
+      for (int j = tid; j < nm; j += kOptThreads) {
+        if (qb + j >= b.q_short_cap) continue;  // a reservation that does not fit is filled with null entries
+        uint4* e = b.q_short + 3 * (qb + j);
+        if (!queued) {
+          e[0] = make_uint4(0, 0, 0, 0);
+          continue;
+        }
+        const uint32_t ent = S.seg[j];
+        const int ss       = int(ent & 0xFFFFu);
+        const unsigned long long head = (unsigned long long)(lo + ss) | ((unsigned long long)(ent >> 16) << 48);
+        // the segment's bytes travel with the entry, so the consumer needs one contiguous read
+        const int at       = 16 + ss;
+        const uint32_t* wp = reinterpret_cast<const uint32_t*>(&S.bytes[at & ~3]);
+        const uint32_t sh  = uint32_t(at & 3) * 8u;
+        uint32_t w[9];
+#pragma unroll
+        for (int q = 0; q < 9; ++q) w[q] = wp[q];
+        e[0] = make_uint4(uint32_t(head), uint32_t(head >> 32), __funnelshift_r(w[0], w[1], sh),
+                          __funnelshift_r(w[1], w[2], sh));
+        e[1] = make_uint4(__funnelshift_r(w[2], w[3], sh), __funnelshift_r(w[3], w[4], sh),
+                          __funnelshift_r(w[4], w[5], sh), __funnelshift_r(w[5], w[6], sh));
+        e[2] = make_uint4(__funnelshift_r(w[6], w[7], sh), __funnelshift_r(w[7], w[8], sh), 0u, 0u);
+      }
+    }
+    if (!queued) {
       const int nseg   = S.nmiss;
       int s            = -1, L = 0;
       uint32_t alive   = 0;
@@ -798,6 +833,76 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
       }
     }
     __syncthreads();
+
+    if (SPLIT) {
+      // ---- split mode: long segments go to their queues, the tile stores its tokens position by
+      //      position (tombstones included); counting and packing happen in later kernels ----
+      const int nl = min(S.nlong, kLongCap);
+      for (int q = tid; q < nl; q += kOptThreads) {
+        const int ss = S.longq[q];
+        const int LL = next_cut(S.cut, ss) - ss;
+        if (LL <= kLongSegMax) {
+          const int64_t at = atomicAdd(b.counters + 5, 1);
+          if (at < b.q_long_cap) b.q_long[at] = (unsigned long long)(lo + ss) | ((unsigned long long)LL << 48);
+          else atomicMax(status, int(kStatusLongQueueOverflow));
+        } else {
+          const int64_t at = atomicAdd(b.counters + 6, 1);
+          if (at < b.q_huge_cap) {
+            b.q_huge[2 * at]     = (unsigned long long)(lo + ss);
+            b.q_huge[2 * at + 1] = (unsigned long long)LL;
+          } else atomicMax(status, int(kStatusLongQueueOverflow));
+        }
+      }
+      if (S.over_start >= 0) {  // CTA-uniform: the segment that runs past the window
+        const int64_t gs0 = lo + S.over_start;
+        if (tid == 0) {
+          int64_t c = b.tile_chunk0[k];
+          while (c + 1 < C && b.chunk_off[c + 1] <= gs0) ++c;
+          S.over_end = b.chunk_off[c + 1];
+        }
+        __syncthreads();
+        const int64_t cend = S.over_end;
+        int64_t ge         = cend;
+        for (int64_t pos = lo + kWindow; pos < cend; pos += kOptThreads) {
+          const int64_t p = pos + tid;
+          const bool cutp = (p < cend) && !adj_bit(S.adj, b.bytes[p - 1], b.bytes[p]);
+          if (__syncthreads_or(cutp)) {
+            if (cutp) atomicMin(reinterpret_cast<unsigned long long*>(&S.over_end), (unsigned long long)p);
+            __syncthreads();
+            ge = S.over_end;
+            break;
+          }
+        }
+        if (tid == 0) {
+          const int64_t LL = ge - gs0;
+          if (LL <= kLongSegMax) {
+            const int64_t at = atomicAdd(b.counters + 5, 1);
+            if (at < b.q_long_cap) b.q_long[at] = (unsigned long long)gs0 | ((unsigned long long)LL << 48);
+            else atomicMax(status, int(kStatusLongQueueOverflow));
+          } else {
+            const int64_t at = atomicAdd(b.counters + 6, 1);
+            if (at < b.q_huge_cap) {
+              b.q_huge[2 * at]     = (unsigned long long)gs0;
+              b.q_huge[2 * at + 1] = (unsigned long long)LL;
+            } else atomicMax(status, int(kStatusLongQueueOverflow));
+          }
+        }
+      }
+      const int first = S.first_start;
+      int end_owned   = 0;
+      if (S.last_start >= 0) end_owned = (S.over_start >= 0) ? S.over_start : next_cut(S.cut, S.last_start);
+      if (end_owned > wlen) end_owned = wlen;
+      for (int g = tid; g < kWindow / 4; g += kOptThreads) {
+        const int i0 = g * 4;
+        if (i0 + 4 <= first || i0 >= end_owned) continue;
+        if (i0 >= first && i0 + 4 <= end_owned) {
+          *reinterpret_cast<uint2*>(b.staging + lo + i0) = *reinterpret_cast<const uint2*>(&S.tok[i0]);
+        } else {
+          for (int i = max(i0, first); i < min(i0 + 4, end_owned); ++i) b.staging[lo + i] = S.tok[i];
+        }
+      }
+      return;
+    }
 
     GTK_PHASE(4);
     // ---- F. one warp per long segment ----
@@ -951,7 +1056,318 @@ __global__ void __launch_bounds__(kOptThreads) k_merge_opt(EncodeBuffers b, Devi
     __syncthreads();
     const int64_t k = S.ticket;
     if (k >= b.n_tiles) break;
-    opt_tile(S, b, T, k, C);
+    opt_tile<false>(S, b, T, k, C);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// split pipeline, stage 1: the tile kernel in split mode (lookup + queues + positional store)
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kOptThreads) k_front_split(EncodeBuffers b, DeviceTable T)
+{
+  __shared__ OptSmem S;
+  const int tid   = threadIdx.x;
+  const int64_t C = b.totals[0];
+  opt_tile_setup(S, T);
+  for (;;) {
+    __syncthreads();
+    if (tid == 0) {
+      S.ticket = atomicAdd(b.counters + 0, 1);
+      opt_tile_reset(S);
+    }
+    __syncthreads();
+    const int64_t k = S.ticket;
+    if (k >= b.n_tiles) break;
+    opt_tile<true>(S, b, T, k, C);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// split pipeline, stage 2: one thread per queued short segment (2..32 bytes).  No CTA barrier:
+// a warp reserves 256 queue entries at a time, its lanes take the next entry whenever they finish
+// one, so a long merge chain delays nobody but its own lane.  Tokens and ranks of a lane live in
+// shared memory, interleaved by lane so that lanes working on the same index hit different banks.
+// ------------------------------------------------------------------------------------------------
+constexpr int kShortThreads = 256;
+constexpr int kShortBatch   = 256;  // queue entries a warp reserves with one global atomic
+
+struct LaneArrays {  // view of one lane's 32 tokens / ranks inside the interleaved arrays
+  uint16_t* base;
+  __device__ __forceinline__ uint16_t& operator[](int i) const { return base[i * kShortThreads]; }
+};
+
+__device__ __forceinline__ bool lane_merge_step(LaneArrays tok, LaneArrays rk, int L, uint32_t& alive,
+                                                const DeviceTable& T)
+{
+  if ((alive & (alive - 1u)) == 0u) return false;
+  uint32_t best = 0xFFFFFFFFu;
+  for (int i = 0; i < L - 1; ++i) best = min(best, (uint32_t(rk[i]) << 16) | uint32_t(i));
+  const uint32_t r = best >> 16;
+  if (r >= SEL) return false;
+  const int j = int(best & 0xFFFFu);
+  const int q = j + __ffs(int(alive >> (j + 1)));
+  const uint32_t c = merged_id(T, r);
+  tok[j] = uint16_t(c);
+  tok[q] = uint16_t(DEAD);
+  rk[q]  = uint16_t(NONE);
+  alive &= ~(1u << q);
+  const uint32_t right = (q >= 31) ? 0u : (alive >> (q + 1));
+  uint32_t rr          = NONE;
+  if (right) rr = probe_rank(T, c, tok[q + __ffs(int(right))]);
+  rk[j] = uint16_t(rr);
+  const uint32_t left = alive & ((1u << j) - 1u);
+  if (left) {
+    const int p = 31 - __clz(int(left));
+    rk[p]       = uint16_t(probe_rank(T, tok[p], c));
+  }
+  return true;
+}
+
+__global__ void __launch_bounds__(kShortThreads) k_merge_short(EncodeBuffers b, DeviceTable T)
+{
+  __shared__ uint16_t s_tok[32 * kShortThreads];
+  __shared__ uint16_t s_rk[32 * kShortThreads];
+  const int tid = threadIdx.x, lane = tid & 31;
+  const uint32_t lt = lanemask_lt();
+  const int64_t count = min(int64_t(b.counters[4]), b.q_short_cap);
+  const LaneArrays tok{s_tok + tid}, rk{s_rk + tid};
+  const bool identity_ids = T.byte_ids_identity != 0;
+  int64_t batch_next = 0, batch_end = 0;  // warp-uniform cursor over the reserved queue range
+  int64_t pos = -1;
+  int L = 0;
+  uint32_t alive = 0;
+  bool drained = false;
+  for (;;) {
+    // lanes without a segment take the next queue entry (bytes travel with the entry) and set up
+    // their token and rank arrays; the entries the warp will take next are prefetched into L1
+    const bool need   = (pos < 0) && !drained;
+    const uint32_t nb = __ballot_sync(0xFFFFFFFFu, need);
+    if (nb) {
+      const int want = __popc(nb);
+      if (batch_next >= batch_end) {  // reserve a new range for the warp
+        long long base = 0;
+        if (lane == 0) base = (long long)atomicAdd(reinterpret_cast<unsigned long long*>(b.counters + 12),
+                                                   (unsigned long long)kShortBatch);
+        base       = __shfl_sync(0xFFFFFFFFu, base, 0);
+        batch_next = base;
+        batch_end  = min(int64_t(base) + kShortBatch, count);
+      }
+      if (need) {
+        const int64_t j = batch_next + __popc(nb & lt);
+        if (j < batch_end) {
+          const uint4* e = b.q_short + 3 * j;
+          if (j + want < batch_end) asm volatile("prefetch.global.L1 [%0];" ::"l"(e + 3 * want));
+          const uint2 head = __ldg(reinterpret_cast<const uint2*>(e));
+          L = int(head.y >> 16);
+          if (L >= 2) {
+            pos   = int64_t(head.x) | (int64_t(head.y & 0xFFFFu) << 32);
+            alive = (L >= 32) ? 0xFFFFFFFFu : ((1u << L) - 1u);
+            const uint8_t* pb = reinterpret_cast<const uint8_t*>(e) + 8;
+            uint32_t prev     = __ldg(pb);
+            tok[0] = identity_ids ? uint16_t(prev) : __ldg(T.byte_to_id + prev);
+            for (int i = 1; i < L; ++i) {
+              const uint32_t cur = __ldg(pb + i);
+              tok[i]    = identity_ids ? uint16_t(cur) : __ldg(T.byte_to_id + cur);
+              rk[i - 1] = __ldg(T.byte_pair_rank + ((prev << 8) | cur));
+              prev      = cur;
+            }
+            rk[L - 1] = uint16_t(NONE);
+          }
+        } else if (batch_next >= count) {
+          drained = true;
+        }
+      }
+      batch_next = min(batch_next + want, batch_end);
+    }
+    if (!__any_sync(0xFFFFFFFFu, pos >= 0)) {
+      if (__all_sync(0xFFFFFFFFu, drained)) break;
+      continue;
+    }
+    if (pos >= 0 && !lane_merge_step(tok, rk, L, alive, T)) {
+      for (int i = 0; i < L; ++i) b.staging[pos + i] = tok[i];  // tokens and tombstones, position by position
+      pos = -1;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// split pipeline, stage 3: one warp per long segment (33..kLongSegMax bytes) in shared memory, and
+// one CTA per huge segment in shared memory or the HBM workspace.  Tokens are written compacted at
+// the start of the segment's byte range, tombstones fill the rest.
+// ------------------------------------------------------------------------------------------------
+constexpr int kLongWarps = 4;
+
+__global__ void __launch_bounds__(kLongWarps * 32) k_merge_long(EncodeBuffers b, DeviceTable T)
+{
+  __shared__ uint16_t s_tok[kLongWarps][kLongSegMax];
+  __shared__ uint16_t s_rk[kLongWarps][kLongSegMax];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t count = min(int64_t(b.counters[5]), b.q_long_cap);
+  int* status = b.counters + 1;
+  uint16_t* tok = s_tok[warp];
+  uint16_t* rk  = s_rk[warp];
+  for (;;) {
+    int at = 0;
+    if (lane == 0) at = atomicAdd(b.counters + 9, 1);
+    at = __shfl_sync(0xFFFFFFFFu, at, 0);
+    if (at >= count) break;
+    const unsigned long long ent = b.q_long[at];
+    const int64_t pos = int64_t(ent & 0xFFFFFFFFFFFFull);
+    const int L       = int(ent >> 48);
+    for (int i = lane; i < L; i += 32) {
+      const uint32_t cur = b.bytes[pos + i];
+      tok[i] = __ldg(T.byte_to_id + cur);
+      rk[i]  = (i + 1 < L) ? __ldg(T.byte_pair_rank + ((cur << 8) | b.bytes[pos + i + 1])) : uint16_t(NONE);
+    }
+    __syncwarp();
+    const int len = group_merge<1>(tok, rk, L, T, nullptr, status);
+    for (int i = lane; i < L; i += 32) b.staging[pos + i] = (i < len) ? tok[i] : uint16_t(DEAD);
+    __syncwarp();
+  }
+}
+
+__global__ void __launch_bounds__(kBaseThreads) k_merge_huge(EncodeBuffers b, DeviceTable T)
+{
+  __shared__ uint16_t s_tok[kBaseSmemTokens];
+  __shared__ uint16_t s_rk[kBaseSmemTokens];
+  __shared__ GroupScratch gs;
+  __shared__ int ticket;
+  const int tid = threadIdx.x;
+  const int64_t count = min(int64_t(b.counters[6]), b.q_huge_cap);
+  int* status = b.counters + 1;
+  for (;;) {
+    __syncthreads();
+    if (tid == 0) ticket = atomicAdd(b.counters + 10, 1);
+    __syncthreads();
+    const int at = ticket;
+    if (at >= count) break;
+    const int64_t pos = int64_t(b.q_huge[2 * at]);
+    const int64_t L64 = int64_t(b.q_huge[2 * at + 1]);
+    uint16_t *tok = s_tok, *rk = s_rk;
+    if (L64 > kBaseSmemTokens) {
+      if (L64 > b.seg_scratch_tokens || b.seg_scratch == nullptr) {
+        if (tid == 0) atomicMax(status, int(kStatusScratchTooSmall));
+        continue;
+      }
+      tok = b.seg_scratch + int64_t(blockIdx.x) * 2 * b.seg_scratch_tokens;
+      rk  = tok + b.seg_scratch_tokens;
+    }
+    const int L = int(L64);
+    for (int i = tid; i < L; i += kBaseThreads) {
+      const uint32_t cur = b.bytes[pos + i];
+      tok[i] = __ldg(T.byte_to_id + cur);
+      rk[i]  = (i + 1 < L) ? __ldg(T.byte_pair_rank + ((cur << 8) | b.bytes[pos + i + 1])) : uint16_t(NONE);
+    }
+    __syncthreads();
+    const int len = group_merge<kBaseThreads / 32>(tok, rk, L, T, &gs, status);
+    for (int i = tid; i < L; i += kBaseThreads) b.staging[pos + i] = (i < len) ? tok[i] : uint16_t(DEAD);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// split pipeline, stages 4 and 5: positional tiles of kTile tokens slots.  k_count_tiles builds the
+// alive bitmap of a tile (slot != tombstone), stores the tile's token count and adds the per-chunk
+// counts; after the scans k_pack_tiles rebuilds the bitmap and writes the int32 ids back to back.
+// ------------------------------------------------------------------------------------------------
+struct PosTileSmem {
+  uint32_t alive[kTile / 32];
+  uint16_t woff[kTile / 32];
+  int scanbuf[33];
+  int32_t out[kTile];
+};
+
+// alive bitmap of tile k into S.alive; every thread handles 16 consecutive slots
+__device__ __forceinline__ void pos_tile_bitmap(const EncodeBuffers& b, int64_t k, uint32_t* alive, uint32_t tok16[8])
+{
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int64_t lo = k * kTile + int64_t(tid) * 16;
+  uint32_t bits = 0;
+  if (lo + 16 <= b.n_bytes && ((reinterpret_cast<uintptr_t>(b.staging + lo) & 15u) == 0)) {
+    const uint4 a = *reinterpret_cast<const uint4*>(b.staging + lo);
+    const uint4 c = *reinterpret_cast<const uint4*>(b.staging + lo + 8);
+    tok16[0] = a.x; tok16[1] = a.y; tok16[2] = a.z; tok16[3] = a.w;
+    tok16[4] = c.x; tok16[5] = c.y; tok16[6] = c.z; tok16[7] = c.w;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t t0 = (lo + 2 * j < b.n_bytes) ? b.staging[lo + 2 * j] : DEAD;
+      const uint32_t t1 = (lo + 2 * j + 1 < b.n_bytes) ? b.staging[lo + 2 * j + 1] : DEAD;
+      tok16[j] = t0 | (t1 << 16);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    bits |= uint32_t((tok16[j] & 0xFFFFu) != DEAD) << (2 * j);
+    bits |= uint32_t((tok16[j] >> 16) != DEAD) << (2 * j + 1);
+  }
+  const uint32_t other = __shfl_xor_sync(0xFFFFFFFFu, bits, 1);
+  if ((lane & 1) == 0) alive[tid >> 1] = bits | (other << 16);
+}
+
+__global__ void __launch_bounds__(kOptThreads) k_count_tiles(EncodeBuffers b)
+{
+  __shared__ PosTileSmem S;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t C = b.totals[0];
+  for (int64_t k = blockIdx.x; k < b.n_tiles; k += gridDim.x) {
+    uint32_t tok16[8];
+    __syncthreads();
+    pos_tile_bitmap(b, k, S.alive, tok16);
+    __syncthreads();
+    int total;
+    block_exclusive_scan((tid < kTile / 32) ? __popc(S.alive[tid]) : 0, S.scanbuf, &total);
+    if (tid == 0) {
+      b.unit_cnt[k]   = total;
+      b.unit_first[k] = k * kTile;
+    }
+    const int64_t lo = k * kTile, region_end = min(lo + kTile, b.n_bytes);
+    for (int64_t c = b.tile_chunk0[k] + warp; c < C; c += kOptThreads / 32) {
+      const int64_t cs_g = b.chunk_off[c];
+      if (cs_g >= region_end) break;
+      const int cs = int(max(cs_g, lo) - lo);
+      const int ce = int(min(b.chunk_off[c + 1], region_end) - lo);
+      if (ce <= cs) continue;
+      int cnt = 0;
+      for (int w = (cs >> 5) + lane; w <= ((ce - 1) >> 5); w += 32) {
+        uint32_t x = S.alive[w];
+        if (w == (cs >> 5)) x &= 0xFFFFFFFFu << (cs & 31);
+        if (w == ((ce - 1) >> 5)) x &= 0xFFFFFFFFu >> (31 - ((ce - 1) & 31));
+        cnt += __popc(x);
+      }
+      cnt = __reduce_add_sync(0xFFFFFFFFu, cnt);
+      if (lane == 0 && cnt) atomicAdd(b.chunk_cnt + c, cnt);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kOptThreads) k_pack_tiles(EncodeBuffers b)
+{
+  __shared__ PosTileSmem S;
+  const int tid = threadIdx.x;
+  for (int64_t k = blockIdx.x; k < b.n_tiles; k += gridDim.x) {
+    uint32_t tok16[8];
+    __syncthreads();
+    pos_tile_bitmap(b, k, S.alive, tok16);
+    __syncthreads();
+    int total;
+    {
+      const int off = block_exclusive_scan((tid < kTile / 32) ? __popc(S.alive[tid]) : 0, S.scanbuf, &total);
+      if (tid < kTile / 32) S.woff[tid] = uint16_t(off);
+    }
+    __syncthreads();
+    {
+      const uint32_t word = S.alive[tid >> 1];
+      const int sh        = (tid & 1) * 16;
+      int d               = S.woff[tid >> 1] + __popc(word & ((1u << sh) - 1u));
+      const uint32_t mine = (word >> sh) & 0xFFFFu;
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if ((mine >> j) & 1u) S.out[d++] = int32_t((tok16[j >> 1] >> ((j & 1) * 16)) & 0xFFFFu);
+    }
+    __syncthreads();
+    const int64_t dst = b.unit_base[k];
+    for (int j = tid; j < total; j += kOptThreads)
+      if (dst + j < b.out_capacity) b.out_ids[dst + j] = S.out[j];
   }
 }
 
@@ -991,6 +1407,11 @@ __global__ void __launch_bounds__(kOptThreads) k_encode_small(EncodeBuffers b, D
   const int tid = threadIdx.x;
   opt_tile_setup(S, T);
   if (tid < 4) b.counters[tid] = 0;
+  if (b.text_off_copy) {  // one parallel read over PCIe instead of dependent reads in the searches below
+    for (int64_t t = tid; t <= b.n_texts; t += kOptThreads) b.text_off_copy[t] = b.text_off[t];
+    b.text_off = b.text_off_copy;
+    __syncthreads();
+  }
   // chunker: chunks per text -> offsets of every chunk -> first chunk of every tile
   const int64_t C = cta_exclusive_scan(ChunksPerText{b.text_off, b.chunk_bytes}, b.n_texts, b.text_chunk_base,
                                        S.scanbuf, &carry_s);
@@ -1022,7 +1443,7 @@ __global__ void __launch_bounds__(kOptThreads) k_encode_small(EncodeBuffers b, D
     __syncthreads();
     if (tid == 0) opt_tile_reset(S);
     __syncthreads();
-    opt_tile(S, b, T, k, C);
+    opt_tile<false>(S, b, T, k, C);
   }
   __syncthreads();
   // output: offsets of units, chunks and texts, then the packed ids
@@ -1185,6 +1606,25 @@ int launch_pack(const EncodeBuffers& b, int mode_base, int grid, cudaStream_t st
     k_pack<<<grid, 256, 0, stream>>>(b.staging, b.unit_first, b.unit_cnt, b.unit_base, b.n_tiles, nullptr, b.out_ids,
                                      b.out_capacity);
   }
+  return 1;
+}
+
+int launch_merge_split(const EncodeBuffers& b, const DeviceTable& t, int sm_count, int grid_front, cudaStream_t stream)
+{
+  if (b.n_tiles <= 0) return 0;
+  if (grid_front > b.n_tiles) grid_front = int(b.n_tiles);
+  k_front_split<<<grid_front, kOptThreads, 0, stream>>>(b, t);
+  k_merge_short<<<sm_count * 6, kShortThreads, 0, stream>>>(b, t);
+  k_merge_long<<<sm_count * 4, kLongWarps * 32, 0, stream>>>(b, t);
+  k_merge_huge<<<sm_count, kBaseThreads, 0, stream>>>(b, t);
+  k_count_tiles<<<unsigned(std::min<int64_t>(b.n_tiles, int64_t(sm_count) * 8)), kOptThreads, 0, stream>>>(b);
+  return 5;
+}
+
+int launch_pack_split(const EncodeBuffers& b, int grid, cudaStream_t stream)
+{
+  if (b.n_tiles <= 0) return 0;
+  k_pack_tiles<<<unsigned(std::min<int64_t>(b.n_tiles, int64_t(grid))), kOptThreads, 0, stream>>>(b);
   return 1;
 }
 

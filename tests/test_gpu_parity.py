@@ -187,6 +187,29 @@ def test_adversarial_long_segments(lib, merges_path, oracle):
     assert np.array_equal(want[:woff[1]], lit)            # 64 Ki of 'a': the literal rule agrees
 
 
+def test_long_and_huge_segments_in_a_large_batch(lib, merges_path, oracle):
+    """Large batches run the split pipeline (queues + separate kernels for short, long and huge
+    segments): segments of every class, including ones far longer than a tile, inside 12 MiB."""
+    rng = np.random.default_rng(3)
+    filler = lib.TextGen(8).text(12 << 20, mix=lib.MIX_STRESS).copy()
+    inserts = [b"a" * 65536, b"ab" * 1500, ("\u65e5" * 900).encode(), b"e" * 2048, b"e" * 2049, b"l" * 33, b"s" * 32,
+               b"x" * 5000 + b" " + b"y" * 4608, bytes(rng.choice(np.frombuffer(b"ae", np.uint8), size=20000))]
+    pos = 1 << 20
+    for blob in inserts:
+        filler[pos:pos + len(blob)] = np.frombuffer(blob, np.uint8)
+        pos += len(blob) + (1 << 20) + 12345
+    lens = [3 << 20, 65536, 0, (5 << 20) + 17, len(filler) - (3 << 20) - 65536 - (5 << 20) - 17]
+    toff_in = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    t = make_tok(lib, merges_path, 65536)
+    chunk_off = [0]
+    for s, e in zip(toff_in[:-1], toff_in[1:]):
+        chunk_off.extend(list(range(int(s) + 65536, int(e), 65536)) + ([int(e)] if e > s else []))
+    want, woff = oracle.encode_chunks(filler, np.array(chunk_off, np.int64), mode=MODE_SEGMENTED, threads=NCPU)
+    ids, toff, coff, _ = t.encode(filler, toff_in)
+    check_chunks(ids, coff, want, woff, "split pipeline, all segment classes")
+    assert t.decode(ids[:coff[20]]) == filler[:chunk_off[20]].tobytes()
+
+
 def test_random_small_batches(lib, merges_path, oracle):
     """Many short texts of assorted lengths in one batch (latency-mode strings, ragged)."""
     rng = np.random.default_rng(11)
