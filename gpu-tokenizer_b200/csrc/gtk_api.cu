@@ -129,6 +129,7 @@ struct gtk_tokenizer {
   gtk::DeviceTable dtab{};
 
   // arenas
+  DevBuf d_memo;  // call-local memo of segment results, cleared by every call
   DevBuf d_q_short, d_q_long, d_q_huge;  // split pipeline queues (shared by all slices: kernels of one stream)
   DevBuf d_bytes, d_text_off, d_text_chunk_base, d_chunk_off, d_tile_chunk0, d_staging, d_unit_first, d_unit_cnt,
       d_chunk_cnt, d_unit_base, d_chunk_id_off, d_text_id_off, d_out_ids, d_seg_scratch, d_scan_sums, d_counters,
@@ -140,6 +141,8 @@ struct gtk_tokenizer {
   uint8_t* small_out_h = nullptr;  // [totals | text id offsets | chunk id offsets | ids]
   uint8_t* small_out_d = nullptr;
   bool result_is_small = false;
+  int tune_pipeline = GTK_PIPELINE_AUTO;  // AUTO currently means FUSED: fastest measured on B200
+  int tune_memo = 0;
   // sliced host path: copy streams and two slice arenas
   cudaStream_t in_stream = nullptr, out_stream = nullptr;
   SliceArena slice[4];
@@ -203,12 +206,19 @@ int64_t chunk_upper_bound(int64_t n_bytes, int64_t n_texts, int chunk_tokens)
 // Batches of at least this many tiles take the split pipeline (queues + separate merge kernels);
 // smaller ones run the single tile kernel, whose per-tile barriers do not matter at that size.
 constexpr int64_t kSplitMinTiles = 1024;
+constexpr uint32_t kMemoLog2 = 18;          // 262 144 slots x 32 bytes = 8 MiB
+constexpr int64_t kMemoMinTiles = 64;       // batches below 256 KiB skip the memo (clearing it would dominate)
 
 bool use_split(const gtk::EncodeBuffers& b, int mode) { return mode == GTK_MODE_OPT && b.q_short != nullptr; }
 
 void attach_queues(gtk_tokenizer* h, gtk::EncodeBuffers& b, int64_t reserve_bytes)
 {
-  if (b.n_tiles < kSplitMinTiles) return;
+  if (h->tune_memo && b.n_tiles >= kMemoMinTiles) {
+    h->d_memo.reserve((size_t(1) << kMemoLog2) * 32);
+    b.memo = h->d_memo.as<uint4>();
+    b.memo_log2 = kMemoLog2;
+  }
+  if (h->tune_pipeline != GTK_PIPELINE_SPLIT || b.n_tiles < kSplitMinTiles) return;
   const int64_t n = std::max(reserve_bytes, b.n_bytes);
   const int64_t cap_short = std::min<int64_t>(n / 8 + 4096, (int64_t(1) << 31) - (int64_t(1) << 24));
   const int64_t cap_long = n / 33 + 1024, cap_huge = n / (gtk::kLongSegMax + 1) + 16;
@@ -309,6 +319,7 @@ void run_front(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* lau
   if (!ev) ev = h->ev;
   GTK_CUDA(cudaMemsetAsync(b.counters, 0, 64, s));
   GTK_CUDA(cudaMemsetAsync(b.chunk_cnt, 0, size_t(b.chunk_cap + 1) * 4, s));
+  if (b.memo && mode != GTK_MODE_BASE) GTK_CUDA(cudaMemsetAsync(b.memo, 0, (size_t(1) << b.memo_log2) * 32, s));
   GTK_CUDA(cudaEventRecord(ev[0], s));
   *launches += gtk::launch_chunker(b, s);
   GTK_CUDA(cudaEventRecord(ev[1], s));
@@ -760,7 +771,7 @@ GTK_API void gtk_destroy(gtk_tokenizer* h)
   if (h->device >= 0) {
     cudaSetDevice(h->device);
     if (h->stream) cudaStreamSynchronize(h->stream);
-    for (DevBuf* b : {&h->d_slots, &h->d_bpr, &h->d_mor, &h->d_sor, &h->d_adj, &h->d_b2i, &h->d_words, &h->d_q_short, &h->d_q_long, &h->d_q_huge, &h->d_bytes, &h->d_text_off,
+    for (DevBuf* b : {&h->d_slots, &h->d_bpr, &h->d_mor, &h->d_sor, &h->d_adj, &h->d_b2i, &h->d_words, &h->d_memo, &h->d_q_short, &h->d_q_long, &h->d_q_huge, &h->d_bytes, &h->d_text_off,
                       &h->d_text_chunk_base, &h->d_chunk_off, &h->d_tile_chunk0, &h->d_staging, &h->d_unit_first,
                       &h->d_unit_cnt, &h->d_chunk_cnt, &h->d_unit_base, &h->d_chunk_id_off, &h->d_text_id_off,
                       &h->d_out_ids, &h->d_seg_scratch, &h->d_scan_sums, &h->d_counters, &h->d_totals})
@@ -1045,6 +1056,16 @@ GTK_API int gtk_set_stream(gtk_tokenizer* h, void* cuda_stream)
   cudaSetDevice(h->device);
   cudaStreamSynchronize(h->stream);
   h->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : h->own_stream;
+  return GTK_OK;
+}
+
+GTK_API int gtk_set_tuning(gtk_tokenizer* h, int pipeline, int memo)
+{
+  if (!h) return GTK_ERR_INVALID_ARG;
+  std::lock_guard<std::mutex> lock(h->mu);
+  if (pipeline < GTK_PIPELINE_AUTO || pipeline > GTK_PIPELINE_SPLIT) return h->fail(GTK_ERR_INVALID_ARG, "unknown pipeline");
+  h->tune_pipeline = pipeline;
+  h->tune_memo = memo ? 1 : 0;
   return GTK_OK;
 }
 

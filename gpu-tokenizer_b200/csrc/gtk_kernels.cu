@@ -68,6 +68,82 @@ __device__ __forceinline__ uint32_t word_lookup(const DeviceTable& T, uint32_t k
   return 0xFFFFFFFFu;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Call-local memo: a short segment (<= 12 bytes, <= 8 resulting ids) that has been merged once is
+// stored under its bytes, so a later occurrence of the same bytes in the same call copies the ids
+// instead of repeating the merges.  The ids stored are the output of the merge loop on exactly
+// these bytes, so a hit cannot change any result.  Slots are written once: empty -> busy (CAS) ->
+// payload -> fence -> ready; a slot is one 32-byte sector and readers bypass L1, so a reader that
+// sees `ready` sees the whole entry.  A taken slot is never replaced (a collision is just a miss).
+// ------------------------------------------------------------------------------------------------
+constexpr uint32_t kMemoReady = 0xA5000000u, kMemoBusy = 0x5A000000u, kMemoStateMask = 0xFF000000u;
+
+__device__ __forceinline__ uint32_t memo_slot(uint32_t k0, uint32_t k1, uint32_t k2, uint32_t L, uint32_t log2)
+{
+  uint32_t h = (k0 * 0x85EBCA77u) ^ (k1 * 0xC2B2AE3Du) ^ (k2 * 0x27D4EB2Fu) ^ (L * 0x165667B1u);
+  h ^= h >> 16;
+  h *= 0x9E3779B1u;
+  return h >> (32 - log2);
+}
+
+// segment bytes at shared-memory offset `at` (any alignment), zero padded to three words
+__device__ __forceinline__ void segment_key(const uint8_t* bytes, int at, int LL, uint32_t& k0, uint32_t& k1,
+                                            uint32_t& k2)
+{
+  const uint32_t* wp = reinterpret_cast<const uint32_t*>(bytes + (at & ~3));
+  const uint32_t sh  = uint32_t(at & 3) * 8u;
+  const uint32_t a0 = wp[0], a1 = wp[1], a2 = wp[2], a3 = wp[3];
+  k0 = __funnelshift_r(a0, a1, sh);
+  k1 = __funnelshift_r(a1, a2, sh);
+  k2 = __funnelshift_r(a2, a3, sh);
+  k0 &= (LL >= 4) ? 0xFFFFFFFFu : ((1u << (8 * LL)) - 1u);
+  k1 &= (LL >= 8) ? 0xFFFFFFFFu : ((LL <= 4) ? 0u : ((1u << (8 * (LL - 4))) - 1u));
+  k2 &= (LL >= 12) ? 0xFFFFFFFFu : ((LL <= 8) ? 0u : ((1u << (8 * (LL - 8))) - 1u));
+}
+
+// returns the number of ids (written to tok[0..n), tombstones behind them), 0 on a miss
+__device__ __forceinline__ int memo_lookup(const uint4* memo, uint32_t log2, uint32_t k0, uint32_t k1, uint32_t k2,
+                                           int LL, uint16_t* tok)
+{
+  const uint4* slot = memo + 2 * size_t(memo_slot(k0, k1, k2, uint32_t(LL), log2));
+  const uint4 a     = __ldcg(slot);
+  if ((a.w & kMemoStateMask) != kMemoReady || a.x != k0 || a.y != k1 || a.z != k2 || ((a.w >> 16) & 0xFFu) != uint32_t(LL))
+    return 0;
+  const uint4 v = __ldcg(slot + 1);
+  const int n   = int(a.w & 0xFFu);
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    if (i < n) tok[i] = uint16_t(w[i >> 1] >> ((i & 1) * 16));
+  for (int i = n; i < LL; ++i) tok[i] = uint16_t(DEAD);
+  return n;
+}
+
+// store the finished segment tok[0..LL) (tombstones skipped) under its bytes
+__device__ __forceinline__ void memo_insert(uint4* memo, uint32_t log2, uint32_t k0, uint32_t k1, uint32_t k2, int LL,
+                                            const uint16_t* tok)
+{
+  uint32_t w[4] = {0, 0, 0, 0};
+  int n = 0;
+  for (int i = 0; i < LL; ++i) {
+    const uint32_t t = tok[i];
+    if (t == DEAD) continue;
+    if (n < 8) w[n >> 1] |= t << ((n & 1) * 16);
+    ++n;
+  }
+  if (n > 8) return;
+  uint4* slot = memo + 2 * size_t(memo_slot(k0, k1, k2, uint32_t(LL), log2));
+  uint32_t* meta = reinterpret_cast<uint32_t*>(slot) + 3;
+  if (atomicCAS(meta, 0u, kMemoBusy) != 0u) return;  // taken (or being written): never replaced
+  uint32_t* p = reinterpret_cast<uint32_t*>(slot);
+  p[0] = k0;
+  p[1] = k1;
+  p[2] = k2;
+  slot[1] = make_uint4(w[0], w[1], w[2], w[3]);
+  __threadfence();
+  atomicExch(meta, kMemoReady | (uint32_t(LL) << 16) | uint32_t(n));
+}
+
 __device__ __forceinline__ uint32_t merged_id(const DeviceTable& T, uint32_t rank)
 {
   return T.merged_is_256_plus_rank ? 256u + rank : __ldg(T.merged_of_rank + rank);
@@ -534,7 +610,7 @@ struct OptSmem {
   GroupScratch gs;
   int scanbuf[33];
   int ticket;
-  int nseg, nlong, seg_next, nmiss, qbase;
+  int nseg, nlong, seg_next, nmiss, qbase, nbig, qfill;
   int first_start, last_start, over_start;
   int over_len;
   long long over_end;
@@ -564,6 +640,8 @@ __device__ __forceinline__ void opt_tile_reset(OptSmem& S)
   S.nlong       = 0;
   S.seg_next    = 0;
   S.nmiss       = 0;
+  S.nbig        = 0;
+  S.qfill       = 0;
   S.first_start = kWindow;
   S.last_start  = -1;
   S.over_start  = -1;
@@ -736,20 +814,15 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
           const int LL = int(ent >> 16);
           miss         = true;
           if (LL <= 12) {
-            const int at       = 16 + ss;
-            const uint32_t* wp = reinterpret_cast<const uint32_t*>(&S.bytes[at & ~3]);
-            const uint32_t sh  = uint32_t(at & 3) * 8u;
-            const uint32_t a0 = wp[0], a1 = wp[1], a2 = wp[2], a3 = wp[3];
-            uint32_t k0 = __funnelshift_r(a0, a1, sh), k1 = __funnelshift_r(a1, a2, sh),
-                     k2 = __funnelshift_r(a2, a3, sh);
-            k0 &= (LL >= 4) ? 0xFFFFFFFFu : ((1u << (8 * LL)) - 1u);
-            k1 &= (LL >= 8) ? 0xFFFFFFFFu : ((LL <= 4) ? 0u : ((1u << (8 * (LL - 4))) - 1u));
-            k2 &= (LL >= 12) ? 0xFFFFFFFFu : ((LL <= 8) ? 0u : ((1u << (8 * (LL - 8))) - 1u));
+            uint32_t k0, k1, k2;
+            segment_key(S.bytes, 16 + ss, LL, k0, k1, k2);
             const uint32_t id = word_lookup(T, k0, k1, k2, uint32_t(LL));
             if (id != 0xFFFFFFFFu) {
               miss      = false;
               S.tok[ss] = uint16_t(id);
               for (int i = 1; i < LL; ++i) S.tok[ss + i] = uint16_t(DEAD);
+            } else if (b.memo && memo_lookup(b.memo, b.memo_log2, k0, k1, k2, LL, S.tok + ss) > 0) {
+              miss = false;
             }
           }
         }
@@ -772,27 +845,36 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
     // ---- E. short segments that missed the lookup.  Split mode: hand them to the batch-wide queue
     //         (one reservation per tile).  Otherwise, or if the queue is full: every lane pulls
     //         segments from a CTA-wide list and does one merge step per loop trip ----
+    // Split mode: segments of more than 12 bytes (long merge chains, not covered by the memo) leave
+    // through the batch-wide queue, one reservation per tile; the rest is merged here.
     bool queued = false;
     if (SPLIT) {
       const int nm = S.nmiss;
-      if (tid == 0) S.qbase = (nm > 0) ? atomicAdd(b.counters + 4, nm) : 0;
+      int mybig    = 0;
+      for (int j = tid; j < nm; j += kOptThreads) mybig += int((S.seg[j] >> 16) > 12u);
+      if (mybig) atomicAdd(&S.nbig, mybig);
+      __syncthreads();
+      const int nbig = S.nbig;
+      if (tid == 0) S.qbase = nbig ? atomicAdd(b.counters + 4, nbig) : 0;
       __syncthreads();
       const int64_t qb = S.qbase;
-      queued           = qb + nm <= b.q_short_cap;
+      queued           = qb + nbig <= b.q_short_cap;
       for (int j = tid; j < nm; j += kOptThreads) {
-        if (qb + j >= b.q_short_cap) continue;  // a reservation that does not fit is filled with null entries
-        uint4* e = b.q_short + 3 * (qb + j);
+        const uint32_t ent = S.seg[j];
+        if ((ent >> 16) <= 12u) continue;
+        const int64_t at = qb + atomicAdd(&S.qfill, 1);
+        if (at >= b.q_short_cap) continue;  // a reservation that does not fit is filled with null entries
+        uint4* e = b.q_short + 3 * at;
         if (!queued) {
           e[0] = make_uint4(0, 0, 0, 0);
           continue;
         }
-        const uint32_t ent = S.seg[j];
-        const int ss       = int(ent & 0xFFFFu);
+        const int ss = int(ent & 0xFFFFu);
         const unsigned long long head = (unsigned long long)(lo + ss) | ((unsigned long long)(ent >> 16) << 48);
         // the segment's bytes travel with the entry, so the consumer needs one contiguous read
-        const int at       = 16 + ss;
-        const uint32_t* wp = reinterpret_cast<const uint32_t*>(&S.bytes[at & ~3]);
-        const uint32_t sh  = uint32_t(at & 3) * 8u;
+        const int at8      = 16 + ss;
+        const uint32_t* wp = reinterpret_cast<const uint32_t*>(&S.bytes[at8 & ~3]);
+        const uint32_t sh  = uint32_t(at8 & 3) * 8u;
         uint32_t w[9];
 #pragma unroll
         for (int q = 0; q < 9; ++q) w[q] = wp[q];
@@ -803,7 +885,8 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
         e[2] = make_uint4(__funnelshift_r(w[6], w[7], sh), __funnelshift_r(w[7], w[8], sh), 0u, 0u);
       }
     }
-    if (!queued) {
+    GTK_PHASE(12);
+    {
       const int nseg   = S.nmiss;
       int s            = -1, L = 0;
       uint32_t alive   = 0;
@@ -822,18 +905,31 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
               drained = true;
             } else {
               const uint32_t ent = S.seg[j];
-              s     = int(ent & 0xFFFFu);
-              L     = int(ent >> 16);
-              alive = (L >= 32) ? 0xFFFFFFFFu : ((1u << L) - 1u);
+              if (!(queued && (ent >> 16) > 12u)) {  // queued segments are merged by a later kernel
+                s     = int(ent & 0xFFFFu);
+                L     = int(ent >> 16);
+                alive = (L >= 32) ? 0xFFFFFFFFu : ((1u << L) - 1u);
+              }
             }
           }
         }
-        if (!__any_sync(0xFFFFFFFFu, s >= 0)) break;  // a lane without work here is drained
-        if (s >= 0 && !thread_merge_step(S.tok + s, S.rk + s, L, alive, T)) s = -1;
+        if (!__any_sync(0xFFFFFFFFu, s >= 0)) {
+          if (__all_sync(0xFFFFFFFFu, drained)) break;
+          continue;
+        }
+        if (s >= 0 && !thread_merge_step(S.tok + s, S.rk + s, L, alive, T)) {
+          if (b.memo && L <= 12) {
+            uint32_t k0, k1, k2;
+            segment_key(S.bytes, 16 + s, L, k0, k1, k2);
+            memo_insert(b.memo, b.memo_log2, k0, k1, k2, L, S.tok + s);
+          }
+          s = -1;
+        }
       }
     }
     __syncthreads();
 
+    GTK_PHASE(13);
     if (SPLIT) {
       // ---- split mode: long segments go to their queues, the tile stores its tokens position by
       //      position (tombstones included); counting and packing happen in later kernels ----
@@ -888,6 +984,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
           }
         }
       }
+      GTK_PHASE(14);
       const int first = S.first_start;
       int end_owned   = 0;
       if (S.last_start >= 0) end_owned = (S.over_start >= 0) ? S.over_start : next_cut(S.cut, S.last_start);
@@ -901,6 +998,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
           for (int i = max(i0, first); i < min(i0 + 4, end_owned); ++i) b.staging[lo + i] = S.tok[i];
         }
       }
+      GTK_PHASE(15);
       return;
     }
 

@@ -66,6 +66,7 @@ def load_library() -> C.CDLL:
     lib.gtk_token_symbols.argtypes = [vp, i32, C.c_char_p, i32]
     lib.gtk_token_symbols.restype = i32
     lib.gtk_set_stream.argtypes = [vp, vp]
+    lib.gtk_set_tuning.argtypes = [vp, C.c_int, C.c_int]
     lib.gtk_encode_chunks_noalloc.argtypes = [vp, vp, i64, vp, i64, i32, vp, vp]
     lib.gtk_pinned_alloc.argtypes = [C.c_size_t]
     lib.gtk_pinned_alloc.restype = vp
@@ -151,6 +152,11 @@ class Tokenizer:
     def set_stream(self, cuda_stream: int | None) -> None:
         """Run later GPU work on the caller's stream (e.g. ``torch.cuda.current_stream().cuda_stream``)."""
         self._check(self._lib.gtk_set_stream(self._h, cuda_stream or None))
+
+    def set_tuning(self, pipeline: int = 0, memo: bool = False) -> None:
+        """pipeline: 0 auto, 1 fused tile kernel, 2 split (queues + per-segment kernels); memo: call-local
+        memo of finished segments.  Results never depend on these."""
+        self._check(self._lib.gtk_set_tuning(self._h, int(pipeline), int(bool(memo))))
 
     # ------------------------------------------------------------------ host buffers
     def _result(self, copy: bool = True):

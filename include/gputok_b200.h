@@ -173,6 +173,14 @@ GTK_API int32_t gtk_token_symbols(const gtk_tokenizer* h, int32_t id, char* buf,
  * time it with its own events.  The entry points stay synchronous on return. */
 GTK_API int gtk_set_stream(gtk_tokenizer* h, void* cuda_stream);
 
+/* Tuning knobs of GTK_MODE_OPT (no counterpart in the reference; results never depend on them).
+ *   pipeline  GTK_PIPELINE_AUTO (default), GTK_PIPELINE_FUSED: one tile kernel merges everything;
+ *             GTK_PIPELINE_SPLIT: segments of more than 12 bytes leave the tile kernel through a
+ *             queue and are merged by barrier-free per-segment kernels (batches >= 4 MiB only)
+ *   memo      0 / 1: call-local memo of finished short segments (off by default)            */
+enum { GTK_PIPELINE_AUTO = 0, GTK_PIPELINE_FUSED = 1, GTK_PIPELINE_SPLIT = 2 };
+GTK_API int gtk_set_tuning(gtk_tokenizer* h, int pipeline, int memo);
+
 /* Longest chunk, in bytes, that gtk_encode_chunks_noalloc accepts. */
 #define GTK_NOALLOC_MAX_CHUNK_BYTES 16384
 
