@@ -44,6 +44,11 @@ for _p in (ROOT, PKG):
 
 BLOCK = 65536  # generator block size
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per input byte of one k_merge_opt launch, from the
+# ncu capture summarised in profiles/k_merge_opt_cfg2_128MiB.md (202.3 MB for 128 MiB of config-2 text);
+# traffic grows in proportion to the tile count, so a launch over n bytes moves this x n.
+MERGE_OPT_DRAM_BYTES_PER_INPUT_BYTE = 202.3e6 / (128 << 20)
+
 WORKLOADS = {
     #        seed  bytes per GPU   chunk   mix  lognormal
     "cfg1": (0, 1 << 20, 1024, 0, False),
@@ -400,7 +405,11 @@ def main() -> None:
                     "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_wall_ms, "steps": e2e_steps},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "kernel": "k_merge_" + args.mode, "achieved": achieved, "peak": peak,
-                         "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_kind,
+                         "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": (MERGE_OPT_DRAM_BYTES_PER_INPUT_BYTE * n_bytes
+                                     if args.mode == "opt" and args.workload == "cfg2" else None),
+                         "traffic_note": "ncu DRAM bytes of a 128 MiB launch scaled by input bytes",
+                         "peak_source": peak_kind,
                          "algorithmic_bytes_per_input_byte": algo_bytes_per_byte,
                          "kernel_ms": avg_merge_ms, "input_GB_per_s_kernel": n_bytes / (avg_merge_ms * 1e-3) / 1e9},
             "cpu_baseline": cpu_base, "parity_check": check, "clocks": clocks,
