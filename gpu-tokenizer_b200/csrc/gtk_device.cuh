@@ -14,7 +14,7 @@ namespace gtk {
 // start inside TILE consecutive bytes and sees HALO more bytes so that the
 // last owned segment can finish inside shared memory.
 constexpr int kTile = 4096;
-constexpr int kHalo = 512;
+constexpr int kHalo = 256;
 constexpr int kWindow = kTile + kHalo;
 constexpr int kOptThreads = 256;
 constexpr int kBaseThreads = 512;

@@ -152,7 +152,7 @@ __device__ __forceinline__ uint32_t merged_id(const DeviceTable& T, uint32_t ran
 __device__ __forceinline__ bool adj_bit(const uint32_t* adj, uint32_t u, uint32_t v)
 {
   const uint32_t bit = (u << 8) | v;
-  return (adj[bit >> 5] >> (bit & 31u)) & 1u;
+  return (__ldg(adj + (bit >> 5)) >> (bit & 31u)) & 1u;
 }
 
 __device__ __forceinline__ uint32_t lanemask_lt()
@@ -599,10 +599,9 @@ __device__ unsigned long long g_phase_cycles[16];
 
 struct OptSmem {
   alignas(16) uint8_t bytes[kWindow + 32];  // [15] = byte before the window, [16+i] = window position i
-  uint32_t adj[2048];
   alignas(8) uint16_t tok[kWindow];
   alignas(8) uint16_t rk[kWindow];  // reused as the compacted output buffer after merging
-  uint32_t seg[kSegCap];  // (start | length << 16) of owned short segments, longest first
+  uint16_t seg[kSegCap];  // starts of owned short segments, longest first (length = distance to the next start)
   int hist[34];
   uint32_t cut[kCutWords + 2];  // segment-start bits; reused as the alive bitmap
   uint16_t woff[kCutWords + 2];
@@ -630,7 +629,6 @@ __device__ __forceinline__ int next_cut(const uint32_t* cut, int s)
 // the all-ones sentinel words behind the segment-start bitmap.
 __device__ __forceinline__ void opt_tile_setup(OptSmem& S, const DeviceTable& T)
 {
-  for (int i = threadIdx.x; i < 2048; i += kOptThreads) S.adj[i] = T.adj[i];
   if (threadIdx.x < 2) S.cut[kCutWords + threadIdx.x] = 0xFFFFFFFFu;
 }
 
@@ -703,7 +701,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
       by[5] = S.bytes[20 + i0];
       uint32_t mergeable = 0;  // bit k: the pair (by[k], by[k+1]) occurs inside some merge result
 #pragma unroll
-      for (int k = 0; k < 5; ++k) mergeable |= uint32_t(adj_bit(S.adj, by[k], by[k + 1])) << k;
+      for (int k = 0; k < 5; ++k) mergeable |= uint32_t(adj_bit(T.adj, by[k], by[k + 1])) << k;
       uint32_t nib = 0, t[4], r[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
@@ -791,7 +789,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
         const int LL = e - ss;
         if (LL <= kThreadSegMax && !(e >= kWindow && wlen == kWindow)) {
           const int pos = atomicAdd(&S.hist[LL], 1);
-          S.seg[pos]    = uint32_t(ss) | (uint32_t(LL) << 16);
+          S.seg[pos]    = uint16_t(ss);
         }
       }
     }
@@ -810,8 +808,8 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
         bool miss    = false;
         if (j < nseg) {
           ent          = S.seg[j];
-          const int ss = int(ent & 0xFFFFu);
-          const int LL = int(ent >> 16);
+          const int ss = int(ent);
+          const int LL = next_cut(S.cut, ss) - ss;
           miss         = true;
           if (LL <= 12) {
             uint32_t k0, k1, k2;
@@ -831,7 +829,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
         if (lane == 0 && bal) wbase = atomicAdd(&S.nmiss, __popc(bal));
         wbase = __shfl_sync(0xFFFFFFFFu, wbase, 0);
         __syncthreads();  // every entry of this round has been read before the list is overwritten
-        if (miss) S.seg[wbase + __popc(bal & lt)] = ent;
+        if (miss) S.seg[wbase + __popc(bal & lt)] = uint16_t(ent);
       }
     }
     __syncthreads();
@@ -851,7 +849,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
     if (SPLIT) {
       const int nm = S.nmiss;
       int mybig    = 0;
-      for (int j = tid; j < nm; j += kOptThreads) mybig += int((S.seg[j] >> 16) > 12u);
+      for (int j = tid; j < nm; j += kOptThreads) mybig += int(next_cut(S.cut, S.seg[j]) - int(S.seg[j]) > 12);
       if (mybig) atomicAdd(&S.nbig, mybig);
       __syncthreads();
       const int nbig = S.nbig;
@@ -860,8 +858,10 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
       const int64_t qb = S.qbase;
       queued           = qb + nbig <= b.q_short_cap;
       for (int j = tid; j < nm; j += kOptThreads) {
-        const uint32_t ent = S.seg[j];
-        if ((ent >> 16) <= 12u) continue;
+        const int ss0 = S.seg[j];
+        const int LL0 = next_cut(S.cut, ss0) - ss0;
+        const uint32_t ent = uint32_t(ss0) | (uint32_t(LL0) << 16);
+        if (LL0 <= 12) continue;
         const int64_t at = qb + atomicAdd(&S.qfill, 1);
         if (at >= b.q_short_cap) continue;  // a reservation that does not fit is filled with null entries
         uint4* e = b.q_short + 3 * at;
@@ -904,10 +904,11 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
             if (j >= nseg) {
               drained = true;
             } else {
-              const uint32_t ent = S.seg[j];
-              if (!(queued && (ent >> 16) > 12u)) {  // queued segments are merged by a later kernel
-                s     = int(ent & 0xFFFFu);
-                L     = int(ent >> 16);
+              const int ss0 = S.seg[j];
+              const int LL0 = next_cut(S.cut, ss0) - ss0;
+              if (!(queued && LL0 > 12)) {  // queued segments are merged by a later kernel
+                s     = ss0;
+                L     = LL0;
                 alive = (L >= 32) ? 0xFFFFFFFFu : ((1u << L) - 1u);
               }
             }
@@ -961,7 +962,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
         int64_t ge         = cend;
         for (int64_t pos = lo + kWindow; pos < cend; pos += kOptThreads) {
           const int64_t p = pos + tid;
-          const bool cutp = (p < cend) && !adj_bit(S.adj, b.bytes[p - 1], b.bytes[p]);
+          const bool cutp = (p < cend) && !adj_bit(T.adj, b.bytes[p - 1], b.bytes[p]);
           if (__syncthreads_or(cutp)) {
             if (cutp) atomicMin(reinterpret_cast<unsigned long long*>(&S.over_end), (unsigned long long)p);
             __syncthreads();
@@ -1099,7 +1100,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
       int64_t ge         = cend;
       for (int64_t pos = lo + kWindow; pos < cend; pos += kOptThreads) {
         const int64_t p = pos + tid;
-        const bool cutp = (p < cend) && !adj_bit(S.adj, b.bytes[p - 1], b.bytes[p]);
+        const bool cutp = (p < cend) && !adj_bit(T.adj, b.bytes[p - 1], b.bytes[p]);
         if (__syncthreads_or(cutp)) {
           if (cutp) atomicMin(reinterpret_cast<unsigned long long*>(&S.over_end), (unsigned long long)p);
           __syncthreads();
@@ -1139,7 +1140,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
   }
 }
 
-__global__ void __launch_bounds__(kOptThreads) k_merge_opt(EncodeBuffers b, DeviceTable T)
+__global__ void __launch_bounds__(kOptThreads, 8) k_merge_opt(EncodeBuffers b, DeviceTable T)
 {
   __shared__ OptSmem S;
   const int tid   = threadIdx.x;
