@@ -206,7 +206,7 @@ int64_t chunk_upper_bound(int64_t n_bytes, int64_t n_texts, int chunk_tokens)
 // Batches of at least this many tiles take the split pipeline (queues + separate merge kernels);
 // smaller ones run the single tile kernel, whose per-tile barriers do not matter at that size.
 constexpr int64_t kSplitMinTiles = 1024;
-constexpr uint32_t kMemoLog2 = 18;          // 262 144 slots x 32 bytes = 8 MiB
+constexpr uint32_t kMemoLog2 = 17;          // 131 072 slots x 64 bytes = 8 MiB
 constexpr int64_t kMemoMinTiles = 64;       // batches below 256 KiB skip the memo (clearing it would dominate)
 
 bool use_split(const gtk::EncodeBuffers& b, int mode) { return mode == GTK_MODE_OPT && b.q_short != nullptr; }
@@ -214,7 +214,7 @@ bool use_split(const gtk::EncodeBuffers& b, int mode) { return mode == GTK_MODE_
 void attach_queues(gtk_tokenizer* h, gtk::EncodeBuffers& b, int64_t reserve_bytes)
 {
   if (h->tune_memo && b.n_tiles >= kMemoMinTiles) {
-    h->d_memo.reserve((size_t(1) << kMemoLog2) * 32);
+    h->d_memo.reserve((size_t(1) << kMemoLog2) * 64);
     b.memo = h->d_memo.as<uint4>();
     b.memo_log2 = kMemoLog2;
   }
@@ -319,7 +319,7 @@ void run_front(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* lau
   if (!ev) ev = h->ev;
   GTK_CUDA(cudaMemsetAsync(b.counters, 0, 64, s));
   GTK_CUDA(cudaMemsetAsync(b.chunk_cnt, 0, size_t(b.chunk_cap + 1) * 4, s));
-  if (b.memo && mode != GTK_MODE_BASE) GTK_CUDA(cudaMemsetAsync(b.memo, 0, (size_t(1) << b.memo_log2) * 32, s));
+  if (b.memo && mode != GTK_MODE_BASE) GTK_CUDA(cudaMemsetAsync(b.memo, 0, (size_t(1) << b.memo_log2) * 64, s));
   GTK_CUDA(cudaEventRecord(ev[0], s));
   *launches += gtk::launch_chunker(b, s);
   GTK_CUDA(cudaEventRecord(ev[1], s));

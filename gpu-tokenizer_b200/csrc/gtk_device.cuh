@@ -83,7 +83,7 @@ struct EncodeBuffers {
   unsigned long long* q_long;   // length 33..kLongSegMax
   unsigned long long* q_huge;   // longer
   int64_t q_short_cap, q_long_cap, q_huge_cap;
-  // call-local memo of finished short segments: 32-byte slots {k0, k1, k2, state|len|ntok ; 8 x u16 ids},
+  // call-local memo of finished short segments: 64-byte slots {key 32 B ; state|len|count, 12 x u16 ids},
   // direct mapped, written once (empty -> busy -> ready) and cleared at the start of every call
   uint4* memo;
   uint32_t memo_log2;

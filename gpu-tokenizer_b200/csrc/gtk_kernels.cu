@@ -69,18 +69,25 @@ __device__ __forceinline__ uint32_t word_lookup(const DeviceTable& T, uint32_t k
 }
 
 // ------------------------------------------------------------------------------------------------
-// Call-local memo: a short segment (<= 12 bytes, <= 8 resulting ids) that has been merged once is
+// Call-local memo: a short segment (<= 32 bytes, <= 12 resulting ids) that has been merged once is
 // stored under its bytes, so a later occurrence of the same bytes in the same call copies the ids
-// instead of repeating the merges.  The ids stored are the output of the merge loop on exactly
-// these bytes, so a hit cannot change any result.  Slots are written once: empty -> busy (CAS) ->
-// payload -> fence -> ready; a slot is one 32-byte sector and readers bypass L1, so a reader that
-// sees `ready` sees the whole entry.  A taken slot is never replaced (a collision is just a miss).
+// instead of repeating the merge chain.  The ids stored are the output of the merge loop on exactly
+// these bytes, so a hit cannot change any result.  A slot is 64 bytes = two 32-byte sectors:
+// sector 0 holds the key (bytes, zero padded), sector 1 the state word and the ids.  Slots are
+// written once -- empty -> busy (CAS) -> key and ids -> fence -> ready -- and never replaced (a
+// collision is a miss); the table is cleared at the start of every call.  Readers bypass L1.  A
+// reader that sees `ready` has the ids of that entry (same sector); if its copy of the key sector
+// is older than the entry it can only be the cleared, all-zero state, which either fails the
+// comparison (a miss) or is the true key of an all-zero segment.
 // ------------------------------------------------------------------------------------------------
 constexpr uint32_t kMemoReady = 0xA5000000u, kMemoBusy = 0x5A000000u, kMemoStateMask = 0xFF000000u;
+constexpr int kMemoMaxIds = 12;
 
-__device__ __forceinline__ uint32_t memo_slot(uint32_t k0, uint32_t k1, uint32_t k2, uint32_t L, uint32_t log2)
+__device__ __forceinline__ uint32_t memo_slot(const uint32_t k[8], uint32_t L, uint32_t log2)
 {
-  uint32_t h = (k0 * 0x85EBCA77u) ^ (k1 * 0xC2B2AE3Du) ^ (k2 * 0x27D4EB2Fu) ^ (L * 0x165667B1u);
+  uint32_t h = (k[0] * 0x85EBCA77u) ^ (k[1] * 0xC2B2AE3Du) ^ (k[2] * 0x27D4EB2Fu) ^ (k[3] * 0x165667B1u);
+  h ^= (k[4] * 0x9E3779B1u) ^ (k[5] * 0xD3A2646Du) ^ (k[6] * 0xFD7046C5u) ^ (k[7] * 0xB55A4F09u);
+  h ^= L * 0x68E31DA4u;
   h ^= h >> 16;
   h *= 0x9E3779B1u;
   return h >> (32 - log2);
@@ -101,45 +108,71 @@ __device__ __forceinline__ void segment_key(const uint8_t* bytes, int at, int LL
   k2 &= (LL >= 12) ? 0xFFFFFFFFu : ((LL <= 8) ? 0u : ((1u << (8 * (LL - 8))) - 1u));
 }
 
-// returns the number of ids (written to tok[0..n), tombstones behind them), 0 on a miss
-__device__ __forceinline__ int memo_lookup(const uint4* memo, uint32_t log2, uint32_t k0, uint32_t k1, uint32_t k2,
-                                           int LL, uint16_t* tok)
+// the same for up to 32 bytes, eight words
+__device__ __forceinline__ void segment_key8(const uint8_t* bytes, int at, int LL, uint32_t k[8])
 {
-  const uint4* slot = memo + 2 * size_t(memo_slot(k0, k1, k2, uint32_t(LL), log2));
-  const uint4 a     = __ldcg(slot);
-  if ((a.w & kMemoStateMask) != kMemoReady || a.x != k0 || a.y != k1 || a.z != k2 || ((a.w >> 16) & 0xFFu) != uint32_t(LL))
-    return 0;
-  const uint4 v = __ldcg(slot + 1);
-  const int n   = int(a.w & 0xFFu);
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  const uint32_t* wp = reinterpret_cast<const uint32_t*>(bytes + (at & ~3));
+  const uint32_t sh  = uint32_t(at & 3) * 8u;
+  uint32_t prev = wp[0];
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
+  for (int q = 0; q < 8; ++q) {
+    uint32_t v = 0;
+    if (4 * q < LL) {
+      const uint32_t next = wp[q + 1];
+      v    = __funnelshift_r(prev, next, sh);
+      prev = next;
+      const int rem = LL - 4 * q;
+      if (rem < 4) v &= (1u << (8 * rem)) - 1u;
+    }
+    k[q] = v;
+  }
+}
+
+// returns the number of ids (written to tok[0..n), tombstones behind them), 0 on a miss
+__device__ __forceinline__ int memo_lookup(const uint4* memo, uint32_t log2, const uint32_t k[8], int LL,
+                                           uint16_t* tok)
+{
+  const uint4* slot = memo + 4 * size_t(memo_slot(k, uint32_t(LL), log2));
+  const uint4 m0    = __ldcg(slot + 2);
+  if ((m0.x & kMemoStateMask) != kMemoReady || ((m0.x >> 16) & 0xFFu) != uint32_t(LL)) return 0;
+  const uint4 m1 = __ldcg(slot + 3);
+  const uint4 a  = __ldcg(slot);
+  const uint4 c  = __ldcg(slot + 1);
+  if (a.x != k[0] || a.y != k[1] || a.z != k[2] || a.w != k[3] || c.x != k[4] || c.y != k[5] || c.z != k[6] ||
+      c.w != k[7])
+    return 0;
+  const int n = int(m0.x & 0xFFu);
+  const uint32_t w[6] = {m0.y, m0.z, m0.w, m1.x, m1.y, m1.z};
+#pragma unroll
+  for (int i = 0; i < kMemoMaxIds; ++i)
     if (i < n) tok[i] = uint16_t(w[i >> 1] >> ((i & 1) * 16));
   for (int i = n; i < LL; ++i) tok[i] = uint16_t(DEAD);
   return n;
 }
 
 // store the finished segment tok[0..LL) (tombstones skipped) under its bytes
-__device__ __forceinline__ void memo_insert(uint4* memo, uint32_t log2, uint32_t k0, uint32_t k1, uint32_t k2, int LL,
+__device__ __forceinline__ void memo_insert(uint4* memo, uint32_t log2, const uint32_t k[8], int LL,
                                             const uint16_t* tok)
 {
-  uint32_t w[4] = {0, 0, 0, 0};
+  uint32_t w[6] = {0, 0, 0, 0, 0, 0};
   int n = 0;
   for (int i = 0; i < LL; ++i) {
     const uint32_t t = tok[i];
     if (t == DEAD) continue;
-    if (n < 8) w[n >> 1] |= t << ((n & 1) * 16);
+    if (n < kMemoMaxIds) w[n >> 1] |= t << ((n & 1) * 16);
     ++n;
   }
-  if (n > 8) return;
-  uint4* slot = memo + 2 * size_t(memo_slot(k0, k1, k2, uint32_t(LL), log2));
-  uint32_t* meta = reinterpret_cast<uint32_t*>(slot) + 3;
+  if (n > kMemoMaxIds) return;
+  uint4* slot    = memo + 4 * size_t(memo_slot(k, uint32_t(LL), log2));
+  uint32_t* meta = reinterpret_cast<uint32_t*>(slot + 2);
   if (atomicCAS(meta, 0u, kMemoBusy) != 0u) return;  // taken (or being written): never replaced
-  uint32_t* p = reinterpret_cast<uint32_t*>(slot);
-  p[0] = k0;
-  p[1] = k1;
-  p[2] = k2;
-  slot[1] = make_uint4(w[0], w[1], w[2], w[3]);
+  slot[0] = make_uint4(k[0], k[1], k[2], k[3]);
+  slot[1] = make_uint4(k[4], k[5], k[6], k[7]);
+  uint32_t* p = reinterpret_cast<uint32_t*>(slot + 2);
+  p[1] = w[0];
+  p[2] = w[1];
+  p[3] = w[2];
+  slot[3] = make_uint4(w[3], w[4], w[5], 0u);
   __threadfence();
   atomicExch(meta, kMemoReady | (uint32_t(LL) << 16) | uint32_t(n));
 }
@@ -819,9 +852,12 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
               miss      = false;
               S.tok[ss] = uint16_t(id);
               for (int i = 1; i < LL; ++i) S.tok[ss + i] = uint16_t(DEAD);
-            } else if (b.memo && memo_lookup(b.memo, b.memo_log2, k0, k1, k2, LL, S.tok + ss) > 0) {
-              miss = false;
             }
+          }
+          if (miss && b.memo) {
+            uint32_t k[8];
+            segment_key8(S.bytes, 16 + ss, LL, k);
+            if (memo_lookup(b.memo, b.memo_log2, k, LL, S.tok + ss) > 0) miss = false;
           }
         }
         const uint32_t bal = __ballot_sync(0xFFFFFFFFu, miss);
@@ -919,10 +955,10 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
           continue;
         }
         if (s >= 0 && !thread_merge_step(S.tok + s, S.rk + s, L, alive, T)) {
-          if (b.memo && L <= 12) {
-            uint32_t k0, k1, k2;
-            segment_key(S.bytes, 16 + s, L, k0, k1, k2);
-            memo_insert(b.memo, b.memo_log2, k0, k1, k2, L, S.tok + s);
+          if (b.memo) {
+            uint32_t k[8];
+            segment_key8(S.bytes, 16 + s, L, k);
+            memo_insert(b.memo, b.memo_log2, k, L, S.tok + s);
           }
           s = -1;
         }
