@@ -6,6 +6,7 @@
   libgputok_b200.so   CUDA kernels + C ABI (nvcc, sm_100a only)
   libgtk_textgen.so   seeded synthetic text generator (gcc, CPU only)
   gputok_gpu*.so      pybind11 module exposing the reference's GpuTokenizer surface (g++)
+  gpu_tokenizer_blockbpe  command-line front end with the reference binary's arguments and output (g++)
 """
 from __future__ import annotations
 
@@ -21,6 +22,7 @@ INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB = os.path.join(HERE, "libgputok_b200.so")
 TEXTGEN = os.path.join(HERE, "libgtk_textgen.so")
 PYMOD = os.path.join(HERE, "gputok_gpu" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
+CLI = os.path.join(HERE, "gpu_tokenizer_blockbpe")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared"]
@@ -68,10 +70,19 @@ def build_pymod(force: bool = False) -> str:
     return PYMOD
 
 
+def build_cli(force: bool = False) -> str:
+    """Command-line front end with the reference binary's arguments and output lines."""
+    src = os.path.join(CSRC, "gpu_tokenizer_blockbpe.cpp")
+    if force or _stale(CLI, [src, os.path.join(INCLUDE, "gputok_b200.h"), LIB]):
+        _run(["g++", "-O2", "-std=c++17", src, "-L", HERE, "-lgputok_b200", "-Wl,-rpath,$ORIGIN", "-o", CLI])
+    return CLI
+
+
 def build_all(force: bool = False) -> None:
     build_cuda(force)
     build_textgen(force)
     build_pymod(force)
+    build_cli(force)
 
 
 if __name__ == "__main__":

@@ -125,7 +125,8 @@ struct gtk_tokenizer {
   mutable std::string last_error;
 
   // table in HBM
-  DevBuf d_slots, d_bpr, d_mor, d_sor, d_adj, d_b2i, d_words;
+  DevBuf d_slots, d_bpr, d_mor, d_sor, d_adj, d_b2i, d_words, d_low_map;
+  int id_space = GTK_IDS_REFERENCE;
   gtk::DeviceTable dtab{};
 
   // arenas
@@ -178,6 +179,7 @@ void upload_table(gtk_tokenizer* h)
   upload(h->d_sor, t.same_of_rank.data(), t.same_of_rank.size(), h->stream);
   upload(h->d_adj, t.adj, sizeof(t.adj), h->stream);
   upload(h->d_b2i, t.byte_to_id, sizeof(t.byte_to_id), h->stream);
+  upload(h->d_low_map, t.gpt2_low_id, sizeof(t.gpt2_low_id), h->stream);
   upload(h->d_words, t.word_slots.data(), t.word_slots.size() * sizeof(gtk::WordSlot), h->stream);
   GTK_CUDA(cudaStreamSynchronize(h->stream));
   h->dtab.slots = h->d_slots.as<uint4>();
@@ -296,6 +298,7 @@ Plan plan_batch(gtk_tokenizer* h, const uint8_t* d_bytes, int64_t n_bytes, const
   b.scan_block_sums = h->d_scan_sums.as<int64_t>();
   b.counters = h->d_counters.as<int32_t>();
   b.totals = h->d_totals.as<int64_t>();
+  b.low_id_map = (h->id_space == GTK_IDS_GPT2) ? h->d_low_map.as<uint16_t>() : nullptr;
   attach_queues(h, b, 0);
   return p;
 }
@@ -475,6 +478,7 @@ gtk::EncodeBuffers slice_buffers(gtk_tokenizer* h, SliceArena& a, const SlicePla
   b.scan_block_sums = a.scan_sums.as<int64_t>();
   b.counters = a.counters.as<int32_t>();
   b.totals = a.totals.as<int64_t>();
+  b.low_id_map = (h->id_space == GTK_IDS_GPT2) ? h->d_low_map.as<uint16_t>() : nullptr;
   attach_queues(h, b, max_bytes);
   return b;
 }
@@ -771,7 +775,7 @@ GTK_API void gtk_destroy(gtk_tokenizer* h)
   if (h->device >= 0) {
     cudaSetDevice(h->device);
     if (h->stream) cudaStreamSynchronize(h->stream);
-    for (DevBuf* b : {&h->d_slots, &h->d_bpr, &h->d_mor, &h->d_sor, &h->d_adj, &h->d_b2i, &h->d_words, &h->d_memo, &h->d_q_short, &h->d_q_long, &h->d_q_huge, &h->d_bytes, &h->d_text_off,
+    for (DevBuf* b : {&h->d_slots, &h->d_bpr, &h->d_mor, &h->d_sor, &h->d_adj, &h->d_b2i, &h->d_words, &h->d_low_map, &h->d_memo, &h->d_q_short, &h->d_q_long, &h->d_q_huge, &h->d_bytes, &h->d_text_off,
                       &h->d_text_chunk_base, &h->d_chunk_off, &h->d_tile_chunk0, &h->d_staging, &h->d_unit_first,
                       &h->d_unit_cnt, &h->d_chunk_cnt, &h->d_unit_base, &h->d_chunk_id_off, &h->d_text_id_off,
                       &h->d_out_ids, &h->d_seg_scratch, &h->d_scan_sums, &h->d_counters, &h->d_totals})
@@ -1056,6 +1060,38 @@ GTK_API int gtk_set_stream(gtk_tokenizer* h, void* cuda_stream)
   cudaSetDevice(h->device);
   cudaStreamSynchronize(h->stream);
   h->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : h->own_stream;
+  return GTK_OK;
+}
+
+GTK_API int gtk_set_id_space(gtk_tokenizer* h, int id_space)
+{
+  if (!h) return GTK_ERR_INVALID_ARG;
+  std::lock_guard<std::mutex> lock(h->mu);
+  if (id_space != GTK_IDS_REFERENCE && id_space != GTK_IDS_GPT2) return h->fail(GTK_ERR_INVALID_ARG, "unknown id space");
+  h->id_space = id_space;
+  return GTK_OK;
+}
+
+GTK_API int gtk_write_token_strings(const gtk_tokenizer* h, const char* path, const int32_t* ids,
+                                    const int64_t* chunk_id_offsets, int64_t n_chunks)
+{
+  if (!h || !path || n_chunks < 0 || (n_chunks > 0 && (!ids || !chunk_id_offsets))) return GTK_ERR_INVALID_ARG;
+  FILE* f = std::fopen(path, "wb");
+  if (!f) return h->fail(GTK_ERR_IO, std::string("Failed to open output file for writing: ") + path);
+  const auto& sym = h->table->id_to_symbols;
+  std::string line;
+  for (int64_t c = 0; c < n_chunks; ++c) {
+    line.clear();
+    for (int64_t i = chunk_id_offsets[c]; i < chunk_id_offsets[c + 1]; ++i) {
+      const int32_t id = ids[i];
+      if (id < 0 || size_t(id) >= sym.size()) line += std::to_string(id);  // raw id, as the reference's fallback
+      else line += sym[size_t(id)];
+      if (i + 1 < chunk_id_offsets[c + 1]) line += ' ';
+    }
+    line += '\n';
+    std::fwrite(line.data(), 1, line.size(), f);
+  }
+  std::fclose(f);
   return GTK_OK;
 }
 

@@ -71,6 +71,7 @@ struct EncodeBuffers {
   int64_t* chunk_id_off;     // [chunk_cap+1] packed id offset of each chunk (caller visible)
   int64_t* text_id_off;      // [n_texts+1] or nullptr
   int32_t* out_ids;
+  const uint16_t* low_id_map;  // nullptr, or 256 entries: output id of every id < 256 (GPT-2 id space)
   int64_t out_capacity;
   // scratch
   uint16_t* seg_scratch;     // per-CTA workspace for segments that do not fit in shared memory

@@ -1502,7 +1502,10 @@ __global__ void __launch_bounds__(kOptThreads) k_pack_tiles(EncodeBuffers b)
     __syncthreads();
     const int64_t dst = b.unit_base[k];
     for (int j = tid; j < total; j += kOptThreads)
-      if (dst + j < b.out_capacity) b.out_ids[dst + j] = S.out[j];
+      if (dst + j < b.out_capacity) {
+        const uint32_t t = uint32_t(S.out[j]);
+        b.out_ids[dst + j] = int32_t((b.low_id_map && t < 256u) ? uint32_t(__ldg(b.low_id_map + t)) : t);
+      }
   }
 }
 
@@ -1589,7 +1592,10 @@ __global__ void __launch_bounds__(kOptThreads) k_encode_small(EncodeBuffers b, D
     const int64_t src = b.unit_first[u], dst = b.unit_base[u];
     const int m       = b.unit_cnt[u];
     for (int j = tid; j < m; j += kOptThreads)
-      if (dst + j < b.out_capacity) b.out_ids[dst + j] = int32_t(b.staging[src + j]);
+      if (dst + j < b.out_capacity) {
+        const uint32_t t = b.staging[src + j];
+        b.out_ids[dst + j] = int32_t((b.low_id_map && t < 256u) ? uint32_t(__ldg(b.low_id_map + t)) : t);
+      }
   }
   if (tid == 0) {
     b.totals[0] = C;
@@ -1649,14 +1655,18 @@ __global__ void __launch_bounds__(kBaseThreads) k_merge_base(EncodeBuffers b, De
 __global__ void __launch_bounds__(256) k_pack(const uint16_t* __restrict__ staging, const int64_t* __restrict__ first,
                                               const int32_t* __restrict__ cnt, const int64_t* __restrict__ base,
                                               int64_t n_units_imm, const int64_t* n_units_ptr,
-                                              int32_t* __restrict__ out, int64_t capacity)
+                                              int32_t* __restrict__ out, int64_t capacity,
+                                              const uint16_t* __restrict__ low_id_map)
 {
   const int64_t U = n_units_ptr ? *n_units_ptr : n_units_imm;
   for (int64_t u = blockIdx.x; u < U; u += gridDim.x) {
     const int64_t src = first[u], dst = base[u];
     const int m = cnt[u];
     for (int j = threadIdx.x; j < m; j += blockDim.x)
-      if (dst + j < capacity) out[dst + j] = int32_t(staging[src + j]);
+      if (dst + j < capacity) {
+        const uint32_t t = staging[src + j];
+        out[dst + j]     = int32_t((low_id_map && t < 256u) ? uint32_t(__ldg(low_id_map + t)) : t);
+      }
   }
 }
 
@@ -1736,10 +1746,10 @@ int launch_pack(const EncodeBuffers& b, int mode_base, int grid, cudaStream_t st
   if (b.n_bytes <= 0) return 0;
   if (mode_base) {
     k_pack<<<grid, 256, 0, stream>>>(b.staging, b.chunk_off, b.chunk_cnt, b.chunk_id_off, 0, b.totals + 0, b.out_ids,
-                                     b.out_capacity);
+                                     b.out_capacity, b.low_id_map);
   } else {
     k_pack<<<grid, 256, 0, stream>>>(b.staging, b.unit_first, b.unit_cnt, b.unit_base, b.n_tiles, nullptr, b.out_ids,
-                                     b.out_capacity);
+                                     b.out_capacity, b.low_id_map);
   }
   return 1;
 }

@@ -93,6 +93,17 @@ HostTable::HostTable(const std::string& merges_path)
   int cp_of_byte[256];
   byte_symbol_codepoints(cp_of_byte);
   for (int b = 0; b < 256; ++b) byte_to_id[b] = uint16_t(add_token(utf8_of(cp_of_byte[b])));
+  // GPT-2's vocabulary lists the byte symbols in bytes_to_unicode order: the 188 bytes that keep
+  // their code point first (in byte order), then the 68 remapped bytes (in byte order).
+  {
+    int next_kept = 0, next_moved = 188;
+    for (int b = 0; b < 256; ++b) {
+      const bool keeps = cp_of_byte[b] == b;
+      for (int id = 0; id < 256; ++id)
+        if (byte_to_id[b] == id) gpt2_low_id[id] = uint16_t(keeps ? next_kept : next_moved);
+      if (keeps) ++next_kept; else ++next_moved;
+    }
+  }
 
   FILE* f = std::fopen(merges_path.c_str(), "rb");
   if (!f) throw std::runtime_error("Failed to open merges file: " + merges_path);

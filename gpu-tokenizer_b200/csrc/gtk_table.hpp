@@ -70,6 +70,7 @@ class HostTable {
   std::vector<std::string> id_to_bytes;                 // token id -> raw bytes ("" + !decodable if impossible)
   std::vector<uint8_t> decodable;
   uint16_t byte_to_id[256];
+  uint16_t gpt2_low_id[256];  // id < 256 (reference id space) -> id of the same byte token in GPT-2's own vocabulary
 
   // merges, unique pairs in rank order
   std::vector<MergeRow> rows;

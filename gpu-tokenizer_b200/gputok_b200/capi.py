@@ -67,6 +67,8 @@ def load_library() -> C.CDLL:
     lib.gtk_token_symbols.restype = i32
     lib.gtk_set_stream.argtypes = [vp, vp]
     lib.gtk_set_tuning.argtypes = [vp, C.c_int, C.c_int]
+    lib.gtk_set_id_space.argtypes = [vp, C.c_int]
+    lib.gtk_write_token_strings.argtypes = [vp, C.c_char_p, vp, vp, i64]
     lib.gtk_encode_chunks_noalloc.argtypes = [vp, vp, i64, vp, i64, i32, vp, vp]
     lib.gtk_pinned_alloc.argtypes = [C.c_size_t]
     lib.gtk_pinned_alloc.restype = vp
@@ -152,6 +154,19 @@ class Tokenizer:
     def set_stream(self, cuda_stream: int | None) -> None:
         """Run later GPU work on the caller's stream (e.g. ``torch.cuda.current_stream().cuda_stream``)."""
         self._check(self._lib.gtk_set_stream(self._h, cuda_stream or None))
+
+    def set_id_space(self, gpt2: bool) -> None:
+        """False (default): ids as the reference produces them (ids < 256 are byte values);
+        True: ids < 256 remapped to GPT-2's own vocabulary order (feedable to a GPT-2 model)."""
+        self._check(self._lib.gtk_set_id_space(self._h, 1 if gpt2 else 0))
+
+    def write_token_strings(self, path: str, ids, chunk_id_offsets) -> None:
+        """One chunk per line, tokens as GPT-2 symbol strings separated by spaces (the reference's
+        data/output/gpu_tokens_blockbpe.txt format)."""
+        a = np.ascontiguousarray(ids, dtype=np.int32)
+        off = np.ascontiguousarray(chunk_id_offsets, dtype=np.int64)
+        self._check(self._lib.gtk_write_token_strings(self._h, os.fsencode(path), a.ctypes.data, off.ctypes.data,
+                                                      len(off) - 1))
 
     def set_tuning(self, pipeline: int = 0, memo: bool = False) -> None:
         """pipeline: 0 auto, 1 fused tile kernel, 2 split (queues + per-segment kernels); memo: call-local

@@ -173,6 +173,23 @@ GTK_API int32_t gtk_token_symbols(const gtk_tokenizer* h, int32_t id, char* buf,
  * time it with its own events.  The entry points stay synchronous on return. */
 GTK_API int gtk_set_stream(gtk_tokenizer* h, void* cuda_stream);
 
+/* Id space of the ids returned by the GPU encode entry points (no counterpart in the reference,
+ * whose ids 0..255 are the byte values -- a permutation of GPT-2's own ids for the byte tokens,
+ * e.g. the space byte is 32 here and 220 in GPT-2's vocab.json; ids >= 256 coincide).
+ *   GTK_IDS_REFERENCE (default)  ids as the reference produces them
+ *   GTK_IDS_GPT2                 ids < 256 are remapped to their position in GPT-2's byte-symbol
+ *                                order, so the ids can be fed to a GPT-2 model directly
+ * gtk_decode / gtk_write_token_strings expect GTK_IDS_REFERENCE ids. */
+enum { GTK_IDS_REFERENCE = 0, GTK_IDS_GPT2 = 1 };
+GTK_API int gtk_set_id_space(gtk_tokenizer* h, int id_space);
+
+/* Replaces the token-string writer of the standalone binary (gputok_blockbpe.cu:841-865): writes
+ * the chunks' tokens as GPT-2 symbol strings, separated by one space, one chunk per line -- the
+ * format of the reference's data/output/gpu_tokens_blockbpe.txt.  chunk_id_offsets[n_chunks+1]
+ * delimits the chunks inside ids (as returned by gtk_result_view). */
+GTK_API int gtk_write_token_strings(const gtk_tokenizer* h, const char* path, const int32_t* ids,
+                                    const int64_t* chunk_id_offsets, int64_t n_chunks);
+
 /* Tuning knobs of GTK_MODE_OPT (no counterpart in the reference; results never depend on them).
  *   pipeline  GTK_PIPELINE_AUTO (default), GTK_PIPELINE_FUSED: one tile kernel merges everything;
  *             GTK_PIPELINE_SPLIT: segments of more than 12 bytes leave the tile kernel through a

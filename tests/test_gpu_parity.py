@@ -269,6 +269,61 @@ def test_device_resident_entry_point(lib, merges_path, oracle):
     assert e.value.code == 4
 
 
+def test_gpt2_id_space(lib, merges_path, oracle):
+    """Optional output in GPT-2's own id space: ids < 256 move to their position in GPT-2's byte-symbol order,
+    ids >= 256 are unchanged."""
+    t = make_tok(lib, merges_path, 2048)
+    ref_ids, _, _, _ = t.encode(b"Hello world")
+    t.set_id_space(True)
+    ids, _, _, _ = t.encode(b"Hello world")
+    assert ids.tolist() == [15496, 995] == ref_ids.tolist()          # whole-word tokens: same in both spaces
+    raw = bytes(range(256)) + b" \n!~"
+    ids, _, _, _ = t.encode(raw)
+    t.set_id_space(False)
+    ref, _, _, _ = t.encode(raw)
+    order = [b for b in range(256) if 33 <= b <= 126 or 161 <= b <= 172 or 174 <= b <= 255]
+    order += [b for b in range(256) if b not in order]                # GPT-2 bytes_to_unicode order
+    gpt2_of_byte = {b: i for i, b in enumerate(order)}
+    want = [gpt2_of_byte[x] if x < 256 else x for x in ref.tolist()]
+    assert ids.tolist() == want
+    assert gpt2_of_byte[0x20] == 220 and gpt2_of_byte[ord("!")] == 0 and gpt2_of_byte[0] == 188
+    big = lib.TextGen(5).text(6 << 20, mix=lib.MIX_STRESS)            # multi-kernel path as well
+    ref, _, _, _ = t.encode(big)
+    t.set_id_space(True)
+    ids, _, _, _ = t.encode(big)
+    lut = np.arange(65536, dtype=np.int32)
+    lut[:256] = [gpt2_of_byte[b] for b in range(256)]
+    assert np.array_equal(ids, lut[ref])
+
+
+def test_standalone_cli_reproduces_reference_run(native_built, merges_path, novel, tmp_path):
+    """The command-line front end: reference argv, reference stdout lines (the regex of
+    benchmark_tokenizer_scaling.py:155-157 must match), exit code 0 on CPU == GPU, and an output file
+    with the sha256 of the reference's committed data/output/gpu_tokens_blockbpe.txt."""
+    import hashlib
+    import json
+    import re
+    import subprocess
+
+    from conftest import GOLDEN
+
+    text = tmp_path / "novel.txt"
+    text.write_bytes(novel)
+    out = tmp_path / "tokens.txt"
+    env = dict(os.environ, GTK_MERGES=merges_path, GTK_OUTPUT=str(out))
+    want = json.load(open(os.path.join(GOLDEN, "MANIFEST.json")))["sources"]["data/output/gpu_tokens_blockbpe.txt"]
+    for extra in ([], ["opt"]):
+        r = subprocess.run([native_built.CLI, "2048", str(text)] + extra, env=env, capture_output=True, text=True,
+                           timeout=300)
+        assert r.returncode == 0, r.stderr
+        m = re.search(r"GPU BlockBPE-style greedy kernel time.*:\s*([0-9.]+)\s*ms", r.stdout)
+        assert m and float(m.group(1)) > 0
+        assert "CPU vs GPU token match (greedy Algorithm 1): OK" in r.stdout
+        assert "Loaded BPE merges: 50000, vocab size: 50256" in r.stderr
+        assert "Tokenized full text into 348 chunk(s), max tokens per chunk: 2048" in r.stderr
+        assert hashlib.sha256(out.read_bytes()).hexdigest() == want
+
+
 def test_pybind_methods_on_gpu(lib, merges_path, oracle):
     import gputok_gpu
 

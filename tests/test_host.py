@@ -140,6 +140,24 @@ def test_pybind_surface(native_built, merges_path, oracle):
     assert tok.table_info()["vocab_size"] == 50256
 
 
+def test_token_string_writer_reproduces_the_reference_output_file(native_built, merges_path, novel, tmp_path):
+    """gtk_write_token_strings == the writer of the standalone binary (gputok_blockbpe.cu:841-865): the file it
+    writes for the sample novel at 2048-byte chunks has the sha256 of the reference's committed
+    data/output/gpu_tokens_blockbpe.txt (recorded in tests/golden/MANIFEST.json)."""
+    import hashlib
+    import json
+
+    from gputok_b200 import Tokenizer
+
+    t = Tokenizer(merges_path, 2048, 50, device=-1)
+    ids, _, coff = t.encode_cpu(novel)
+    out = tmp_path / "gpu_tokens_blockbpe.txt"
+    t.write_token_strings(str(out), ids, coff)
+    want = json.load(open(os.path.join(GOLDEN, "MANIFEST.json")))["sources"]["data/output/gpu_tokens_blockbpe.txt"]
+    assert hashlib.sha256(out.read_bytes()).hexdigest() == want
+    assert out.read_bytes().count(b"\n") == 348
+
+
 def test_textgen_is_deterministic_and_shaped(native_built):
     from gputok_b200 import MIX_STRESS, TextGen
 
