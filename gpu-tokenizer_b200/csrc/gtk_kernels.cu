@@ -854,7 +854,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
               for (int i = 1; i < LL; ++i) S.tok[ss + i] = uint16_t(DEAD);
             }
           }
-          if (miss && b.memo) {
+          if (!SPLIT && miss && b.memo) {
             uint32_t k[8];
             segment_key8(S.bytes, 16 + ss, LL, k);
             if (memo_lookup(b.memo, b.memo_log2, k, LL, S.tok + ss) > 0) miss = false;
@@ -885,7 +885,10 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
     if (SPLIT) {
       const int nm = S.nmiss;
       int mybig    = 0;
-      for (int j = tid; j < nm; j += kOptThreads) mybig += int(next_cut(S.cut, S.seg[j]) - int(S.seg[j]) > 12);
+      // with the memo every miss leaves through the queue (the consumer owns the memo); without it only
+      // segments of more than 12 bytes do
+      const int keep_max = b.memo ? 1 : 12;
+      for (int j = tid; j < nm; j += kOptThreads) mybig += int(next_cut(S.cut, S.seg[j]) - int(S.seg[j]) > keep_max);
       if (mybig) atomicAdd(&S.nbig, mybig);
       __syncthreads();
       const int nbig = S.nbig;
@@ -897,7 +900,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
         const int ss0 = S.seg[j];
         const int LL0 = next_cut(S.cut, ss0) - ss0;
         const uint32_t ent = uint32_t(ss0) | (uint32_t(LL0) << 16);
-        if (LL0 <= 12) continue;
+        if (LL0 <= keep_max) continue;
         const int64_t at = qb + atomicAdd(&S.qfill, 1);
         if (at >= b.q_short_cap) continue;  // a reservation that does not fit is filled with null entries
         uint4* e = b.q_short + 3 * at;
@@ -942,7 +945,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
             } else {
               const int ss0 = S.seg[j];
               const int LL0 = next_cut(S.cut, ss0) - ss0;
-              if (!(queued && LL0 > 12)) {  // queued segments are merged by a later kernel
+              if (!(queued && LL0 > (b.memo ? 1 : 12))) {  // queued segments are merged by a later kernel
                 s     = ss0;
                 L     = LL0;
                 alive = (L >= 32) ? 0xFFFFFFFFu : ((1u << L) - 1u);
@@ -955,7 +958,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
           continue;
         }
         if (s >= 0 && !thread_merge_step(S.tok + s, S.rk + s, L, alive, T)) {
-          if (b.memo) {
+          if (!SPLIT && b.memo) {
             uint32_t k[8];
             segment_key8(S.bytes, 16 + s, L, k);
             memo_insert(b.memo, b.memo_log2, k, L, S.tok + s);
@@ -1272,6 +1275,7 @@ __global__ void __launch_bounds__(kShortThreads) k_merge_short(EncodeBuffers b, 
   int L = 0;
   uint32_t alive = 0;
   bool drained = false;
+  uint32_t key[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // bytes of the current segment (memo key)
   for (;;) {
     // lanes without a segment take the next queue entry (bytes travel with the entry) and set up
     // their token and rank arrays; the entries the warp will take next are prefetched into L1
@@ -1292,21 +1296,52 @@ __global__ void __launch_bounds__(kShortThreads) k_merge_short(EncodeBuffers b, 
         if (j < batch_end) {
           const uint4* e = b.q_short + 3 * j;
           if (j + want < batch_end) asm volatile("prefetch.global.L1 [%0];" ::"l"(e + 3 * want));
-          const uint2 head = __ldg(reinterpret_cast<const uint2*>(e));
-          L = int(head.y >> 16);
+          const uint4 e0 = __ldg(e);
+          L = int(e0.y >> 16);
           if (L >= 2) {
-            pos   = int64_t(head.x) | (int64_t(head.y & 0xFFFFu) << 32);
-            alive = (L >= 32) ? 0xFFFFFFFFu : ((1u << L) - 1u);
-            const uint8_t* pb = reinterpret_cast<const uint8_t*>(e) + 8;
-            uint32_t prev     = __ldg(pb);
-            tok[0] = identity_ids ? uint16_t(prev) : __ldg(T.byte_to_id + prev);
-            for (int i = 1; i < L; ++i) {
-              const uint32_t cur = __ldg(pb + i);
-              tok[i]    = identity_ids ? uint16_t(cur) : __ldg(T.byte_to_id + cur);
-              rk[i - 1] = __ldg(T.byte_pair_rank + ((prev << 8) | cur));
-              prev      = cur;
+            pos = int64_t(e0.x) | (int64_t(e0.y & 0xFFFFu) << 32);
+            bool hit = false;
+            if (b.memo) {  // an earlier occurrence of the same bytes in this call: copy its ids
+              const uint4 e1 = __ldg(e + 1), e2 = __ldg(e + 2);
+              key[0] = e0.z; key[1] = e0.w; key[2] = e1.x; key[3] = e1.y;
+              key[4] = e1.z; key[5] = e1.w; key[6] = e2.x; key[7] = e2.y;
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const int rem = L - 4 * q;
+                if (rem <= 0) key[q] = 0u;
+                else if (rem < 4) key[q] &= (1u << (8 * rem)) - 1u;
+              }
+              const uint4* slot = b.memo + 4 * size_t(memo_slot(key, uint32_t(L), b.memo_log2));
+              const uint4 m0    = __ldcg(slot + 2);
+              if ((m0.x & kMemoStateMask) == kMemoReady && ((m0.x >> 16) & 0xFFu) == uint32_t(L)) {
+                const uint4 m1 = __ldcg(slot + 3), a = __ldcg(slot), c = __ldcg(slot + 1);
+                if (a.x == key[0] && a.y == key[1] && a.z == key[2] && a.w == key[3] && c.x == key[4] &&
+                    c.y == key[5] && c.z == key[6] && c.w == key[7]) {
+                  const int n = int(m0.x & 0xFFu);
+                  const uint32_t w[6] = {m0.y, m0.z, m0.w, m1.x, m1.y, m1.z};
+#pragma unroll
+                  for (int i = 0; i < kMemoMaxIds; ++i)
+                    if (i < n) b.staging[pos + i] = uint16_t(w[i >> 1] >> ((i & 1) * 16));
+                  for (int i = n; i < L; ++i) b.staging[pos + i] = uint16_t(DEAD);
+                  hit = true;
+                }
+              }
             }
-            rk[L - 1] = uint16_t(NONE);
+            if (hit) {
+              pos = -1;
+            } else {
+              alive = (L >= 32) ? 0xFFFFFFFFu : ((1u << L) - 1u);
+              const uint8_t* pb = reinterpret_cast<const uint8_t*>(e) + 8;
+              uint32_t prev     = __ldg(pb);
+              tok[0] = identity_ids ? uint16_t(prev) : __ldg(T.byte_to_id + prev);
+              for (int i = 1; i < L; ++i) {
+                const uint32_t cur = __ldg(pb + i);
+                tok[i]    = identity_ids ? uint16_t(cur) : __ldg(T.byte_to_id + cur);
+                rk[i - 1] = __ldg(T.byte_pair_rank + ((prev << 8) | cur));
+                prev      = cur;
+              }
+              rk[L - 1] = uint16_t(NONE);
+            }
           }
         } else if (batch_next >= count) {
           drained = true;
@@ -1319,7 +1354,30 @@ __global__ void __launch_bounds__(kShortThreads) k_merge_short(EncodeBuffers b, 
       continue;
     }
     if (pos >= 0 && !lane_merge_step(tok, rk, L, alive, T)) {
-      for (int i = 0; i < L; ++i) b.staging[pos + i] = tok[i];  // tokens and tombstones, position by position
+      uint32_t w[6] = {0, 0, 0, 0, 0, 0};
+      int n = 0;
+      for (int i = 0; i < L; ++i) {  // tokens and tombstones, position by position
+        const uint32_t t = tok[i];
+        b.staging[pos + i] = uint16_t(t);
+        if (t != DEAD) {
+          if (n < kMemoMaxIds) w[n >> 1] |= t << ((n & 1) * 16);
+          ++n;
+        }
+      }
+      if (b.memo && n <= kMemoMaxIds) {  // publish for later occurrences (write-once slot)
+        uint4* slot    = b.memo + 4 * size_t(memo_slot(key, uint32_t(L), b.memo_log2));
+        uint32_t* meta = reinterpret_cast<uint32_t*>(slot + 2);
+        if (atomicCAS(meta, 0u, kMemoBusy) == 0u) {
+          slot[0] = make_uint4(key[0], key[1], key[2], key[3]);
+          slot[1] = make_uint4(key[4], key[5], key[6], key[7]);
+          meta[1] = w[0];
+          meta[2] = w[1];
+          meta[3] = w[2];
+          slot[3] = make_uint4(w[3], w[4], w[5], 0u);
+          __threadfence();
+          atomicExch(meta, kMemoReady | (uint32_t(L) << 16) | uint32_t(n));
+        }
+      }
       pos = -1;
     }
   }
