@@ -319,6 +319,15 @@ def main() -> None:
     wall_ms = (time.perf_counter() - t0) * 1e3
     dev_ms = ev0.elapsed_time(ev1)  # CUDA events on the stream the kernels run on
     step_ms = allmax(dev_ms / args.steps)
+    # per-GPU load imbalance: max / mean of the ranks' own step times (1.0 = perfectly balanced)
+    if world > 1:
+        mine = torch.tensor([dev_ms / args.steps], dtype=torch.float64, device="cuda")
+        every = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        per_gpu_ms = [float(t.item()) for t in every]
+    else:
+        per_gpu_ms = [dev_ms / args.steps]
+    imbalance = max(per_gpu_ms) / (sum(per_gpu_ms) / len(per_gpu_ms))
     total_bytes = allsum(float(n_bytes))
     total_ids = allsum(float(n_ids))
     value = total_bytes / (step_ms * 1e-3) / 1e6
@@ -398,7 +407,7 @@ def main() -> None:
             "vs_baseline": None, "dtype": "u16", "data": "synthetic",
             "config": dict(desc, mode=args.mode, parallelism=f"byte-range shards x{world}, no collectives"),
             "tokens_per_s": total_ids / (step_ms * 1e-3), "tokens_per_byte": tau, "chunks_per_gpu": int(n_chunks),
-            "wall_ms_per_step": wall_ms / args.steps,
+            "wall_ms_per_step": wall_ms / args.steps, "per_gpu_ms": per_gpu_ms, "imbalance": imbalance,
             "stage_ms": {k: float(v / args.steps) for k, v in zip(("chunker", "merge", "scan", "pack", "pipeline"),
                                                                stage_acc)},
             "e2e": {"value": e2e_value, "unit": "MB/s", "h2d_bytes_per_step": int(h2d),
