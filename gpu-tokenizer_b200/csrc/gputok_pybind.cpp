@@ -3,7 +3,7 @@
 // thin wrapper over the C ABI of include/gputok_b200.h.  No CUDA code here.
 //
 //   GpuTokenizer(merges_path, chunk_tokens=2048, max_iters=50, device=0)
-//   .tokenize_batch(texts)               -> (list[list[int]], kernel_ms)
+//   .tokenize_batch(texts, merge_rule="greedy") -> (list[list[int]], kernel_ms)
 //   .tokenize_batch_blockbpe_base(texts) -> (list[list[int]], kernel_ms)
 //   .tokenize_batch_cpu(texts, merge_rule="greedy") -> list[list[int]]
 // plus array-returning variants that skip the per-token Python objects:
@@ -216,11 +216,14 @@ PYBIND11_MODULE(gputok_gpu, m)
   py::class_<GpuTokenizer>(m, "GpuTokenizer")
     .def(py::init<const std::string&, int, int, int>(), py::arg("merges_path"), py::arg("chunk_tokens") = 2048,
          py::arg("max_iters") = 50, py::arg("device") = 0)
-    .def("tokenize_batch", [](GpuTokenizer& self, const std::vector<std::string>& texts) {
-           return self.tokenize(texts, GTK_MODE_OPT);
-         }, py::arg("texts"),
-         "Tokenize a batch of UTF-8 strings with the segment-parallel kernel.\n"
-         "Returns (list[list[int]], kernel_time_ms).")
+    .def("tokenize_batch", [](GpuTokenizer& self, const std::vector<std::string>& texts, const std::string& rule) {
+           if (rule == "greedy") return self.tokenize(texts, GTK_MODE_OPT);
+           if (rule == "localmin") return self.tokenize(texts, GTK_MODE_LOCALMIN);
+           throw std::invalid_argument("merge_rule must be 'greedy' or 'localmin'");
+         }, py::arg("texts"), py::arg("merge_rule") = "greedy",
+         "Tokenize a batch of UTF-8 strings with the segment-parallel kernel (greedy rule).\n"
+         "merge_rule='localmin' runs the reference method's own rule (local minimum, max_iters passes,\n"
+         "per chunk) on the GPU instead.  Returns (list[list[int]], kernel_time_ms).")
     .def("tokenize_batch_blockbpe_base", [](GpuTokenizer& self, const std::vector<std::string>& texts) {
            return self.tokenize(texts, GTK_MODE_BASE);
          }, py::arg("texts"),

@@ -322,15 +322,16 @@ void run_front(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* lau
   if (!ev) ev = h->ev;
   GTK_CUDA(cudaMemsetAsync(b.counters, 0, 64, s));
   GTK_CUDA(cudaMemsetAsync(b.chunk_cnt, 0, size_t(b.chunk_cap + 1) * 4, s));
-  if (b.memo && mode != GTK_MODE_BASE) GTK_CUDA(cudaMemsetAsync(b.memo, 0, (size_t(1) << b.memo_log2) * 64, s));
+  if (b.memo && mode == GTK_MODE_OPT) GTK_CUDA(cudaMemsetAsync(b.memo, 0, (size_t(1) << b.memo_log2) * 64, s));
   GTK_CUDA(cudaEventRecord(ev[0], s));
   *launches += gtk::launch_chunker(b, s);
   GTK_CUDA(cudaEventRecord(ev[1], s));
   if (mode == GTK_MODE_BASE) *launches += gtk::launch_merge_base(b, h->dtab, h->base_grid, s);
+  else if (mode == GTK_MODE_LOCALMIN) *launches += gtk::launch_merge_localmin(b, h->dtab, h->base_grid, h->max_iters, s);
   else if (use_split(b, mode)) *launches += gtk::launch_merge_split(b, h->dtab, h->sm_count, h->opt_grid, s);
   else *launches += gtk::launch_merge_opt(b, h->dtab, h->opt_grid, s);
   GTK_CUDA(cudaEventRecord(ev[2], s));
-  *launches += gtk::launch_output_scans(b, mode == GTK_MODE_BASE, s);
+  *launches += gtk::launch_output_scans(b, mode != GTK_MODE_OPT, s);
   GTK_CUDA(cudaEventRecord(ev[3], s));
   GTK_CUDA(cudaGetLastError());
   int64_t* ht = pinned_totals ? pinned_totals : h->h_totals.as<int64_t>();
@@ -344,7 +345,7 @@ void run_pack(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* laun
   if (!ev) ev = h->ev;
   GTK_CUDA(cudaEventRecord(ev[5], s));
   if (use_split(b, mode)) *launches += gtk::launch_pack_split(b, h->sm_count * 8, s);
-  else *launches += gtk::launch_pack(b, mode == GTK_MODE_BASE, h->sm_count * 8, s);
+  else *launches += gtk::launch_pack(b, mode != GTK_MODE_OPT, h->sm_count * 8, s);
   GTK_CUDA(cudaEventRecord(ev[4], s));
   GTK_CUDA(cudaGetLastError());
 }
@@ -826,7 +827,7 @@ GTK_API int gtk_encode_device(gtk_tokenizer* h, int mode, const uint8_t* d_bytes
   if (!h) return GTK_ERR_INVALID_ARG;
   std::lock_guard<std::mutex> lock(h->mu);
   if (h->device < 0) return h->fail(GTK_ERR_NO_DEVICE, "host-only handle: no GPU entry points");
-  if (mode != GTK_MODE_OPT && mode != GTK_MODE_BASE) return h->fail(GTK_ERR_INVALID_ARG, "unknown mode");
+  if (mode != GTK_MODE_OPT && mode != GTK_MODE_BASE && mode != GTK_MODE_LOCALMIN) return h->fail(GTK_ERR_INVALID_ARG, "unknown mode");
   if (n_bytes < 0 || n_texts < 0) return h->fail(GTK_ERR_INVALID_ARG, "negative size");
   if (n_ids) *n_ids = 0;
   if (n_chunks) *n_chunks = 0;
@@ -874,7 +875,7 @@ GTK_API int gtk_encode(gtk_tokenizer* h, int mode, const uint8_t* bytes, const i
   if (!h) return GTK_ERR_INVALID_ARG;
   std::lock_guard<std::mutex> lock(h->mu);
   if (h->device < 0) return h->fail(GTK_ERR_NO_DEVICE, "host-only handle: no GPU entry points");
-  if (mode != GTK_MODE_OPT && mode != GTK_MODE_BASE) return h->fail(GTK_ERR_INVALID_ARG, "unknown mode");
+  if (mode != GTK_MODE_OPT && mode != GTK_MODE_BASE && mode != GTK_MODE_LOCALMIN) return h->fail(GTK_ERR_INVALID_ARG, "unknown mode");
   if (int rc = validate_offsets(h, text_offsets, n_texts)) return rc;
   if (kernel_ms) *kernel_ms = 0.f;
   h->result_is_cpu = false;

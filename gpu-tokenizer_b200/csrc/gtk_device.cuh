@@ -99,6 +99,7 @@ int launch_merge_opt(const EncodeBuffers& b, const DeviceTable& t, int grid, cud
 int launch_merge_split(const EncodeBuffers& b, const DeviceTable& t, int sm_count, int grid_front, cudaStream_t stream);
 int launch_pack_split(const EncodeBuffers& b, int grid, cudaStream_t stream);
 int launch_merge_base(const EncodeBuffers& b, const DeviceTable& t, int grid, cudaStream_t stream);
+int launch_merge_localmin(const EncodeBuffers& b, const DeviceTable& t, int grid, int max_iters, cudaStream_t stream);
 int launch_output_scans(const EncodeBuffers& b, int mode_base, cudaStream_t stream);
 int launch_pack(const EncodeBuffers& b, int mode_base, int grid, cudaStream_t stream);
 // Whole pipeline in one single-CTA kernel for small batches; totals[0..2] receive n_chunks, n_ids, status.

@@ -1708,6 +1708,105 @@ __global__ void __launch_bounds__(kBaseThreads) k_merge_base(EncodeBuffers b, De
 }
 
 // ------------------------------------------------------------------------------------------------
+// local-minimum rule, one CTA per chunk (GTK_MODE_LOCALMIN).  The reference's tokenize_batch runs
+// this rule, not Algorithm 1 (bpe_merge_kernel_optimized, gputok_binding.cu:290-414): per pass
+// every adjacent pair gets its rank; a mergeable pair is merged unless its left neighbour ranks
+// strictly lower or its right neighbour ranks lower or equal; all such pairs merge in the same
+// pass; at most max_iters passes.  The reference compacts with one thread; here the compaction is
+// the in-place ballot/popc routine.
+// ------------------------------------------------------------------------------------------------
+template <int NW>
+__device__ int compact_tokens(uint16_t* tok, int len, GroupScratch* gs)
+{
+  constexpr int G = NW * 32, E = 4;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t lt = lanemask_lt();
+  int out = 0;
+  for (int base = 0; base < len; base += G * E) {
+    uint16_t t[E];
+    uint32_t bal[E];
+    int wt = 0;
+#pragma unroll
+    for (int k = 0; k < E; ++k) {
+      const int i = base + warp * 32 * E + k * 32 + lane;
+      t[k]   = (i < len) ? tok[i] : uint16_t(DEAD);
+      bal[k] = __ballot_sync(0xFFFFFFFFu, t[k] != DEAD);
+      wt += __popc(bal[k]);
+    }
+    if (lane == 0) gs->wsum[warp] = uint32_t(wt);
+    __syncthreads();
+    int pre = 0, tot = 0;
+    for (int w = 0; w < NW; ++w) {
+      const int x = int(gs->wsum[w]);
+      if (w < warp) pre += x;
+      tot += x;
+    }
+    int o = out + pre;
+#pragma unroll
+    for (int k = 0; k < E; ++k) {
+      if (t[k] != DEAD) tok[o + __popc(bal[k] & lt)] = t[k];
+      o += __popc(bal[k]);
+    }
+    out += tot;
+    __syncthreads();
+  }
+  return out;
+}
+
+__global__ void __launch_bounds__(kBaseThreads) k_merge_localmin(EncodeBuffers b, DeviceTable T, int max_iters)
+{
+  __shared__ uint16_t s_tok[kBaseSmemTokens];
+  __shared__ uint16_t s_rk[kBaseSmemTokens];
+  __shared__ GroupScratch gs;
+  __shared__ int ticket;
+  const int tid   = threadIdx.x;
+  const int64_t C = b.totals[0];
+  int* status     = b.counters + 1;
+  for (;;) {
+    __syncthreads();
+    if (tid == 0) ticket = atomicAdd(b.counters + 2, 1);
+    __syncthreads();
+    const int64_t c = ticket;
+    if (c >= C) break;
+    const int64_t cs  = b.chunk_off[c];
+    const int64_t L64 = b.chunk_off[c + 1] - cs;
+    uint16_t *tok = s_tok, *rk = s_rk;
+    if (L64 > kBaseSmemTokens) {
+      if (L64 > b.seg_scratch_tokens || b.seg_scratch == nullptr) {
+        if (tid == 0) {
+          atomicMax(status, int(kStatusScratchTooSmall));
+          b.chunk_cnt[c] = 0;
+        }
+        continue;
+      }
+      tok = b.seg_scratch + int64_t(blockIdx.x) * 2 * b.seg_scratch_tokens;
+      rk  = tok + b.seg_scratch_tokens;
+    }
+    int len = int(L64);
+    for (int i = tid; i < len; i += kBaseThreads) tok[i] = __ldg(T.byte_to_id + b.bytes[cs + i]);
+    __syncthreads();
+    for (int iter = 0; iter < max_iters && len >= 2; ++iter) {
+      for (int i = tid; i < len - 1; i += kBaseThreads) rk[i] = uint16_t(probe_rank(T, tok[i], tok[i + 1]));
+      __syncthreads();
+      bool mine = false;
+      for (int i = tid; i < len - 1; i += kBaseThreads) {
+        const uint32_t r = rk[i];
+        if (r == NONE) continue;
+        if (i > 0 && uint32_t(rk[i - 1]) < r) continue;
+        if (i + 1 < len - 1 && uint32_t(rk[i + 1]) <= r) continue;
+        tok[i]     = uint16_t(merged_id(T, r));  // two kept positions are never adjacent
+        tok[i + 1] = uint16_t(DEAD);
+        mine       = true;
+      }
+      if (!__syncthreads_or(mine)) break;
+      len = compact_tokens<kBaseThreads / 32>(tok, len, &gs);
+    }
+    for (int j = tid; j < len; j += kBaseThreads) b.staging[cs + j] = tok[j];
+    if (tid == 0) b.chunk_cnt[c] = len;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // output: pack staged 16-bit tokens of every unit into the int32 id buffer
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) k_pack(const uint16_t* __restrict__ staging, const int64_t* __restrict__ first,
@@ -1778,6 +1877,15 @@ int launch_merge_base(const EncodeBuffers& b, const DeviceTable& t, int grid, cu
   if (grid > b.chunk_cap) grid = int(b.chunk_cap);
   if (grid < 1) grid = 1;
   k_merge_base<<<grid, kBaseThreads, 0, stream>>>(b, t);
+  return 1;
+}
+
+int launch_merge_localmin(const EncodeBuffers& b, const DeviceTable& t, int grid, int max_iters, cudaStream_t stream)
+{
+  if (b.n_bytes <= 0) return 0;
+  if (grid > b.chunk_cap) grid = int(b.chunk_cap);
+  if (grid < 1) grid = 1;
+  k_merge_localmin<<<grid, kBaseThreads, 0, stream>>>(b, t, max_iters);
   return 1;
 }
 

@@ -9,12 +9,12 @@ and the shard planner.
 There is no CPU fallback: importing works everywhere, but every GPU entry
 point raises if the CUDA library is missing or no device is present.
 """
-from .capi import (GTK_MODE_BASE, GTK_MODE_OPT, GTK_RULE_GREEDY, GTK_RULE_LOCALMIN, GtkError, Tokenizer,
+from .capi import (GTK_MODE_BASE, GTK_MODE_LOCALMIN, GTK_MODE_OPT, GTK_RULE_GREEDY, GTK_RULE_LOCALMIN, GtkError, Tokenizer,
                    library_path, load_library)
 from .shards import partition_by_bytes, stitch_offsets
 from .textgen import MIX_PLAIN, MIX_STRESS, TextGen
 
 __all__ = [
-    "GTK_MODE_BASE", "GTK_MODE_OPT", "GTK_RULE_GREEDY", "GTK_RULE_LOCALMIN", "GtkError", "Tokenizer",
+    "GTK_MODE_BASE", "GTK_MODE_LOCALMIN", "GTK_MODE_OPT", "GTK_RULE_GREEDY", "GTK_RULE_LOCALMIN", "GtkError", "Tokenizer",
     "library_path", "load_library", "partition_by_bytes", "stitch_offsets", "MIX_PLAIN", "MIX_STRESS", "TextGen",
 ]

@@ -8,6 +8,7 @@ import numpy as np
 
 GTK_MODE_OPT = 0
 GTK_MODE_BASE = 1
+GTK_MODE_LOCALMIN = 2  # the reference's other rule (local minimum, max_iters passes), per chunk
 GTK_RULE_GREEDY = 0
 GTK_RULE_LOCALMIN = 1
 NOALLOC_MAX_CHUNK_BYTES = 16384

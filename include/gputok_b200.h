@@ -55,7 +55,10 @@ enum {
 /* which merge kernel serves the call */
 enum {
   GTK_MODE_OPT  = 0, /* GpuTokenizer::tokenize_batch               (gputok_binding.cu:704-846) */
-  GTK_MODE_BASE = 1  /* GpuTokenizer::tokenize_batch_blockbpe_base (gputok_binding.cu:850-989) */
+  GTK_MODE_BASE = 1, /* GpuTokenizer::tokenize_batch_blockbpe_base (gputok_binding.cu:850-989) */
+  GTK_MODE_LOCALMIN = 2 /* the reference's OTHER rule on the GPU: bpe_merge_kernel_optimized (gputok_binding.cu:290-414),
+                           per chunk, at most max_iters passes; not greedy Algorithm 1 -- offered for timing and
+                           behaviour comparisons with the reference's tokenize_batch only */
 };
 
 /* merge rule of the host reference entry point */

@@ -269,6 +269,31 @@ def test_device_resident_entry_point(lib, merges_path, oracle):
     assert e.value.code == 4
 
 
+def test_localmin_rule_on_gpu(lib, merges_path, oracle, novel, ref_cases):
+    """GTK_MODE_LOCALMIN: the reference's other merge rule (bpe_merge_kernel_optimized), per chunk, capped at
+    max_iters passes -- against the oracle's restatement of bpe_merge_cpu (pinned by the reference's
+    gpu_tokens_optimized.txt) and the outputs recorded from the reference's compiled function."""
+    from oracle.loader import MODE_LOCALMIN
+
+    t = make_tok(lib, merges_path, 4096)
+    blob, case_off = ref_cases["bytes"], ref_cases["case_offsets"]
+    ids, toff, _, _ = t.encode(blob, case_off, mode=lib.GTK_MODE_LOCALMIN)
+    assert np.array_equal(toff, ref_cases["localmin_offsets"])
+    assert np.array_equal(ids, ref_cases["localmin_ids"]), first_mismatch(ids, ref_cases["localmin_ids"])
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "golden_localmin_512.npz"))
+    ids, _, _, _ = t.encode(z["text"], mode=lib.GTK_MODE_LOCALMIN)
+    assert np.array_equal(ids, z["ids"])
+    for data, chunk in ((novel[:400_000], 2048), (lib.TextGen(3).text(3 << 20, mix=lib.MIX_STRESS), 32768),
+                        (b"a" * 70000 + b" " + b"ab" * 5000, 65536)):
+        t = make_tok(lib, merges_path, chunk)
+        off = fixed_chunk_offsets(len(data), chunk)
+        want, woff = oracle.encode_chunks(data, off, mode=MODE_LOCALMIN, max_iters=50, threads=NCPU)
+        ids, _, coff, ms = t.encode(data, mode=lib.GTK_MODE_LOCALMIN)
+        check_chunks(ids, coff, want, woff, f"localmin chunk {chunk}")
+        greedy, _, _, _ = t.encode(data)
+        assert len(greedy) <= len(ids)                    # the capped local-minimum rule never merges more
+
+
 def test_gpt2_id_space(lib, merges_path, oracle):
     """Optional output in GPT-2's own id space: ids < 256 move to their position in GPT-2's byte-symbol order,
     ids >= 256 are unchanged."""
@@ -338,5 +363,7 @@ def test_pybind_methods_on_gpu(lib, merges_path, oracle):
     assert tok.tokenize_batch([]) == ([], 0.0)
     assert tok.tokenize_batch(["", ""]) == ([], 0.0)     # all-empty batch, as the reference
     assert tok.tokenize_batch_cpu(texts) == tok.tokenize_batch(texts)[0]
+    lm_gpu, _ = tok.tokenize_batch(texts[:3], merge_rule="localmin")      # texts shorter than a chunk
+    assert lm_gpu == tok.tokenize_batch_cpu(texts[:3], merge_rule="localmin")
     ids, toff, coff, ms = tok.encode_packed(texts)
     assert ids.dtype == np.int32 and toff.dtype == np.int64 and toff[-1] == len(ids)
