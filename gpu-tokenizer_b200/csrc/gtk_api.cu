@@ -125,6 +125,7 @@ struct gtk_tokenizer {
   mutable std::string last_error;
 
   // table in HBM
+  DevBuf d_bpi;
   DevBuf d_slots, d_bpr, d_mor, d_sor, d_adj, d_b2i, d_words, d_low_map;
   int id_space = GTK_IDS_REFERENCE;
   gtk::DeviceTable dtab{};
@@ -175,6 +176,7 @@ void upload_table(gtk_tokenizer* h)
   const gtk::HostTable& t = *h->table;
   upload(h->d_slots, t.slots.data(), t.slots.size() * sizeof(gtk::HashSlot), h->stream);
   upload(h->d_bpr, t.byte_pair_rank.data(), t.byte_pair_rank.size() * sizeof(uint16_t), h->stream);
+  upload(h->d_bpi, t.byte_pair_info.data(), t.byte_pair_info.size() * sizeof(uint16_t), h->stream);
   upload(h->d_mor, t.merged_of_rank.data(), t.merged_of_rank.size() * sizeof(uint32_t), h->stream);
   upload(h->d_sor, t.same_of_rank.data(), t.same_of_rank.size(), h->stream);
   upload(h->d_adj, t.adj, sizeof(t.adj), h->stream);
@@ -184,6 +186,7 @@ void upload_table(gtk_tokenizer* h)
   GTK_CUDA(cudaStreamSynchronize(h->stream));
   h->dtab.slots = h->d_slots.as<uint4>();
   h->dtab.byte_pair_rank = h->d_bpr.as<uint16_t>();
+  h->dtab.byte_pair_info = h->d_bpi.as<uint16_t>();
   h->dtab.merged_of_rank = h->d_mor.as<uint32_t>();
   h->dtab.same_of_rank = h->d_sor.as<uint8_t>();
   h->dtab.adj = h->d_adj.as<uint32_t>();
@@ -776,7 +779,7 @@ GTK_API void gtk_destroy(gtk_tokenizer* h)
   if (h->device >= 0) {
     cudaSetDevice(h->device);
     if (h->stream) cudaStreamSynchronize(h->stream);
-    for (DevBuf* b : {&h->d_slots, &h->d_bpr, &h->d_mor, &h->d_sor, &h->d_adj, &h->d_b2i, &h->d_words, &h->d_low_map, &h->d_memo, &h->d_q_short, &h->d_q_long, &h->d_q_huge, &h->d_bytes, &h->d_text_off,
+    for (DevBuf* b : {&h->d_bpi, &h->d_slots, &h->d_bpr, &h->d_mor, &h->d_sor, &h->d_adj, &h->d_b2i, &h->d_words, &h->d_low_map, &h->d_memo, &h->d_q_short, &h->d_q_long, &h->d_q_huge, &h->d_bytes, &h->d_text_off,
                       &h->d_text_chunk_base, &h->d_chunk_off, &h->d_tile_chunk0, &h->d_staging, &h->d_unit_first,
                       &h->d_unit_cnt, &h->d_chunk_cnt, &h->d_unit_base, &h->d_chunk_id_off, &h->d_text_id_off,
                       &h->d_out_ids, &h->d_seg_scratch, &h->d_scan_sums, &h->d_counters, &h->d_totals})

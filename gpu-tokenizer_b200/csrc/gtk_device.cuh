@@ -26,6 +26,7 @@ constexpr int kThreadSegMax = 32;      // longest segment a single thread merges
 struct DeviceTable {
   const uint4* slots;              // HashSlot[capacity]: {right, left, rank, merged}
   const uint16_t* byte_pair_rank;  // [65536]
+  const uint16_t* byte_pair_info;  // [65536]: 0xFFFF cut, 0xFFFE mergeable boundary without a byte-pair rank, else rank
   const uint32_t* merged_of_rank;  // [max_rank+1]
   const uint8_t* same_of_rank;     // [max_rank+1]
   const uint32_t* adj;             // [2048]

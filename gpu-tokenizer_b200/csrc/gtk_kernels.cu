@@ -732,19 +732,19 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
       by[3] = (w >> 16) & 0xFFu;
       by[4] = w >> 24;
       by[5] = S.bytes[20 + i0];
-      uint32_t mergeable = 0;  // bit k: the pair (by[k], by[k+1]) occurs inside some merge result
+      // one 16-bit table entry per byte pair answers both questions: can this boundary ever merge
+      // (anything but 0xFFFF), and what is the rank of the byte pair (values below 0xFFFE)
+      uint32_t info[5];
 #pragma unroll
-      for (int k = 0; k < 5; ++k) mergeable |= uint32_t(adj_bit(T.adj, by[k], by[k + 1])) << k;
+      for (int k = 0; k < 5; ++k) info[k] = __ldg(T.byte_pair_info + ((by[k] << 8) | by[k + 1]));
       uint32_t nib = 0, t[4], r[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         const int i      = i0 + k;
-        const bool start = (i >= wlen) || (lo + i == 0) || !((mergeable >> k) & 1u);
+        const bool start = (i >= wlen) || (lo + i == 0) || (info[k] == 0xFFFFu);
         nib |= uint32_t(start) << k;
         t[k] = (i < wlen) ? (identity_ids ? by[k + 1] : uint32_t(__ldg(T.byte_to_id + by[k + 1]))) : DEAD;
-        r[k] = ((i + 1 < wlen) && ((mergeable >> (k + 1)) & 1u))
-                   ? uint32_t(__ldg(T.byte_pair_rank + ((by[k + 1] << 8) | by[k + 2])))
-                   : NONE;
+        r[k] = ((i + 1 < wlen) && info[k + 1] < SEL) ? info[k + 1] : NONE;
       }
       const uint32_t word = __reduce_or_sync(0xFFu << (lane & 24), nib << (4 * (lane & 7)));
       if ((lane & 7) == 0) S.cut[g >> 3] = word;

@@ -274,6 +274,14 @@ void HostTable::build_derived()
   }
   adj_count = 0;
   for (uint32_t w : adj) adj_count += __builtin_popcount(w);
+  // one lookup answers both "may this boundary ever merge" and "rank of this byte pair"
+  byte_pair_info.assign(65536, uint16_t(0xFFFF));
+  for (uint32_t bit = 0; bit < 65536; ++bit) {
+    const bool inside = (adj[bit >> 5] >> (bit & 31)) & 1u;
+    const uint16_t rk = byte_pair_rank[bit];
+    if (rk != uint16_t(kNoRank16)) byte_pair_info[bit] = rk;  // a merge pair is inside its own result
+    else if (inside) byte_pair_info[bit] = uint16_t(0xFFFE);
+  }
 }
 
 // Greedy rule on one chunk.  The chunk is cut at never-merge boundaries (the

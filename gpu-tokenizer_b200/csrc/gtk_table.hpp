@@ -81,6 +81,8 @@ class HostTable {
   uint32_t log2_capacity = 0;
   uint32_t max_probe = 0;                  // longest displacement of a stored key
   std::vector<uint16_t> byte_pair_rank;    // [256*256], index (u<<8|v) on raw bytes, kNoRank16 if none
+  std::vector<uint16_t> byte_pair_info;    // [256*256]: 0xFFFF bigram never inside a merge result (cut), 0xFFFE inside
+                                           // one but not itself a merge, else the rank of the byte pair
   std::vector<uint32_t> merged_of_rank;    // [max_rank+1]
   std::vector<uint8_t> same_of_rank;       // [max_rank+1]: 1 if left == right
   uint32_t adj[2048];                      // bit (u<<8|v): bigram occurs inside a merge result

@@ -269,6 +269,56 @@ def test_device_resident_entry_point(lib, merges_path, oracle):
     assert e.value.code == 4
 
 
+def test_batch_beyond_2_gib_uses_64_bit_offsets(lib, merges_path, oracle):
+    """2.25 GiB in one call (byte positions and id offsets beyond 2^31): every chunk must decode to exactly its own
+    bytes (token byte lengths summed per chunk), a seeded sample of chunks must equal the oracle, and the
+    device-resident entry point must agree with the host path."""
+    import torch
+
+    n = (9 << 28) + 4096 * 3 + 17
+    data = lib.TextGen(11).text(n)
+    t = make_tok(lib, merges_path, 4096)
+    ids, toff, coff, _ = t.encode(data)
+    n_chunks = (n + 4095) // 4096
+    assert len(coff) - 1 == n_chunks and toff.tolist() == [0, len(ids)] and coff[-1] == len(ids)
+    lens = np.array([len(oracle.token_bytes(i)) for i in range(oracle.vocab_size)], dtype=np.int64)
+    per_chunk = np.add.reduceat(lens[ids], coff[:-1])
+    want_len = np.full(n_chunks, 4096, dtype=np.int64)
+    want_len[-1] = n - 4096 * (n_chunks - 1)
+    assert np.array_equal(per_chunk, want_len)
+    rng = np.random.default_rng(2)
+    sample = np.unique(np.concatenate([rng.integers(0, n_chunks, size=400), [0, n_chunks - 1, (1 << 31) // 4096,
+                                                                            (1 << 31) // 4096 - 1]]))
+    for c in sample:
+        lo, hi = int(c) * 4096, min(int(c) * 4096 + 4096, n)
+        want, _ = oracle.encode_chunks(data[lo:hi], np.array([0, hi - lo]), mode=MODE_SEGMENTED)
+        assert np.array_equal(ids[coff[c]:coff[c + 1]], want), f"chunk {c}"
+    d_bytes = torch.from_numpy(data).cuda()
+    d_toff = torch.tensor([0, n], dtype=torch.int64, device="cuda")
+    d_ids = torch.empty(len(ids) + 16, dtype=torch.int32, device="cuda")
+    d_coff = torch.empty(n_chunks + 8, dtype=torch.int64, device="cuda")
+    n_ids, n_c, _ = t.encode_device(d_bytes.data_ptr(), n, d_toff.data_ptr(), 1, d_ids.data_ptr(), d_ids.numel(),
+                                    d_coff.data_ptr(), d_coff.numel())
+    assert n_ids == len(ids) and n_c == n_chunks
+    assert torch.equal(d_ids[:n_ids].cpu(), torch.from_numpy(ids))
+    assert torch.equal(d_coff[:n_c + 1].cpu(), torch.from_numpy(coff))
+
+
+def test_invalid_arguments_are_reported(lib, merges_path):
+    t = make_tok(lib, merges_path, 2048)
+    with pytest.raises(lib.GtkError) as e:
+        t.encode(b"abcdef", np.array([0, 4, 2, 6], dtype=np.int64))      # offsets must not decrease
+    assert e.value.code == 1
+    with pytest.raises(lib.GtkError) as e:
+        t.encode(b"abcdef", np.array([1, 6], dtype=np.int64))            # first offset must be 0
+    assert e.value.code == 1
+    with pytest.raises(lib.GtkError) as e:
+        t.encode(b"abc", mode=7)
+    assert e.value.code == 1
+    ids, _, _, _ = t.encode(b"abc")                                       # the handle stays usable
+    assert len(ids) >= 1
+
+
 def test_localmin_rule_on_gpu(lib, merges_path, oracle, novel, ref_cases):
     """GTK_MODE_LOCALMIN: the reference's other merge rule (bpe_merge_kernel_optimized), per chunk, capped at
     max_iters passes -- against the oracle's restatement of bpe_merge_cpu (pinned by the reference's
