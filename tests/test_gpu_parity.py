@@ -235,6 +235,29 @@ def test_random_small_batches(lib, merges_path, oracle):
     assert np.array_equal(toff, woff[starts])
 
 
+def test_generated_adversarial_strings(lib, merges_path, oracle):
+    """Seeded adversarial strings (runs, tiny alphabets, arbitrary bytes, multi-byte characters, empty) in
+    batches that take the single-kernel small path and the multi-kernel path, at several chunk sizes."""
+    rng = np.random.default_rng(21)
+    alphabets = [b"a", b"ab", b"ae l", b"\n", bytes(range(256)), "\u00e9\u65e5\U0001F600 x".encode(), b"the and ing tion ", b" \t.,"]
+    texts = []
+    for i in range(600):
+        alpha = np.frombuffer(alphabets[i % len(alphabets)], dtype=np.uint8)
+        texts.append(bytes(rng.choice(alpha, size=int(rng.integers(0, 200)))))
+    for chunk in (5, 64, 2048):
+        t = make_tok(lib, merges_path, chunk)
+        for batch in (texts[:40], texts):                                  # small path, general path
+            ids, toff, coff, _ = t.encode_texts(batch)
+            blob = b"".join(batch)
+            chunk_off = [0]
+            pos = 0
+            for x in batch:
+                chunk_off.extend(list(range(pos + chunk, pos + len(x), chunk)) + ([pos + len(x)] if x else []))
+                pos += len(x)
+            want, woff = oracle.encode_chunks(blob, np.array(chunk_off, np.int64), mode=MODE_GREEDY)
+            check_chunks(ids, coff, want, woff, f"generated strings, chunk {chunk}, {len(batch)} texts")
+
+
 def test_latency_strings_one_call_each(lib, merges_path, oracle):
     """Config 3 in miniature: independent 512-byte strings, batch size 1, every string checked."""
     gen = lib.TextGen(2)

@@ -112,6 +112,35 @@ def _rechunk(text_off, chunk):
     return np.array(out, dtype=np.int64)
 
 
+def test_host_greedy_on_generated_strings(native_built, merges_path, oracle):
+    """Property test: the host reference entry point (segment cuts + cached ranks) equals the literal
+    Algorithm 1 loop on adversarial byte strings -- runs, tiny alphabets, arbitrary bytes, chunk cuts
+    inside UTF-8 sequences."""
+    from hypothesis import given, settings
+    from hypothesis import strategies as st
+
+    from gputok_b200 import Tokenizer
+
+    toks = {c: Tokenizer(merges_path, c, 50, device=-1) for c in (1, 3, 16, 4096)}
+    piece = st.one_of(
+        st.binary(min_size=0, max_size=40),
+        st.builds(lambda ch, k: bytes([ch]) * k, st.sampled_from(list(b"ae l\n0.")), st.integers(1, 80)),
+        st.text(alphabet="abeilnorst THE,.!\n", min_size=0, max_size=60).map(str.encode),
+        st.text(alphabet="\u00e9\u65e5\u672c\U0001F600 a", min_size=0, max_size=20).map(lambda x: x.encode("utf-8")),
+    )
+
+    @settings(max_examples=150, deadline=None)
+    @given(st.lists(piece, min_size=0, max_size=6), st.sampled_from([1, 3, 16, 4096]))
+    def check(pieces, chunk):
+        data = b"".join(pieces)
+        ids, toff, coff = toks[chunk].encode_cpu(data)
+        want, woff = oracle.encode_fixed(data, chunk, mode=MODE_GREEDY)
+        assert np.array_equal(ids, want) and np.array_equal(coff, woff)
+        assert toks[chunk].decode(ids) == data
+
+    check()
+
+
 def test_pybind_surface(native_built, merges_path, oracle):
     """Same class and method names as the reference's module (gputok_binding.cu:1015-1065)."""
     import gputok_gpu
