@@ -720,9 +720,14 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
     __syncthreads();
 
     GTK_PHASE(0);
+    // Only the 32-position words that hold text are processed; the words behind them are all
+    // "segment start" (the window may be shorter than a tile at the end of the text or in small batches).
+    const int used_words  = (wlen + 31) >> 5;
+    const int used_groups = used_words * 8;
+    if (tid >= used_words && tid < kCutWords) S.cut[tid] = 0xFFFFFFFFu;
     // ---- B. segment starts from the never-merge bitmap, initial ids and byte-pair ranks.
     //         Four consecutive positions per thread; eight lanes assemble one 32-bit bitmap word ----
-    for (int g = tid; g < kWindow / 4; g += kOptThreads) {
+    for (int g = tid; g < used_groups; g += kOptThreads) {
       const int i0     = g * 4;
       const uint32_t w = *reinterpret_cast<const uint32_t*>(&S.bytes[16 + i0]);
       uint32_t by[6];
@@ -1029,7 +1034,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
       int end_owned   = 0;
       if (S.last_start >= 0) end_owned = (S.over_start >= 0) ? S.over_start : next_cut(S.cut, S.last_start);
       if (end_owned > wlen) end_owned = wlen;
-      for (int g = tid; g < kWindow / 4; g += kOptThreads) {
+      for (int g = tid; g < used_groups; g += kOptThreads) {
         const int i0 = g * 4;
         if (i0 + 4 <= first || i0 >= end_owned) continue;
         if (i0 >= first && i0 + 4 <= end_owned) {
@@ -1063,7 +1068,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
     if (S.last_start >= 0) end_owned = (S.over_start >= 0) ? S.over_start : next_cut(S.cut, S.last_start);
     if (end_owned > wlen) end_owned = wlen;
     __syncthreads();  // every thread has read cut[] before it becomes the alive bitmap
-    for (int g = tid; g < kWindow / 4; g += kOptThreads) {
+    for (int g = tid; g < used_groups; g += kOptThreads) {
       const int i0   = g * 4;
       const uint2 tk = *reinterpret_cast<const uint2*>(&S.tok[i0]);
       const uint32_t t[4] = {tk.x & 0xFFFFu, tk.x >> 16, tk.y & 0xFFFFu, tk.y >> 16};
@@ -1077,12 +1082,12 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
     __syncthreads();
     int total;
     {
-      const int cnt = (tid < kCutWords) ? __popc(S.cut[tid]) : 0;
+      const int cnt = (tid < used_words) ? __popc(S.cut[tid]) : 0;
       const int off = block_exclusive_scan(cnt, S.scanbuf, &total);
-      if (tid < kCutWords) S.woff[tid] = uint16_t(off);
+      if (tid < used_words) S.woff[tid] = uint16_t(off);
     }
     __syncthreads();
-    for (int g = tid; g < kWindow / 4; g += kOptThreads) {
+    for (int g = tid; g < used_groups; g += kOptThreads) {
       const int i0        = g * 4;
       const int sh        = 4 * (lane & 7);
       const uint32_t word = S.cut[g >> 3];
