@@ -1,6 +1,6 @@
 """Regenerates the committed fixtures from the reference tree (run where it is mounted).
 
-    python tests/golden/make_fixtures.py [/root/reference]
+    python tests/golden/make_fixtures.py <reference root>
 
 Writes next to this script:
   gpt2_merges.txt            the reference's data/gpt2_tokenizer/merges.txt (the merge table every
@@ -14,7 +14,7 @@ Writes next to this script:
   ref_greedy_cases.npz       outputs of the reference's own bpe_merge_cpu_greedy (compiled in place by
                              oracle/Makefile) on adversarial byte strings
   MANIFEST.json              sha256 of every source and product
-The test-suite reads only these files; nothing under /root/reference is needed at test time.
+The test-suite reads only these files; the reference tree is not needed at test time.
 """
 from __future__ import annotations
 
