@@ -205,12 +205,24 @@ __device__ __forceinline__ uint32_t lanemask_lt()
 // Algorithm 1 restricted to the segment -- and re-probes the two pairs next
 // to it.  Returns false when no pair of the segment is mergeable any more.
 // ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ bool thread_merge_step(uint16_t* tok, uint16_t* rk, int L, uint32_t& alive,
-                                                  const DeviceTable& T)
+__device__ __forceinline__ bool thread_merge_step(uint16_t* tok_all, uint16_t* rk_all, int s, int L,
+                                                  uint32_t& alive, const DeviceTable& T)
 {
   if ((alive & (alive - 1u)) == 0u) return false;  // one token left
+  uint16_t* tok = tok_all + s;
+  uint16_t* rk  = rk_all + s;
+  // argmin over the cached ranks, two per 32-bit load.  The words may reach one slot before the segment
+  // (when s is odd) and the segment's own last slot: both always hold NONE, so they never win.
   uint32_t best = 0xFFFFFFFFu;
-  for (int i = 0; i < L - 1; ++i) best = min(best, (uint32_t(rk[i]) << 16) | uint32_t(i));
+  {
+    const uint32_t* words = reinterpret_cast<const uint32_t*>(rk_all);
+    const int w_last = (s + L - 2) >> 1;
+    uint32_t rel     = uint32_t(((s >> 1) << 1) - s);  // index of the low half relative to s: 0 or -1
+    for (int w = s >> 1; w <= w_last; ++w, rel += 2) {
+      const uint32_t x = words[w];
+      best = min(best, min((x << 16) | (rel & 0xFFFFu), (x & 0xFFFF0000u) | ((rel + 1u) & 0xFFFFu)));
+    }
+  }
   const uint32_t r = best >> 16;
   if (r >= SEL) return false;
   const int j = int(best & 0xFFFFu);
@@ -930,7 +942,26 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
       }
     }
     GTK_PHASE(12);
-    {
+    if (!queued && S.nmiss <= kOptThreads) {
+      // at most one segment per thread (the usual case): no queue, thread t takes entry t of the sorted list
+      int s = -1, L = 0;
+      uint32_t alive = 0;
+      if (tid < S.nmiss) {
+        s     = S.seg[tid];
+        L     = next_cut(S.cut, s) - s;
+        alive = (L >= 32) ? 0xFFFFFFFFu : ((1u << L) - 1u);
+      }
+      while (__any_sync(0xFFFFFFFFu, s >= 0)) {
+        if (s >= 0 && !thread_merge_step(S.tok, S.rk, s, L, alive, T)) {
+          if (!SPLIT && b.memo) {
+            uint32_t k[8];
+            segment_key8(S.bytes, 16 + s, L, k);
+            memo_insert(b.memo, b.memo_log2, k, L, S.tok + s);
+          }
+          s = -1;
+        }
+      }
+    } else {
       const int nseg   = S.nmiss;
       int s            = -1, L = 0;
       uint32_t alive   = 0;
@@ -962,7 +993,13 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
           if (__all_sync(0xFFFFFFFFu, drained)) break;
           continue;
         }
-        if (s >= 0 && !thread_merge_step(S.tok + s, S.rk + s, L, alive, T)) {
+#ifdef GTK_PHASE_TIMING
+        const long long step_t0 = clock64();
+        const bool step_active  = s >= 0;
+#endif
+        if (s >= 0 && !thread_merge_step(S.tok, S.rk, s, L, alive, T)) {
+#ifdef GTK_PHASE_TIMING
+#endif
           if (!SPLIT && b.memo) {
             uint32_t k[8];
             segment_key8(S.bytes, 16 + s, L, k);
@@ -970,6 +1007,12 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
           }
           s = -1;
         }
+#ifdef GTK_PHASE_TIMING
+        if (tid == 0 && step_active) {  // wall cycles of one merge step as seen by lane 0 of warp 0
+          atomicAdd(&g_phase_cycles[14], (unsigned long long)(clock64() - step_t0));
+          atomicAdd(&g_phase_cycles[15], 1ull);
+        }
+#endif
       }
     }
     __syncthreads();
