@@ -172,7 +172,7 @@ class GpuTokenizer {
     d["num_merges"] = ti.num_merges;
     d["max_rank"] = ti.max_rank;
     d["hash_capacity"] = ti.hash_capacity;
-    d["hash_max_probe"] = ti.hash_max_probe;
+    d["hash_overflow_entries"] = ti.hash_overflow_entries;
     d["hash_bytes"] = ti.hash_bytes;
     d["monotone"] = bool(ti.monotone);
     d["merged_is_256_plus_rank"] = bool(ti.merged_is_256_plus_rank);
@@ -183,7 +183,7 @@ class GpuTokenizer {
     d["device"] = ti.device;
     d["sm_count"] = ti.sm_count;
     d["whole_segment_entries"] = ti.whole_segment_entries;
-    d["whole_segment_max_probe"] = ti.whole_segment_max_probe;
+    d["whole_segment_dropped"] = ti.whole_segment_dropped;
     return d;
   }
 

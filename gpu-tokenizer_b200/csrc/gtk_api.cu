@@ -126,7 +126,7 @@ struct gtk_tokenizer {
 
   // table in HBM
   DevBuf d_bpi;
-  DevBuf d_slots, d_bpr, d_mor, d_sor, d_adj, d_b2i, d_words, d_low_map;
+  DevBuf d_slots, d_overflow, d_bpr, d_mor, d_sor, d_adj, d_b2i, d_words, d_low_map;
   int id_space = GTK_IDS_REFERENCE;
   gtk::DeviceTable dtab{};
 
@@ -174,7 +174,9 @@ void upload(DevBuf& buf, const void* src, size_t bytes, cudaStream_t s)
 void upload_table(gtk_tokenizer* h)
 {
   const gtk::HostTable& t = *h->table;
-  upload(h->d_slots, t.slots.data(), t.slots.size() * sizeof(gtk::HashSlot), h->stream);
+  upload(h->d_slots, t.pair_buckets.data(), t.pair_buckets.size() * sizeof(gtk::PairBucket), h->stream);
+  if (!t.pair_overflow.empty())
+    upload(h->d_overflow, t.pair_overflow.data(), t.pair_overflow.size() * sizeof(gtk::PairSlot), h->stream);
   upload(h->d_bpr, t.byte_pair_rank.data(), t.byte_pair_rank.size() * sizeof(uint16_t), h->stream);
   upload(h->d_bpi, t.byte_pair_info.data(), t.byte_pair_info.size() * sizeof(uint16_t), h->stream);
   upload(h->d_mor, t.merged_of_rank.data(), t.merged_of_rank.size() * sizeof(uint32_t), h->stream);
@@ -184,7 +186,9 @@ void upload_table(gtk_tokenizer* h)
   upload(h->d_low_map, t.gpt2_low_id, sizeof(t.gpt2_low_id), h->stream);
   upload(h->d_words, t.word_slots.data(), t.word_slots.size() * sizeof(gtk::WordSlot), h->stream);
   GTK_CUDA(cudaStreamSynchronize(h->stream));
-  h->dtab.slots = h->d_slots.as<uint4>();
+  h->dtab.pair_buckets = h->d_slots.as<uint4>();
+  h->dtab.pair_overflow = t.pair_overflow.empty() ? nullptr : h->d_overflow.as<uint2>();
+  h->dtab.pair_overflow_mask = t.pair_overflow.empty() ? 0u : uint32_t(t.pair_overflow.size() - 1);
   h->dtab.byte_pair_rank = h->d_bpr.as<uint16_t>();
   h->dtab.byte_pair_info = h->d_bpi.as<uint16_t>();
   h->dtab.merged_of_rank = h->d_mor.as<uint32_t>();
@@ -193,9 +197,6 @@ void upload_table(gtk_tokenizer* h)
   h->dtab.byte_to_id = h->d_b2i.as<uint16_t>();
   h->dtab.word_slots = h->d_words.as<uint4>();
   h->dtab.word_log2_capacity = t.word_log2_capacity;
-  h->dtab.word_max_probe = t.word_max_probe;
-  h->dtab.log2_capacity = t.log2_capacity;
-  h->dtab.max_probe = t.max_probe;
   h->dtab.monotone = t.monotone ? 1 : 0;
   h->dtab.merged_is_256_plus_rank = t.merged_is_256_plus_rank ? 1 : 0;
   h->dtab.byte_ids_identity = t.byte_ids_identity ? 1 : 0;
@@ -779,7 +780,7 @@ GTK_API void gtk_destroy(gtk_tokenizer* h)
   if (h->device >= 0) {
     cudaSetDevice(h->device);
     if (h->stream) cudaStreamSynchronize(h->stream);
-    for (DevBuf* b : {&h->d_bpi, &h->d_slots, &h->d_bpr, &h->d_mor, &h->d_sor, &h->d_adj, &h->d_b2i, &h->d_words, &h->d_low_map, &h->d_memo, &h->d_q_short, &h->d_q_long, &h->d_q_huge, &h->d_bytes, &h->d_text_off,
+    for (DevBuf* b : {&h->d_bpi, &h->d_slots, &h->d_overflow, &h->d_bpr, &h->d_mor, &h->d_sor, &h->d_adj, &h->d_b2i, &h->d_words, &h->d_low_map, &h->d_memo, &h->d_q_short, &h->d_q_long, &h->d_q_huge, &h->d_bytes, &h->d_text_off,
                       &h->d_text_chunk_base, &h->d_chunk_off, &h->d_tile_chunk0, &h->d_staging, &h->d_unit_first,
                       &h->d_unit_cnt, &h->d_chunk_cnt, &h->d_unit_base, &h->d_chunk_id_off, &h->d_text_id_off,
                       &h->d_out_ids, &h->d_seg_scratch, &h->d_scan_sums, &h->d_counters, &h->d_totals})
@@ -806,9 +807,9 @@ GTK_API int gtk_table_info_get(const gtk_tokenizer* h, gtk_table_info* out)
   out->vocab_size = int32_t(t.id_to_symbols.size());
   out->num_merges = int32_t(t.rows.size());
   out->max_rank = t.max_rank;
-  out->hash_capacity = 1u << t.log2_capacity;
-  out->hash_max_probe = t.max_probe;
-  out->hash_bytes = uint32_t(t.slots.size() * sizeof(gtk::HashSlot));
+  out->hash_capacity = uint32_t(t.pair_buckets.size() * 4);
+  out->hash_overflow_entries = t.pair_overflow_count;
+  out->hash_bytes = uint32_t(t.pair_buckets.size() * sizeof(gtk::PairBucket) + t.pair_overflow.size() * sizeof(gtk::PairSlot));
   out->monotone = t.monotone;
   out->merged_is_256_plus_rank = t.merged_is_256_plus_rank;
   out->byte_ids_identity = t.byte_ids_identity;
@@ -818,7 +819,7 @@ GTK_API int gtk_table_info_get(const gtk_tokenizer* h, gtk_table_info* out)
   out->device = h->device;
   out->sm_count = h->sm_count;
   out->whole_segment_entries = int32_t(t.word_count);
-  out->whole_segment_max_probe = t.word_max_probe;
+  out->whole_segment_dropped = t.word_dropped;
   return GTK_OK;
 }
 

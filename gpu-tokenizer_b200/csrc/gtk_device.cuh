@@ -24,18 +24,17 @@ constexpr int kThreadSegMax = 32;      // longest segment a single thread merges
 
 // Pointers into HBM, passed by value to every kernel.
 struct DeviceTable {
-  const uint4* slots;              // HashSlot[capacity]: {right, left, rank, merged}
+  const uint4* pair_buckets;       // PairBucket[65536]: four words rank << 16 | low16(key * kPairMul), empty = all ones
+  const uint2* pair_overflow;      // {key, rank} open addressing, or nullptr when no bucket overflowed
+  uint32_t pair_overflow_mask;     // capacity - 1
   const uint16_t* byte_pair_rank;  // [65536]
   const uint16_t* byte_pair_info;  // [65536]: 0xFFFF cut, 0xFFFE mergeable boundary without a byte-pair rank, else rank
   const uint32_t* merged_of_rank;  // [max_rank+1]
   const uint8_t* same_of_rank;     // [max_rank+1]
   const uint32_t* adj;             // [2048]
   const uint16_t* byte_to_id;      // [256]
-  const uint4* word_slots;         // WordSlot[word capacity]: {k0, k1, k2, length << 16 | id}
+  const uint4* word_slots;         // WordSlot[word capacity]: {k0, k1, k2, length << 16 | id}, two-choice cuckoo
   uint32_t word_log2_capacity;
-  uint32_t word_max_probe;
-  uint32_t log2_capacity;
-  uint32_t max_probe;
   int monotone;
   int merged_is_256_plus_rank;
   int byte_ids_identity;

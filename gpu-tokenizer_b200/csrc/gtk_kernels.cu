@@ -33,38 +33,75 @@ constexpr uint32_t DEAD = 0xFFFFu;  // token slot holds nothing
 // merge table probes
 // ------------------------------------------------------------------------------------------------
 
-__device__ __forceinline__ uint32_t probe_rank(const DeviceTable& T, uint32_t left, uint32_t right)
+// What a probe of the pair table needs, small enough to travel in registers.
+struct PairTable {
+  const uint4* buckets;
+  const uint2* overflow;           // nullptr when no bucket overflowed
+  const uint32_t* merged_of_rank;  // nullptr when merged id = 256 + rank
+  uint32_t overflow_mask;
+};
+
+__device__ __forceinline__ PairTable pair_table(const DeviceTable& T)
 {
-  const uint32_t mask = (1u << T.log2_capacity) - 1u;
-  uint32_t h          = (((left << 16) ^ right) * 0x9E3779B1u) >> (32 - T.log2_capacity);
-  uint4 s             = __ldg(T.slots + h);
-  if (s.x == right && s.y == left) return s.z;  // load factor 0.38: the first slot answers most probes
-  if ((s.x & s.y) == 0xFFFFFFFFu) return NONE;
-  for (uint32_t d = 1; d <= T.max_probe; ++d) {
+  return PairTable{T.pair_buckets, T.pair_overflow, T.merged_is_256_plus_rank ? nullptr : T.merged_of_rank,
+                   T.pair_overflow_mask};
+}
+
+// keys of a full bucket that has no match may live in the overflow table
+__device__ __noinline__ uint32_t probe_overflow(const uint2* overflow, uint32_t mask, uint32_t key)
+{
+  uint32_t h = ((key * 0x85EBCA77u) >> 7) & mask;
+  for (uint32_t d = 0; d <= mask; ++d) {
+    const uint2 s = __ldg(overflow + h);
+    if (s.x == key) return s.y;
+    if (s.x == 0xFFFFFFFFu) return NONE;
     h = (h + 1u) & mask;
-    s = __ldg(T.slots + h);
-    if (s.x == right && s.y == left) return s.z;
-    if ((s.x & s.y) == 0xFFFFFFFFu) return NONE;
   }
   return NONE;
 }
 
+// rank of the key whose hash is h in its home bucket v, NONE if it is not there (an empty word can only
+// "match" with rank NONE, which is the right answer for a bucket that is not full)
+__device__ __forceinline__ uint32_t bucket_rank(const uint4& v, uint32_t h)
+{
+  const uint32_t f = h & 0xFFFFu;
+  uint32_t r       = NONE;
+  if ((v.x & 0xFFFFu) == f) r = v.x >> 16;
+  if ((v.y & 0xFFFFu) == f) r = v.y >> 16;
+  if ((v.z & 0xFFFFu) == f) r = v.z >> 16;
+  if ((v.w & 0xFFFFu) == f) r = v.w >> 16;
+  return r;
+}
+
+__device__ __forceinline__ uint32_t resolve_rank(const uint4& v, uint32_t key, const uint2* overflow, uint32_t mask)
+{
+  uint32_t r = bucket_rank(v, key * 0x9E3779B1u);
+  if (r >= SEL && overflow != nullptr && (v.w >> 16) != NONE) r = probe_overflow(overflow, mask, key);
+  return r;
+}
+
+__device__ __forceinline__ uint32_t probe_rank(const DeviceTable& T, uint32_t left, uint32_t right)
+{
+  const uint32_t key = (left << 16) | right;
+  const uint4 v      = __ldg(T.pair_buckets + ((key * 0x9E3779B1u) >> 16));
+  return resolve_rank(v, key, T.pair_overflow, T.pair_overflow_mask);
+}
+
 // Whole-segment table: id of the vocabulary string (k0,k1,k2 = bytes zero padded, L = length)
-// if the greedy rule turns exactly that string into one token, else 0xFFFFFFFF.
+// if the greedy rule turns exactly that string into one token, else 0xFFFFFFFF.  Two-choice cuckoo
+// table: both candidate slots are loaded at once.
 __device__ __forceinline__ uint32_t word_lookup(const DeviceTable& T, uint32_t k0, uint32_t k1, uint32_t k2,
                                                 uint32_t L)
 {
-  const uint32_t mask = (1u << T.word_log2_capacity) - 1u;
-  uint32_t h          = (k0 * 0x9E3779B1u) ^ (k1 * 0x85EBCA77u) ^ (k2 * 0xC2B2AE3Du);
-  h ^= h >> 15;
-  h *= 0x2C1B3C6Du;
-  h >>= (32 - T.word_log2_capacity);
-  for (uint32_t d = 0; d <= T.word_max_probe; ++d) {
-    const uint4 s = __ldg(T.word_slots + h);
-    if (s.w == 0u) return 0xFFFFFFFFu;
-    if (s.x == k0 && s.y == k1 && s.z == k2 && (s.w >> 16) == L) return s.w & 0xFFFFu;
-    h = (h + 1u) & mask;
-  }
+  uint32_t m = (k0 * 0x9E3779B1u) ^ (k1 * 0x85EBCA77u) ^ (k2 * 0xC2B2AE3Du);
+  m ^= m >> 15;
+  m *= 0x2C1B3C6Du;
+  const uint32_t sh = 32 - T.word_log2_capacity;
+  const uint4 a = __ldg(T.word_slots + (m >> sh));
+  const uint4 c = __ldg(T.word_slots + (((m ^ (m >> 13)) * 0x165667B1u) >> sh));
+  const uint32_t meta = (L << 16);
+  if (a.x == k0 && a.y == k1 && a.z == k2 && (a.w & 0xFFFF0000u) == meta) return a.w & 0xFFFFu;
+  if (c.x == k0 && c.y == k1 && c.z == k2 && (c.w & 0xFFFF0000u) == meta) return c.w & 0xFFFFu;
   return 0xFFFFFFFFu;
 }
 
@@ -196,52 +233,88 @@ __device__ __forceinline__ uint32_t lanemask_lt()
 }
 
 // ------------------------------------------------------------------------------------------------
-// One merge step of one short segment (<= 32 tokens), executed by a single thread.
+// One short segment (<= 32 tokens) merged by a single thread.
 //
 // tok[0..L) / rk[0..L) live in shared memory; rk[i] is the rank of the pair
 // (token i, next live token), NONE for dead slots and for the last live one.
 // Dead slots become DEAD tombstones and stay where they are; the alive set is
-// a 32-bit register mask.  A step merges the left-most pair of lowest rank --
-// Algorithm 1 restricted to the segment -- and re-probes the two pairs next
-// to it.  Returns false when no pair of the segment is mergeable any more.
+// a 32-bit register mask.  `best` = (rank << 16 | position) of the left-most
+// pair of lowest rank -- the pair Algorithm 1 restricted to the segment merges
+// next.  A step merges it, starts the two table probes for the pairs next to
+// the new token, scans the cached ranks of all other pairs while the probes are
+// in flight, and folds the two new ranks into the next `best`.
 // ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ bool thread_merge_step(uint16_t* tok_all, uint16_t* rk_all, int s, int L,
-                                                  uint32_t& alive, const DeviceTable& T)
+__device__ __forceinline__ uint32_t segment_argmin(const uint16_t* rk_all, int s, int L)
 {
-  if ((alive & (alive - 1u)) == 0u) return false;  // one token left
-  uint16_t* tok = tok_all + s;
-  uint16_t* rk  = rk_all + s;
-  // argmin over the cached ranks, two per 32-bit load.  The words may reach one slot before the segment
-  // (when s is odd) and the segment's own last slot: both always hold NONE, so they never win.
-  uint32_t best = 0xFFFFFFFFu;
-  {
-    const uint32_t* words = reinterpret_cast<const uint32_t*>(rk_all);
-    const int w_last = (s + L - 2) >> 1;
-    uint32_t rel     = uint32_t(((s >> 1) << 1) - s);  // index of the low half relative to s: 0 or -1
-    for (int w = s >> 1; w <= w_last; ++w, rel += 2) {
-      const uint32_t x = words[w];
-      best = min(best, min((x << 16) | (rel & 0xFFFFu), (x & 0xFFFF0000u) | ((rel + 1u) & 0xFFFFu)));
-    }
+  // two ranks per 32-bit load.  The words may reach one slot before the segment (when s is odd) and the
+  // segment's own last slot: both always hold NONE, so they never win.
+  uint32_t best         = 0xFFFFFFFFu;
+  const uint32_t* words = reinterpret_cast<const uint32_t*>(rk_all);
+  const int w_last      = (s + L - 2) >> 1;
+  uint32_t rel          = uint32_t(((s >> 1) << 1) - s);  // index of the low half relative to s: 0 or -1
+  for (int w = s >> 1; w <= w_last; ++w, rel += 2) {
+    const uint32_t x = words[w];
+    best = min(best, min((x << 16) | (rel & 0xFFFFu), (x & 0xFFFF0000u) | ((rel + 1u) & 0xFFFFu)));
   }
+  return best;
+}
+
+// Returns false (and changes nothing) when no pair of the segment is mergeable any more.
+__device__ __forceinline__ bool thread_merge_step(uint16_t* tok_all, uint16_t* rk_all, int s, int L,
+                                                  uint32_t& alive, uint32_t& best, const PairTable& P)
+{
   const uint32_t r = best >> 16;
   if (r >= SEL) return false;
-  const int j = int(best & 0xFFFFu);
-  const int q = j + __ffs(int(alive >> (j + 1)));  // next live slot after j (j <= 30)
-  const uint32_t c = merged_id(T, r);
+  uint16_t* tok = tok_all + s;
+  uint16_t* rk  = rk_all + s;
+  const int j   = int(best & 0xFFFFu);
+  const int q   = j + __ffs(int(alive >> (j + 1)));  // next live slot after j (j <= 30)
+  const uint32_t c = P.merged_of_rank ? __ldg(P.merged_of_rank + r) : 256u + r;
+  alive &= ~(1u << q);
+  const uint32_t right = (q >= 31) ? 0u : (alive >> (q + 1));
+  const uint32_t left  = alive & ((1u << j) - 1u);
+  const int p          = left ? 31 - __clz(int(left)) : j;  // j itself when there is no left neighbour
+  // both probes leave before anything waits for them; an absent neighbour reads as an empty slot
+  uint32_t keyR = 0xFFFFFFFFu, keyL = 0xFFFFFFFFu;
+  uint4 vR = make_uint4(0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu), vL = vR;
+  if (right) {
+    keyR = (c << 16) | uint32_t(tok[q + __ffs(int(right))]);
+    vR   = __ldg(P.buckets + ((keyR * 0x9E3779B1u) >> 16));
+  }
+  if (left) {
+    keyL = (uint32_t(tok[p]) << 16) | c;
+    vL   = __ldg(P.buckets + ((keyL * 0x9E3779B1u) >> 16));
+  }
   tok[j] = uint16_t(c);
   tok[q] = uint16_t(DEAD);
   rk[q]  = uint16_t(NONE);
-  alive &= ~(1u << q);
-  const uint32_t right = (q >= 31) ? 0u : (alive >> (q + 1));
-  uint32_t rr          = NONE;
-  if (right) rr = probe_rank(T, c, tok[q + __ffs(int(right))]);
-  rk[j] = uint16_t(rr);
-  const uint32_t left = alive & ((1u << j) - 1u);
-  if (left) {
-    const int p = 31 - __clz(int(left));
-    rk[p]       = uint16_t(probe_rank(T, tok[p], c));
+  rk[j]  = uint16_t(NONE);
+  rk[p]  = uint16_t(NONE);
+  best   = segment_argmin(rk_all, s, L);  // every pair but the two new ones
+  const uint32_t rr = resolve_rank(vR, keyR, P.overflow, P.overflow_mask);
+  const uint32_t rl = resolve_rank(vL, keyL, P.overflow, P.overflow_mask);
+  if (rr < SEL) {
+    rk[j] = uint16_t(rr);
+    best  = min(best, (rr << 16) | uint32_t(j));
+  }
+  if (rl < SEL) {
+    rk[p] = uint16_t(rl);
+    best  = min(best, (rl << 16) | uint32_t(p));
   }
   return true;
+}
+
+// Every lane merges its own segment [s, s+L) to the end (s < 0: no segment).  Kept out of line so that
+// the loop gets registers of its own instead of sharing them with the tile code around the call.
+__device__ __noinline__ void thread_merge_segments(uint16_t* tok, uint16_t* rk, int s, int L, PairTable P)
+{
+  uint32_t alive = 0, best = 0xFFFFFFFFu;
+  if (s >= 0) {
+    alive = (L >= 32) ? 0xFFFFFFFFu : ((1u << L) - 1u);
+    best  = segment_argmin(rk, s, L);
+  }
+  while (__any_sync(0xFFFFFFFFu, best < (SEL << 16)))
+    if (best < (SEL << 16)) thread_merge_step(tok, rk, s, L, alive, best, P);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -871,11 +944,6 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
               for (int i = 1; i < LL; ++i) S.tok[ss + i] = uint16_t(DEAD);
             }
           }
-          if (!SPLIT && miss && b.memo) {
-            uint32_t k[8];
-            segment_key8(S.bytes, 16 + ss, LL, k);
-            if (memo_lookup(b.memo, b.memo_log2, k, LL, S.tok + ss) > 0) miss = false;
-          }
         }
         const uint32_t bal = __ballot_sync(0xFFFFFFFFu, miss);
         int wbase          = 0;
@@ -886,10 +954,36 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
       }
     }
     __syncthreads();
+    // ---- E1b. call-local memo, on the dense list of misses: a segment whose bytes were merged earlier
+    //           in this call copies the ids; what is left is compacted once more ----
+    int nmiss = S.nmiss;
+    if (!SPLIT && b.memo) {
+      for (int r0 = 0; r0 < nmiss; r0 += kOptThreads) {
+        const int j  = r0 + tid;
+        uint32_t ent = 0;
+        bool miss    = false;
+        if (j < nmiss) {
+          ent          = S.seg[j];
+          const int ss = int(ent);
+          const int LL = next_cut(S.cut, ss) - ss;
+          uint32_t k[8];
+          segment_key8(S.bytes, 16 + ss, LL, k);
+          miss = memo_lookup(b.memo, b.memo_log2, k, LL, S.tok + ss) <= 0;
+        }
+        const uint32_t bal = __ballot_sync(0xFFFFFFFFu, miss);
+        int wbase          = 0;
+        if (lane == 0 && bal) wbase = atomicAdd(&S.nbig, __popc(bal));
+        wbase = __shfl_sync(0xFFFFFFFFu, wbase, 0);
+        __syncthreads();
+        if (miss) S.seg[wbase + __popc(bal & lt)] = uint16_t(ent);
+      }
+      __syncthreads();
+      nmiss = S.nbig;
+    }
 
 #ifdef GTK_PHASE_TIMING
     if (tid == 0) {
-      atomicAdd(&g_phase_cycles[10], (unsigned long long)S.nmiss);
+      atomicAdd(&g_phase_cycles[10], (unsigned long long)nmiss);
       atomicAdd(&g_phase_cycles[11], (unsigned long long)S.nseg);
     }
 #endif
@@ -942,30 +1036,25 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
       }
     }
     GTK_PHASE(12);
-    if (!queued && S.nmiss <= kOptThreads) {
+    if (!queued && nmiss <= kOptThreads) {
       // at most one segment per thread (the usual case): no queue, thread t takes entry t of the sorted list
       int s = -1, L = 0;
-      uint32_t alive = 0;
-      if (tid < S.nmiss) {
-        s     = S.seg[tid];
-        L     = next_cut(S.cut, s) - s;
-        alive = (L >= 32) ? 0xFFFFFFFFu : ((1u << L) - 1u);
+      if (tid < nmiss) {
+        s = S.seg[tid];
+        L = next_cut(S.cut, s) - s;
       }
-      while (__any_sync(0xFFFFFFFFu, s >= 0)) {
-        if (s >= 0 && !thread_merge_step(S.tok, S.rk, s, L, alive, T)) {
-          if (!SPLIT && b.memo) {
-            uint32_t k[8];
-            segment_key8(S.bytes, 16 + s, L, k);
-            memo_insert(b.memo, b.memo_log2, k, L, S.tok + s);
-          }
-          s = -1;
-        }
+      thread_merge_segments(S.tok, S.rk, s, L, pair_table(T));
+      if (!SPLIT && b.memo && s >= 0) {
+        uint32_t k[8];
+        segment_key8(S.bytes, 16 + s, L, k);
+        memo_insert(b.memo, b.memo_log2, k, L, S.tok + s);
       }
     } else {
-      const int nseg   = S.nmiss;
+      const int nseg   = nmiss;
       int s            = -1, L = 0;
-      uint32_t alive   = 0;
+      uint32_t alive   = 0, best = 0xFFFFFFFFu;
       bool drained     = false;
+      const PairTable P = pair_table(T);
       for (;;) {
         const bool need   = (s < 0) && !drained;
         const uint32_t nb = __ballot_sync(0xFFFFFFFFu, need);
@@ -985,6 +1074,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
                 s     = ss0;
                 L     = LL0;
                 alive = (L >= 32) ? 0xFFFFFFFFu : ((1u << L) - 1u);
+                best  = segment_argmin(S.rk, s, L);
               }
             }
           }
@@ -997,7 +1087,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
         const long long step_t0 = clock64();
         const bool step_active  = s >= 0;
 #endif
-        if (s >= 0 && !thread_merge_step(S.tok, S.rk, s, L, alive, T)) {
+        if (s >= 0 && !thread_merge_step(S.tok, S.rk, s, L, alive, best, P)) {
 #ifdef GTK_PHASE_TIMING
 #endif
           if (!SPLIT && b.memo) {

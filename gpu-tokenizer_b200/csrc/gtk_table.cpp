@@ -187,16 +187,56 @@ void HostTable::build_words()
   word_count = uint32_t(words.size());
   word_log2_capacity = 10;
   while ((size_t(1) << word_log2_capacity) < words.size() * 2 + 1) ++word_log2_capacity;
-  const uint32_t cap = 1u << word_log2_capacity, mask = cap - 1;
-  word_slots.assign(cap, WordSlot{0, 0, 0, 0});
-  word_max_probe = 0;
+  word_slots.assign(size_t(1) << word_log2_capacity, WordSlot{0, 0, 0, 0});
+  word_dropped = 0;
+  auto home = [&](const WordSlot& w, int which) {
+    const uint32_t m = word_mix(w.k0, w.k1, w.k2);
+    return which ? word_hash_b(m, word_log2_capacity) : word_hash_a(m, word_log2_capacity);
+  };
   for (auto& w : words) {
     uint32_t k[3] = {0, 0, 0};
     for (size_t i = 0; i < w.first.size(); ++i) k[i >> 2] |= uint32_t((unsigned char)w.first[i]) << (8 * (i & 3));
-    uint32_t h = word_hash(k[0], k[1], k[2], word_log2_capacity), d = 0;
-    while (word_slots[h].meta != 0) { h = (h + 1) & mask; ++d; }
-    word_slots[h] = {k[0], k[1], k[2], (uint32_t(w.first.size()) << 16) | uint32_t(w.second)};
-    word_max_probe = std::max(word_max_probe, d);
+    WordSlot cur{k[0], k[1], k[2], (uint32_t(w.first.size()) << 16) | uint32_t(w.second)};
+    // cuckoo insertion: take the first free choice, else evict from alternating choices
+    bool placed = false;
+    int which   = 0;
+    for (int kick = 0; kick < 500 && !placed; ++kick) {
+      const uint32_t ha = home(cur, 0), hb = home(cur, 1);
+      if (word_slots[ha].meta == 0) { word_slots[ha] = cur; placed = true; break; }
+      if (word_slots[hb].meta == 0) { word_slots[hb] = cur; placed = true; break; }
+      const uint32_t at = which ? hb : ha;
+      std::swap(cur, word_slots[at]);
+      // the evicted entry must move to its other choice next
+      which = (home(cur, 0) == at) ? 1 : 0;
+    }
+    if (!placed) ++word_dropped;  // `cur` (some entry) is left out: it only loses the shortcut
+  }
+}
+
+void HostTable::build_pair_buckets()
+{
+  pair_buckets.assign(kPairBuckets, PairBucket{{0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu}});
+  std::vector<PairSlot> spilled;
+  for (const MergeRow& r : rows) {
+    const uint32_t key = (uint32_t(r.left) << 16) | uint32_t(r.right);
+    const uint32_t h   = key * kPairMul;
+    PairBucket& b      = pair_buckets[h >> 16];
+    int i = 0;
+    while (i < 4 && b.w[i] != 0xFFFFFFFFu) ++i;
+    if (i < 4) b.w[i] = (r.rank << 16) | (h & 0xFFFFu);
+    else spilled.push_back(PairSlot{key, r.rank});
+  }
+  pair_overflow_count = uint32_t(spilled.size());
+  pair_overflow.clear();
+  if (!spilled.empty()) {
+    size_t cap = 16;
+    while (cap < spilled.size() * 4) cap <<= 1;
+    pair_overflow.assign(cap, PairSlot{0xFFFFFFFFu, 0xFFFFFFFFu});
+    for (const PairSlot& e : spilled) {
+      size_t h = (e.key * 0x85EBCA77u) >> 7 & (cap - 1);
+      while (pair_overflow[h].key != 0xFFFFFFFFu) h = (h + 1) & (cap - 1);
+      pair_overflow[h] = e;
+    }
   }
 }
 
@@ -245,6 +285,7 @@ void HostTable::build_derived()
   byte_ids_identity = true;
   for (int b = 0; b < 256; ++b) byte_ids_identity = byte_ids_identity && (byte_to_id[b] == b);
   if (fits_u16) {
+    build_pair_buckets();
     for (int u = 0; u < 256; ++u)
       for (int v = 0; v < 256; ++v) {
         uint32_t rk;

@@ -27,6 +27,21 @@ struct alignas(16) HashSlot {
   uint32_t merged;
 };
 
+// Device form of the pair table when ids and ranks fit 16 bits.  key = left << 16 | right; h = key * kPairMul is a
+// bijection on 32 bits, so inside bucket (h >> 16) the low 16 bits of h identify the key exactly.  A bucket is
+// four 32-bit words (rank << 16 | low16(h)), filled front to back, 0xFFFFFFFF = empty: one 128-bit load answers
+// a probe, found or not.  Keys whose bucket already holds four entries go to a small open-addressing overflow
+// table of {key, rank} (empty = all ones), looked at only when the home bucket is full and has no match.
+constexpr uint32_t kPairMul = 0x9E3779B1u;
+constexpr uint32_t kPairBuckets = 65536;
+struct alignas(16) PairBucket {
+  uint32_t w[4];
+};
+struct alignas(8) PairSlot {
+  uint32_t key;
+  uint32_t rank;
+};
+
 // One slot of the whole-segment table: a byte string of 2..12 bytes (zero padded to three
 // words) whose greedy tokenisation is the single id in `meta` (length << 16 | id); meta 0 = empty.
 struct alignas(16) WordSlot {
@@ -35,12 +50,18 @@ struct alignas(16) WordSlot {
 };
 constexpr int kWordMaxBytes = 12;
 
-inline uint32_t word_hash(uint32_t k0, uint32_t k1, uint32_t k2, uint32_t log2_capacity)
+// The whole-segment table is a two-choice cuckoo table: a string sits at word_hash_a or word_hash_b of its
+// key, so a lookup is two independent 128-bit loads and no loop, found or not.
+inline uint32_t word_mix(uint32_t k0, uint32_t k1, uint32_t k2)
 {
   uint32_t h = (k0 * 0x9E3779B1u) ^ (k1 * 0x85EBCA77u) ^ (k2 * 0xC2B2AE3Du);
   h ^= h >> 15;
-  h *= 0x2C1B3C6Du;
-  return h >> (32 - log2_capacity);
+  return h * 0x2C1B3C6Du;
+}
+inline uint32_t word_hash_a(uint32_t m, uint32_t log2_capacity) { return m >> (32 - log2_capacity); }
+inline uint32_t word_hash_b(uint32_t m, uint32_t log2_capacity)
+{
+  return ((m ^ (m >> 13)) * 0x165667B1u) >> (32 - log2_capacity);
 }
 
 struct MergeRow {
@@ -78,6 +99,9 @@ class HostTable {
 
   // flat arrays for the device
   std::vector<HashSlot> slots;
+  std::vector<PairBucket> pair_buckets;    // device form (only when fits_u16)
+  std::vector<PairSlot> pair_overflow;     // power-of-two capacity, or empty when nothing overflowed
+  uint32_t pair_overflow_count = 0;
   uint32_t log2_capacity = 0;
   uint32_t max_probe = 0;                  // longest displacement of a stored key
   std::vector<uint16_t> byte_pair_rank;    // [256*256], index (u<<8|v) on raw bytes, kNoRank16 if none
@@ -92,8 +116,8 @@ class HostTable {
   // into exactly its own id (verified one by one with greedy_chunk at build time)
   std::vector<WordSlot> word_slots;
   uint32_t word_log2_capacity = 0;
-  uint32_t word_max_probe = 0;
-  uint32_t word_count = 0;
+  uint32_t word_count = 0;    // strings that qualify
+  uint32_t word_dropped = 0;  // of those, not placed (they take the merge path instead)
 
   // properties the kernels rely on
   bool monotone = false;        // rank(m) > rank of every merge producing one of m's parts
@@ -121,6 +145,7 @@ class HostTable {
   void build_hash();
   void build_derived();
   void build_words();
+  void build_pair_buckets();
 };
 
 }  // namespace gtk

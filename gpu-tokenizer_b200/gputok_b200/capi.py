@@ -25,11 +25,11 @@ class GtkError(RuntimeError):
 
 class _TableInfo(C.Structure):
     _fields_ = [("vocab_size", C.c_int32), ("num_merges", C.c_int32), ("max_rank", C.c_uint32),
-                ("hash_capacity", C.c_uint32), ("hash_max_probe", C.c_uint32), ("hash_bytes", C.c_uint32),
+                ("hash_capacity", C.c_uint32), ("hash_overflow_entries", C.c_uint32), ("hash_bytes", C.c_uint32),
                 ("monotone", C.c_int32), ("merged_is_256_plus_rank", C.c_int32), ("byte_ids_identity", C.c_int32),
                 ("adj_bigrams", C.c_int32), ("chunk_tokens", C.c_int32), ("max_iters", C.c_int32),
                 ("device", C.c_int32), ("sm_count", C.c_int32),
-                ("whole_segment_entries", C.c_int32), ("whole_segment_max_probe", C.c_uint32)]
+                ("whole_segment_entries", C.c_int32), ("whole_segment_dropped", C.c_uint32)]
 
 
 def library_path() -> str:

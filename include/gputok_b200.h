@@ -73,9 +73,9 @@ typedef struct gtk_table_info {
   int32_t  vocab_size;       /* number of token ids (50 256 for GPT-2 merges.txt) */
   int32_t  num_merges;       /* distinct (left,right) pairs in the table */
   uint32_t max_rank;         /* highest rank present */
-  uint32_t hash_capacity;    /* slots of the open-addressing table (power of two) */
-  uint32_t hash_max_probe;   /* longest probe sequence of any stored key */
-  uint32_t hash_bytes;       /* bytes of the slot array in HBM */
+  uint32_t hash_capacity;    /* slots of the pair table: 65 536 buckets of four */
+  uint32_t hash_overflow_entries; /* pairs whose bucket was full (side table, second load) */
+  uint32_t hash_bytes;       /* bytes of the pair table in HBM */
   int32_t  monotone;         /* 1: every merge has a higher rank than the merges that create its parts */
   int32_t  merged_is_256_plus_rank; /* 1: merged id == 256 + rank for every merge */
   int32_t  byte_ids_identity;       /* 1: id of byte b == b for all 256 bytes */
@@ -85,7 +85,7 @@ typedef struct gtk_table_info {
   int32_t  device;           /* CUDA device ordinal, -1 for a host-only handle */
   int32_t  sm_count;
   int32_t  whole_segment_entries;   /* vocabulary strings (2..12 bytes) answered by one table probe */
-  uint32_t whole_segment_max_probe; /* longest probe sequence in that table */
+  uint32_t whole_segment_dropped; /* qualifying strings that found no place (they are merged instead) */
 } gtk_table_info;
 
 /* Library version string. */

@@ -35,7 +35,9 @@ def test_table_info(native_built, merges_path):
     assert ti["vocab_size"] == 50256 and ti["num_merges"] == 50000 and ti["max_rank"] == 49999
     assert ti["monotone"] == 1 and ti["merged_is_256_plus_rank"] == 1 and ti["byte_ids_identity"] == 1
     assert ti["adj_bigrams"] == 2689
-    assert ti["hash_capacity"] == 131072 and ti["hash_bytes"] == 2 * 1024 * 1024  # L2-resident, load 0.38
+    # 65 536 buckets of four 32-bit entries (1 MiB, L2-resident) plus a few overflow pairs
+    assert ti["hash_capacity"] == 262144 and 1024 * 1024 <= ti["hash_bytes"] < 1024 * 1024 + 65536
+    assert ti["hash_overflow_entries"] < 500 and ti["whole_segment_dropped"] == 0
     assert ti["device"] == -1
 
 
