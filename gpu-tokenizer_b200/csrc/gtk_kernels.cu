@@ -25,6 +25,10 @@
 namespace gtk {
 namespace {
 
+#ifdef GTK_PHASE_TIMING
+__device__ unsigned long long g_phase_cycles[24];
+#endif
+
 constexpr uint32_t NONE = 0xFFFFu;  // pair not mergeable
 constexpr uint32_t SEL  = 0xFFFEu;  // pair selected for the current pass
 constexpr uint32_t DEAD = 0xFFFFu;  // token slot holds nothing
@@ -313,8 +317,39 @@ __device__ __noinline__ void thread_merge_segments(uint16_t* tok, uint16_t* rk, 
     alive = (L >= 32) ? 0xFFFFFFFFu : ((1u << L) - 1u);
     best  = segment_argmin(rk, s, L);
   }
-  while (__any_sync(0xFFFFFFFFu, best < (SEL << 16)))
+#ifdef GTK_PHASE_TIMING
+  if (threadIdx.x == 0) {  // in-situ latency of one table load and of one rank scan
+    const long long a0 = clock64();
+    const uint4 v      = __ldg(P.buckets + (uint32_t(a0) * 2654435761u >> 16));
+    const long long a1 = clock64() + (v.x == 0x12345u);
+    atomicAdd(&g_phase_cycles[16], (unsigned long long)(a1 - a0));
+    atomicAdd(&g_phase_cycles[17], 1ull);
+    if (s >= 0) {
+      const long long b0 = clock64();
+      const uint32_t bb  = segment_argmin(rk, s, L);
+      const long long b1 = clock64() + (bb == 0x12345u);
+      atomicAdd(&g_phase_cycles[18], (unsigned long long)(b1 - b0));
+      atomicAdd(&g_phase_cycles[19], 1ull);
+      atomicAdd(&g_phase_cycles[20], (unsigned long long)L);
+    }
+  }
+  const long long t0 = clock64();
+  int steps          = 0;
+#endif
+  while (__any_sync(0xFFFFFFFFu, best < (SEL << 16))) {
     if (best < (SEL << 16)) thread_merge_step(tok, rk, s, L, alive, best, P);
+#ifdef GTK_PHASE_TIMING
+    ++steps;
+#endif
+  }
+#ifdef GTK_PHASE_TIMING
+  if (threadIdx.x == 0) {  // warp 0: loop trips and their wall cycles
+    atomicAdd(&g_phase_cycles[14], (unsigned long long)(clock64() - t0));
+    atomicAdd(&g_phase_cycles[15], (unsigned long long)steps);
+  }
+  if ((threadIdx.x & 31) == 0) atomicAdd(&g_phase_cycles[21], (unsigned long long)steps);  // all warps
+  if (s >= 0) atomicAdd(&g_phase_cycles[22], (unsigned long long)(L - __popc(alive)));      // merges done
+#endif
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -702,7 +737,6 @@ constexpr int kLongCap  = 128;
 // Optional per-phase cycle accounting of k_merge_opt (build with -DGTK_PHASE_TIMING): thread 0 of
 // every CTA accumulates clock64() deltas between phase boundaries; read with gtk_debug_phase_cycles.
 #ifdef GTK_PHASE_TIMING
-__device__ unsigned long long g_phase_cycles[16];
 #define GTK_PHASE(k)                                              \
   do {                                                            \
     if (tid == 0) {                                               \
@@ -754,6 +788,7 @@ __device__ __forceinline__ void opt_tile_setup(OptSmem& S, const DeviceTable& T)
 __device__ __forceinline__ void opt_tile_reset(OptSmem& S)
 {
   S.nlong       = 0;
+  S.nseg        = 0;
   S.seg_next    = 0;
   S.nmiss       = 0;
   S.nbig        = 0;
@@ -859,101 +894,72 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
     __syncthreads();
 
     GTK_PHASE(2);
-    // ---- D. owned segments of at least two bytes, sorted by length (longest first) so that the
-    //         lanes of a warp work on segments of similar length in step E ----
+    // ---- D/E1. every thread walks the multi-byte segments that start in its 16 positions.
+    //      Whole-segment lookup: a segment whose bytes are a vocabulary string that the greedy rule
+    //      collapses to one id is finished with two independent table loads; the others go to the
+    //      list of misses (short), the warp queue (long) or the oversize slot (runs past the window) ----
     {
-      uint32_t m = 0;
-      if (tid < 33) S.hist[tid] = 0;
       if (tid < kTile / 32) {
         const int w0        = tid * 32;
-        const uint32_t word = S.cut[tid], nextw = S.cut[tid + 1];
+        const uint32_t word = S.cut[tid];
         const uint32_t ownmask = (w0 + 32 <= own) ? 0xFFFFFFFFu : (w0 >= own ? 0u : ((1u << (own - w0)) - 1u));
         const uint32_t starts  = word & ownmask;
         if (starts) {
           atomicMin(&S.first_start, w0 + __ffs(int(starts)) - 1);
           atomicMax(&S.last_start, w0 + 31 - __clz(int(starts)));
         }
-        m = starts & ~((word >> 1) | (nextw << 31));
       }
-      __syncthreads();
-      for (uint32_t mm = m; mm;) {  // pass 1: length histogram, long and oversize segments set aside
-        const int ss = tid * 32 + __ffs(int(mm)) - 1;
-        mm &= mm - 1;
-        const int e  = next_cut(S.cut, ss);
-        const int LL = e - ss;
-        if (e >= kWindow && wlen == kWindow) {
-          S.over_start = ss;  // runs past the window: finished in the HBM workspace below
-        } else if (LL <= kThreadSegMax) {
-          atomicAdd(&S.hist[LL], 1);
-        } else {
-          const int q = atomicAdd(&S.nlong, 1);
-          if (q < kLongCap) S.longq[q] = uint16_t(ss);
-          else atomicMax(status, int(kStatusLongQueueOverflow));
-        }
+      const int base = tid * 16;
+      uint32_t m16   = 0;
+      if (base < own) {
+        const uint32_t w32     = __funnelshift_r(S.cut[tid >> 1], S.cut[(tid >> 1) + 1], (tid & 1) * 16);
+        const uint32_t ownmask = (base + 16 <= own) ? 0xFFFFu : ((1u << (own - base)) - 1u);
+        m16 = w32 & ~(w32 >> 1) & ownmask;  // starts whose next position is not a start
       }
-      __syncthreads();
-      if (warp == 0) {  // exclusive prefix over lengths 32, 31, ... 2
-        const int len = 32 - lane;
-        const int v   = S.hist[len];
-        int inc       = v;
-#pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-          const int y = __shfl_up_sync(0xFFFFFFFFu, inc, d);
-          if (lane >= d) inc += y;
-        }
-        S.hist[len] = inc - v;
-        if (lane == 31) S.nseg = inc;
-      }
-      __syncthreads();
-      for (uint32_t mm = m; mm;) {  // pass 2: scatter (start, length) into the sorted list
-        const int ss = tid * 32 + __ffs(int(mm)) - 1;
-        mm &= mm - 1;
-        const int e  = next_cut(S.cut, ss);
-        const int LL = e - ss;
-        if (LL <= kThreadSegMax && !(e >= kWindow && wlen == kWindow)) {
-          const int pos = atomicAdd(&S.hist[LL], 1);
-          S.seg[pos]    = uint16_t(ss);
-        }
-      }
-    }
-    __syncthreads();
-
-    GTK_PHASE(3);
-    // ---- E1. whole-segment lookup: a segment whose bytes are a vocabulary string that the greedy
-    //          rule collapses to one id is finished with a single table probe; the others are
-    //          compacted to the front of the list for the merge loop ----
-    GTK_PHASE(9);
-    {
-      const int nseg = S.nseg;
-      for (int r0 = 0; r0 < nseg; r0 += kOptThreads) {
-        const int j  = r0 + tid;
-        uint32_t ent = 0;
-        bool miss    = false;
-        if (j < nseg) {
-          ent          = S.seg[j];
-          const int ss = int(ent);
-          const int LL = next_cut(S.cut, ss) - ss;
-          miss         = true;
-          if (LL <= 12) {
-            uint32_t k0, k1, k2;
-            segment_key(S.bytes, 16 + ss, LL, k0, k1, k2);
-            const uint32_t id = word_lookup(T, k0, k1, k2, uint32_t(LL));
-            if (id != 0xFFFFFFFFu) {
-              miss      = false;
-              S.tok[ss] = uint16_t(id);
-              for (int i = 1; i < LL; ++i) S.tok[ss + i] = uint16_t(DEAD);
+      int nseg_mine = 0;
+      while (__any_sync(0xFFFFFFFFu, m16 != 0)) {
+        bool miss = false;
+        int ss    = 0;
+        if (m16) {
+          ss = base + __ffs(int(m16)) - 1;
+          m16 &= m16 - 1;
+          ++nseg_mine;
+          const int e  = next_cut(S.cut, ss);
+          const int LL = e - ss;
+          if (e >= kWindow && wlen == kWindow) {
+            S.over_start = ss;  // runs past the window: finished in the HBM workspace below
+          } else if (LL > kThreadSegMax) {
+            const int q = atomicAdd(&S.nlong, 1);
+            if (q < kLongCap) S.longq[q] = uint16_t(ss);
+            else atomicMax(status, int(kStatusLongQueueOverflow));
+          } else {
+            miss = true;
+            if (LL <= 12) {
+              uint32_t k0, k1, k2;
+              segment_key(S.bytes, 16 + ss, LL, k0, k1, k2);
+              const uint32_t id = word_lookup(T, k0, k1, k2, uint32_t(LL));
+              if (id != 0xFFFFFFFFu) {
+                miss      = false;
+                S.tok[ss] = uint16_t(id);
+                for (int i = 1; i < LL; ++i) S.tok[ss + i] = uint16_t(DEAD);
+              }
             }
           }
         }
         const uint32_t bal = __ballot_sync(0xFFFFFFFFu, miss);
-        int wbase          = 0;
-        if (lane == 0 && bal) wbase = atomicAdd(&S.nmiss, __popc(bal));
-        wbase = __shfl_sync(0xFFFFFFFFu, wbase, 0);
-        __syncthreads();  // every entry of this round has been read before the list is overwritten
-        if (miss) S.seg[wbase + __popc(bal & lt)] = uint16_t(ent);
+        if (bal) {
+          int wbase = 0;
+          if (lane == 0) wbase = atomicAdd(&S.nmiss, __popc(bal));
+          wbase = __shfl_sync(0xFFFFFFFFu, wbase, 0);
+          if (miss) S.seg[wbase + __popc(bal & lt)] = uint16_t(ss);
+        }
       }
+#ifdef GTK_PHASE_TIMING
+      atomicAdd(&S.nseg, nseg_mine);
+#endif
     }
     __syncthreads();
+    GTK_PHASE(3);
     // ---- E1b. call-local memo, on the dense list of misses: a segment whose bytes were merged earlier
     //           in this call copies the ids; what is left is compacted once more ----
     int nmiss = S.nmiss;
@@ -979,6 +985,34 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
       }
       __syncthreads();
       nmiss = S.nbig;
+    }
+
+    // ---- E1c. the misses, sorted by length (longest first) so that the lanes of a warp work on segments of
+    //           similar length in step E2: thread j keeps entry j in registers while the list is rewritten ----
+    if (!SPLIT && nmiss > 32 && nmiss <= kOptThreads) {
+      if (tid < 34) S.hist[tid] = 0;
+      __syncthreads();
+      int ss = 0, LL = 0, slot = 0;
+      if (tid < nmiss) {
+        ss   = S.seg[tid];
+        LL   = next_cut(S.cut, ss) - ss;
+        slot = atomicAdd(&S.hist[LL], 1);
+      }
+      __syncthreads();
+      if (warp == 0) {  // exclusive prefix over lengths 32, 31, ... 2
+        const int len = 32 - lane;
+        const int v   = S.hist[len];
+        int inc       = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int y = __shfl_up_sync(0xFFFFFFFFu, inc, d);
+          if (lane >= d) inc += y;
+        }
+        S.hist[len] = inc - v;
+      }
+      __syncthreads();
+      if (tid < nmiss) S.seg[S.hist[LL] + slot] = uint16_t(ss);
+      __syncthreads();
     }
 
 #ifdef GTK_PHASE_TIMING
@@ -2084,12 +2118,12 @@ int launch_encode_small(const EncodeBuffers& b, const DeviceTable& t, cudaStream
 }
 
 #ifdef GTK_PHASE_TIMING
-extern "C" __attribute__((visibility("default"))) void gtk_debug_phase_cycles(unsigned long long out[16], int reset)
+extern "C" __attribute__((visibility("default"))) void gtk_debug_phase_cycles(unsigned long long out[24], int reset)
 {
   cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out, g_phase_cycles, sizeof(unsigned long long) * 16);
+  cudaMemcpyFromSymbol(out, g_phase_cycles, sizeof(unsigned long long) * 24);
   if (reset) {
-    unsigned long long z[16] = {};
+    unsigned long long z[24] = {};
     cudaMemcpyToSymbol(g_phase_cycles, z, sizeof(z));
   }
 }
