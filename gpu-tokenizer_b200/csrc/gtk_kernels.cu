@@ -310,7 +310,7 @@ __device__ __forceinline__ bool thread_merge_step(uint16_t* tok_all, uint16_t* r
 
 // Every lane merges its own segment [s, s+L) to the end (s < 0: no segment).  Kept out of line so that
 // the loop gets registers of its own instead of sharing them with the tile code around the call.
-__device__ __noinline__ void thread_merge_segments(uint16_t* tok, uint16_t* rk, int s, int L, PairTable P)
+__device__ __noinline__ uint32_t thread_merge_segments(uint16_t* tok, uint16_t* rk, int s, int L, PairTable P)
 {
   uint32_t alive = 0, best = 0xFFFFFFFFu;
   if (s >= 0) {
@@ -347,9 +347,8 @@ __device__ __noinline__ void thread_merge_segments(uint16_t* tok, uint16_t* rk, 
     atomicAdd(&g_phase_cycles[14], (unsigned long long)(clock64() - t0));
     atomicAdd(&g_phase_cycles[15], (unsigned long long)steps);
   }
-  if ((threadIdx.x & 31) == 0) atomicAdd(&g_phase_cycles[21], (unsigned long long)steps);  // all warps
-  if (s >= 0) atomicAdd(&g_phase_cycles[22], (unsigned long long)(L - __popc(alive)));      // merges done
 #endif
+  return alive;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -766,6 +765,7 @@ struct OptSmem {
   int over_len;
   long long over_end;
   int over_chunk;
+  int end_owned;
 };
 
 // first segment start strictly after window position s (words past the window are all ones)
@@ -775,6 +775,31 @@ __device__ __forceinline__ int next_cut(const uint32_t* cut, int s)
   uint32_t x = cut[w] & (0xFFFFFFFFu << ((s + 1) & 31));
   while (!x) x = cut[++w];
   return w * 32 + __ffs(int(x)) - 1;
+}
+
+// The segment-start bitmap turns into the bitmap of live tokens as segments finish: the first token of a
+// segment is always live, so a finished segment adds the bits of its other live slots (`a`, relative to
+// its start s; bit 0 is ignored).  Only bits inside the segment change, so next_cut() of any other
+// segment still finds the same end.
+__device__ __forceinline__ void mark_alive(uint32_t* cut, int s, uint32_t a)
+{
+  a &= ~1u;
+  if (!a) return;
+  const int sh = s & 31;
+  atomicOr(&cut[s >> 5], a << sh);
+  if (sh && (a >> (32 - sh))) atomicOr(&cut[(s >> 5) + 1], a >> (32 - sh));
+}
+
+// one warp: positions [lo, hi) become live
+__device__ __forceinline__ void mark_alive_range(uint32_t* cut, int lo, int hi, int lane)
+{
+  if (hi <= lo) return;
+  for (int w = (lo >> 5) + lane; w <= ((hi - 1) >> 5); w += 32) {
+    uint32_t x = 0xFFFFFFFFu;
+    if (w == (lo >> 5)) x &= 0xFFFFFFFFu << (lo & 31);
+    if (w == ((hi - 1) >> 5)) x &= 0xFFFFFFFFu >> (31 - ((hi - 1) & 31));
+    atomicOr(&cut[w], x);
+  }
 }
 
 // Per-CTA set-up shared by the kernels that process tiles: never-merge bitmap into shared memory and
@@ -797,6 +822,7 @@ __device__ __forceinline__ void opt_tile_reset(OptSmem& S)
   S.last_start  = -1;
   S.over_start  = -1;
   S.over_len    = 0;
+  S.end_owned   = 0;
 }
 
 // One tile of the byte stream: tokenises every segment that starts in bytes [k*kTile, (k+1)*kTile),
@@ -905,8 +931,12 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
         const uint32_t ownmask = (w0 + 32 <= own) ? 0xFFFFFFFFu : (w0 >= own ? 0u : ((1u << (own - w0)) - 1u));
         const uint32_t starts  = word & ownmask;
         if (starts) {
+          const int last = w0 + 31 - __clz(int(starts));
           atomicMin(&S.first_start, w0 + __ffs(int(starts)) - 1);
-          atomicMax(&S.last_start, w0 + 31 - __clz(int(starts)));
+          atomicMax(&S.last_start, last);
+          // end of the owned region = end of the last owned segment, taken while the bitmap still holds
+          // segment starts only (ends grow with starts, so the maximum is the last segment's end)
+          atomicMax(&S.end_owned, next_cut(S.cut, last));
         }
       }
       const int base = tid * 16;
@@ -941,7 +971,8 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
               if (id != 0xFFFFFFFFu) {
                 miss      = false;
                 S.tok[ss] = uint16_t(id);
-                for (int i = 1; i < LL; ++i) S.tok[ss + i] = uint16_t(DEAD);
+                if (SPLIT)  // the split pipeline stores tokens by position, tombstones included
+                  for (int i = 1; i < LL; ++i) S.tok[ss + i] = uint16_t(DEAD);
               }
             }
           }
@@ -974,7 +1005,9 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
           const int LL = next_cut(S.cut, ss) - ss;
           uint32_t k[8];
           segment_key8(S.bytes, 16 + ss, LL, k);
-          miss = memo_lookup(b.memo, b.memo_log2, k, LL, S.tok + ss) <= 0;
+          const int got = memo_lookup(b.memo, b.memo_log2, k, LL, S.tok + ss);  // ids at the front of the segment
+          miss          = got <= 0;
+          if (got > 1) mark_alive(S.cut, ss, (got >= 32) ? 0xFFFFFFFFu : ((1u << got) - 1u));
         }
         const uint32_t bal = __ballot_sync(0xFFFFFFFFu, miss);
         int wbase          = 0;
@@ -1077,7 +1110,8 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
         s = S.seg[tid];
         L = next_cut(S.cut, s) - s;
       }
-      thread_merge_segments(S.tok, S.rk, s, L, pair_table(T));
+      const uint32_t alive = thread_merge_segments(S.tok, S.rk, s, L, pair_table(T));
+      if (!SPLIT && s >= 0) mark_alive(S.cut, s, alive);
       if (!SPLIT && b.memo && s >= 0) {
         uint32_t k[8];
         segment_key8(S.bytes, 16 + s, L, k);
@@ -1117,13 +1151,8 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
           if (__all_sync(0xFFFFFFFFu, drained)) break;
           continue;
         }
-#ifdef GTK_PHASE_TIMING
-        const long long step_t0 = clock64();
-        const bool step_active  = s >= 0;
-#endif
         if (s >= 0 && !thread_merge_step(S.tok, S.rk, s, L, alive, best, P)) {
-#ifdef GTK_PHASE_TIMING
-#endif
+          if (!SPLIT) mark_alive(S.cut, s, alive);
           if (!SPLIT && b.memo) {
             uint32_t k[8];
             segment_key8(S.bytes, 16 + s, L, k);
@@ -1131,12 +1160,6 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
           }
           s = -1;
         }
-#ifdef GTK_PHASE_TIMING
-        if (tid == 0 && step_active) {  // wall cycles of one merge step as seen by lane 0 of warp 0
-          atomicAdd(&g_phase_cycles[14], (unsigned long long)(clock64() - step_t0));
-          atomicAdd(&g_phase_cycles[15], 1ull);
-        }
-#endif
       }
     }
     __syncthreads();
@@ -1221,8 +1244,8 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
       for (int q = warp; q < nl; q += kOptThreads / 32) {
         const int s   = S.longq[q];
         const int L   = next_cut(S.cut, s) - s;
-        const int len = group_merge<1>(S.tok + s, S.rk + s, L, T, nullptr, status);
-        for (int i = len + lane; i < L; i += 32) S.tok[s + i] = uint16_t(DEAD);
+        const int len = group_merge<1>(S.tok + s, S.rk + s, L, T, nullptr, status);  // ids at the front
+        mark_alive_range(S.cut, s + 1, s + len, lane);
         __syncwarp();
       }
     }
@@ -1230,26 +1253,19 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
 
     GTK_PHASE(5);
     // ---- G/H. compact the owned region [first, end) into S.rk, then to staging ----
-    const int first = S.first_start;
-    int end_owned   = 0;
-    if (S.last_start >= 0) end_owned = (S.over_start >= 0) ? S.over_start : next_cut(S.cut, S.last_start);
-    if (end_owned > wlen) end_owned = wlen;
-    __syncthreads();  // every thread has read cut[] before it becomes the alive bitmap
-    for (int g = tid; g < used_groups; g += kOptThreads) {
-      const int i0   = g * 4;
-      const uint2 tk = *reinterpret_cast<const uint2*>(&S.tok[i0]);
-      const uint32_t t[4] = {tk.x & 0xFFFFu, tk.x >> 16, tk.y & 0xFFFFu, tk.y >> 16};
-      uint32_t nib = 0;
-#pragma unroll
-      for (int k = 0; k < 4; ++k)
-        nib |= uint32_t((i0 + k >= first) && (i0 + k < end_owned) && (t[k] != DEAD)) << k;
-      const uint32_t word = __reduce_or_sync(0xFFu << (lane & 24), nib << (4 * (lane & 7)));
-      if ((lane & 7) == 0) S.cut[g >> 3] = word;
-    }
-    __syncthreads();
+    const int first     = S.first_start;
+    const int end_owned = min((S.over_start >= 0) ? S.over_start : S.end_owned, wlen);
     int total;
     {
-      const int cnt = (tid < used_words) ? __popc(S.cut[tid]) : 0;
+      int cnt = 0;
+      if (tid < used_words) {  // the bitmap now marks live tokens; keep the owned range [first, end_owned)
+        const int w0 = tid * 32;
+        uint32_t x   = S.cut[tid];
+        x &= (first <= w0) ? 0xFFFFFFFFu : ((first >= w0 + 32) ? 0u : (0xFFFFFFFFu << (first - w0)));
+        x &= (end_owned >= w0 + 32) ? 0xFFFFFFFFu : ((end_owned <= w0) ? 0u : ((1u << (end_owned - w0)) - 1u));
+        S.cut[tid] = x;
+        cnt        = __popc(x);
+      }
       const int off = block_exclusive_scan(cnt, S.scanbuf, &total);
       if (tid < used_words) S.woff[tid] = uint16_t(off);
     }
