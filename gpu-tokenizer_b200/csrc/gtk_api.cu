@@ -75,10 +75,23 @@ struct PinBuf {
     GTK_CUDA(cudaHostAlloc(&p, want, cudaHostAllocDefault));
     cap = want;
   }
+  // page-locked memory that kernels write directly (dp = the address as the device sees it)
+  void* dp = nullptr;
+  void reserve_mapped(size_t bytes)
+  {
+    if (bytes <= cap && dp) return;
+    if (p) GTK_CUDA(cudaFreeHost(p));
+    p = dp = nullptr;
+    cap = 0;
+    size_t want = std::max(bytes, size_t(4096));
+    GTK_CUDA(cudaHostAlloc(&p, want, cudaHostAllocMapped));
+    GTK_CUDA(cudaHostGetDevicePointer(&dp, p, 0));
+    cap = want;
+  }
   void release()
   {
     if (p) cudaFreeHost(p);
-    p = nullptr;
+    p = dp = nullptr;
     cap = 0;
   }
   template <class T>
@@ -90,9 +103,9 @@ struct PinBuf {
 // Buffers of one in-flight slice of a large host batch (kSliceArenas sets rotate).
 constexpr int kSliceArenas = 4;
 struct SliceArena {
-  DevBuf text_off, text_chunk_base, chunk_off, tile_chunk0, unit_first, unit_cnt, chunk_cnt, unit_base,
-      chunk_id_off, text_id_off, scan_sums, counters, totals;
-  PinBuf h_totals, h_piece_off, h_piece_id_off;
+  DevBuf text_chunk_base, chunk_off, tile_chunk0, unit_first, unit_cnt, chunk_cnt, unit_base, scan_sums, counters,
+      totals;
+  PinBuf h_totals;  // mapped: written by a kernel
   cudaEvent_t ev[6] = {};          // stage timing
   cudaEvent_t ev_in = nullptr;     // slice text is in HBM
   cudaEvent_t ev_front = nullptr;  // totals of the slice are on the host
@@ -100,10 +113,10 @@ struct SliceArena {
   cudaEvent_t ev_out = nullptr;    // results of the slice are on the host
   void release()
   {
-    for (DevBuf* b : {&text_off, &text_chunk_base, &chunk_off, &tile_chunk0, &unit_first, &unit_cnt, &chunk_cnt,
-                      &unit_base, &chunk_id_off, &text_id_off, &scan_sums, &counters, &totals})
+    for (DevBuf* b : {&text_chunk_base, &chunk_off, &tile_chunk0, &unit_first, &unit_cnt, &chunk_cnt, &unit_base,
+                      &scan_sums, &counters, &totals})
       b->release();
-    for (PinBuf* b : {&h_totals, &h_piece_off, &h_piece_id_off}) b->release();
+    h_totals.release();
     for (auto& e : ev)
       if (e) cudaEventDestroy(e);
     for (cudaEvent_t* e : {&ev_in, &ev_front, &ev_packed, &ev_out})
@@ -137,6 +150,9 @@ struct gtk_tokenizer {
       d_chunk_cnt, d_unit_base, d_chunk_id_off, d_text_id_off, d_out_ids, d_seg_scratch, d_scan_sums, d_counters,
       d_totals;
   PinBuf h_ids, h_text_id_off, h_chunk_id_off, h_totals;
+  // sliced host batches: offsets of all slices, moved once per batch
+  DevBuf d_piece_off, d_piece_id_off, d_chunk_id_all;
+  PinBuf h_piece_off, h_piece_id_off, h_chunk_id_all;
   // small batches: input and results live in mapped page-locked memory, one kernel per call
   uint8_t* small_in_h = nullptr;   // [text offsets | bytes]
   uint8_t* small_in_d = nullptr;
@@ -146,8 +162,8 @@ struct gtk_tokenizer {
   int tune_pipeline = GTK_PIPELINE_AUTO;  // AUTO currently means FUSED: fastest measured on B200
   int tune_memo = 0;
   // sliced host path: copy streams and two slice arenas
-  cudaStream_t in_stream = nullptr, out_stream = nullptr;
-  SliceArena slice[4];
+  cudaStream_t in_stream = nullptr, out_stream = nullptr, pack_stream = nullptr;
+  SliceArena slice[kSliceArenas];
   // host-side result of gtk_encode_cpu
   std::vector<int32_t> cpu_ids;
   std::vector<int64_t> cpu_text_off, cpu_chunk_off;
@@ -320,7 +336,7 @@ const char* status_text(int s)
 // Chunker -> merge -> scans.  Leaves totals (n_chunks, n_ids) and the status
 // word in the pinned totals buffer; the caller synchronises and then packs.
 void run_front(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* launches, cudaEvent_t* ev = nullptr,
-               int64_t* pinned_totals = nullptr)
+               int64_t* pinned_totals = nullptr, int64_t* mapped_totals = nullptr)
 {
   cudaStream_t s = h->stream;
   if (!ev) ev = h->ev;
@@ -338,14 +354,19 @@ void run_front(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* lau
   *launches += gtk::launch_output_scans(b, mode != GTK_MODE_OPT, s);
   GTK_CUDA(cudaEventRecord(ev[3], s));
   GTK_CUDA(cudaGetLastError());
+  if (mapped_totals) {  // one small kernel writes the four words into mapped host memory: no copy-engine round trips
+    *launches += gtk::launch_publish_totals(b, mapped_totals, s);
+    return;
+  }
   int64_t* ht = pinned_totals ? pinned_totals : h->h_totals.as<int64_t>();
   GTK_CUDA(cudaMemcpyAsync(ht, b.totals, 16, cudaMemcpyDeviceToHost, s));
   GTK_CUDA(cudaMemcpyAsync(ht + 2, b.counters, 16, cudaMemcpyDeviceToHost, s));
 }
 
-void run_pack(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* launches, cudaEvent_t* ev = nullptr)
+void run_pack(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* launches, cudaEvent_t* ev = nullptr,
+              cudaStream_t on = nullptr)
 {
-  cudaStream_t s = h->stream;
+  cudaStream_t s = on ? on : h->stream;
   if (!ev) ev = h->ev;
   GTK_CUDA(cudaEventRecord(ev[5], s));
   if (use_split(b, mode)) *launches += gtk::launch_pack_split(b, h->sm_count * 8, s);
@@ -425,7 +446,6 @@ void slice_arena_prepare(gtk_tokenizer* h, SliceArena& a, int64_t max_bytes, int
 {
   const int64_t chunk_cap = chunk_upper_bound(max_bytes, max_pieces, h->chunk_tokens);
   const int64_t n_tiles   = (max_bytes + gtk::kTile - 1) / gtk::kTile;
-  a.text_off.reserve(size_t(max_pieces + 1) * 8);
   a.text_chunk_base.reserve(size_t(max_pieces + 1) * 8);
   a.chunk_off.reserve(size_t(chunk_cap + 1) * 8);
   a.tile_chunk0.reserve(size_t(n_tiles + 1) * 4);
@@ -433,14 +453,10 @@ void slice_arena_prepare(gtk_tokenizer* h, SliceArena& a, int64_t max_bytes, int
   a.unit_cnt.reserve(size_t(n_tiles + 1) * 4);
   a.chunk_cnt.reserve(size_t(chunk_cap + 1) * 4);
   a.unit_base.reserve(size_t(n_tiles + 2) * 8);
-  a.chunk_id_off.reserve(size_t(chunk_cap + 1) * 8);
-  a.text_id_off.reserve(size_t(max_pieces + 1) * 8);
   a.scan_sums.reserve(size_t(std::max<int64_t>(std::max(chunk_cap, n_tiles), max_pieces) / 4096 + 2) * 8);
   a.counters.reserve(64);
   a.totals.reserve(64);
-  a.h_totals.reserve(64);
-  a.h_piece_off.reserve(size_t(max_pieces + 1) * 8);
-  a.h_piece_id_off.reserve(size_t(max_pieces + 1) * 8);
+  a.h_totals.reserve_mapped(64);
   for (auto& e : a.ev)
     if (!e) GTK_CUDA(cudaEventCreate(&e));
   for (cudaEvent_t* e : {&a.ev_in, &a.ev_front, &a.ev_packed, &a.ev_out})
@@ -459,7 +475,7 @@ gtk::EncodeBuffers slice_buffers(gtk_tokenizer* h, SliceArena& a, const SlicePla
   const int64_t pieces  = int64_t(sp.piece_off.size()) - 1;
   b.bytes = h->d_bytes.as<uint8_t>() + dev_off;
   b.n_bytes = n_bytes;
-  b.text_off = a.text_off.as<int64_t>();
+  b.text_off = nullptr;  // the three offset arrays are set by the caller (batch-wide buffers)
   b.n_texts = pieces;
   b.chunk_bytes = h->chunk_tokens;
   b.text_chunk_base = a.text_chunk_base.as<int64_t>();
@@ -472,8 +488,8 @@ gtk::EncodeBuffers slice_buffers(gtk_tokenizer* h, SliceArena& a, const SlicePla
   b.unit_cnt = a.unit_cnt.as<int32_t>();
   b.chunk_cnt = a.chunk_cnt.as<int32_t>();
   b.unit_base = a.unit_base.as<int64_t>();
-  b.chunk_id_off = a.chunk_id_off.as<int64_t>();
-  b.text_id_off = a.text_id_off.as<int64_t>();
+  b.chunk_id_off = nullptr;
+  b.text_id_off = nullptr;
   b.out_ids = h->d_out_ids.as<int32_t>() + dev_off;  // worst case one id per byte: slices never overlap
   b.out_capacity = n_bytes;
   const int64_t longest = std::min<int64_t>(h->chunk_tokens, n_bytes);
@@ -493,13 +509,22 @@ int encode_host_sliced(gtk_tokenizer* h, int mode, const uint8_t* bytes, const i
                        int64_t n_texts, int64_t n_bytes, float* kernel_ms)
 {
   const std::vector<SlicePlan> slices = plan_slices(text_offsets, n_texts, h->chunk_tokens, kSliceTargetBytes);
-  const int ns = int(slices.size());
-  int64_t max_bytes = 0, max_pieces = 0, total_pieces = 0;
-  for (const SlicePlan& sp : slices) {
-    max_bytes = std::max(max_bytes, sp.byte_hi - sp.byte_lo);
-    max_pieces = std::max<int64_t>(max_pieces, int64_t(sp.piece_off.size()) - 1);
-    total_pieces += int64_t(sp.piece_off.size()) - 1;
+  const int ns     = int(slices.size());
+  const size_t nsz = size_t(ns);
+  // Offsets travel once per batch, not once per slice: the piece offsets of all slices go up in one copy
+  // before the first slice, the per-piece and per-chunk id offsets of all slices come back in two copies
+  // after the last one.  Slice i owns entries [piece_at[i], piece_at[i+1]) and [chunk_at[i], chunk_at[i+1]).
+  std::vector<int64_t> piece_at(nsz + 1, 0), chunk_at(nsz + 1, 0);
+  int64_t max_bytes = 0, max_pieces = 0;
+  for (int i = 0; i < ns; ++i) {
+    const SlicePlan& sp  = slices[size_t(i)];
+    const int64_t pieces = int64_t(sp.piece_off.size()) - 1;
+    max_bytes  = std::max(max_bytes, sp.byte_hi - sp.byte_lo);
+    max_pieces = std::max(max_pieces, pieces);
+    piece_at[size_t(i) + 1] = piece_at[size_t(i)] + pieces + 1;
+    chunk_at[size_t(i) + 1] = chunk_at[size_t(i)] + chunk_upper_bound(sp.byte_hi - sp.byte_lo, pieces, h->chunk_tokens) + 1;
   }
+  const int64_t total_pieces = piece_at[nsz] - ns;
   // everything is sized before the first copy is issued: nothing may be reallocated in flight
   const size_t span = size_t(n_bytes) + 16 * size_t(ns) + 64;  // slices sit at 16-aligned, disjoint offsets
   h->d_bytes.reserve(span);
@@ -510,49 +535,63 @@ int encode_host_sliced(gtk_tokenizer* h, int mode, const uint8_t* bytes, const i
     if (longest > gtk::kHalo)
       h->d_seg_scratch.reserve(size_t(std::max(h->opt_grid, h->base_grid)) * 2 * size_t((longest + 63) & ~int64_t(63)) * 2);
   }
+  h->d_piece_off.reserve(size_t(piece_at[nsz]) * 8);
+  h->d_piece_id_off.reserve(size_t(piece_at[nsz]) * 8);
+  h->d_chunk_id_all.reserve(size_t(chunk_at[nsz]) * 8);
+  h->h_piece_off.reserve(size_t(piece_at[nsz]) * 8);
+  h->h_piece_id_off.reserve(size_t(piece_at[nsz]) * 8);
+  h->h_chunk_id_all.reserve(size_t(chunk_at[nsz]) * 8);
   h->h_text_id_off.reserve(size_t(n_texts + 1) * 8);
   h->h_chunk_id_off.reserve(size_t(chunk_upper_bound(n_bytes, total_pieces, h->chunk_tokens) + 2) * 8);
   h->h_ids.reserve(size_t(n_bytes) * 2);  // grown below if the batch yields more than one id per two bytes
   if (!h->in_stream) GTK_CUDA(cudaStreamCreateWithFlags(&h->in_stream, cudaStreamNonBlocking));
   if (!h->out_stream) GTK_CUDA(cudaStreamCreateWithFlags(&h->out_stream, cudaStreamNonBlocking));
+  if (!h->pack_stream) GTK_CUDA(cudaStreamCreateWithFlags(&h->pack_stream, cudaStreamNonBlocking));
   for (auto& a : h->slice) slice_arena_prepare(h, a, max_bytes, max_pieces);
   GTK_CUDA(cudaStreamSynchronize(h->stream));
 
-  const size_t nsz = size_t(ns);
+  for (int i = 0; i < ns; ++i) {
+    const SlicePlan& sp = slices[size_t(i)];
+    std::memcpy(h->h_piece_off.as<int64_t>() + piece_at[size_t(i)], sp.piece_off.data(), sp.piece_off.size() * 8);
+  }
+  GTK_CUDA(cudaMemcpyAsync(h->d_piece_off.p, h->h_piece_off.p, size_t(piece_at[nsz]) * 8, cudaMemcpyHostToDevice,
+                           h->in_stream));
+
   std::vector<gtk::EncodeBuffers> bufs(nsz);
-  std::vector<int64_t> sl_n(nsz), sl_c(nsz), sl_r(nsz), sl_cbase(nsz);
+  std::vector<int64_t> sl_c(nsz), sl_r(nsz), sl_cbase(nsz);
   int launches = 0;
   int64_t R = 0, Cbase = 0;
-  int64_t* h_text = h->h_text_id_off.as<int64_t>();
 
   auto issue_front = [&](int i) {
     SliceArena& a = h->slice[i % kSliceArenas];
     const SlicePlan& sp = slices[size_t(i)];
-    const int64_t pieces = int64_t(sp.piece_off.size()) - 1;
-    std::memcpy(a.h_piece_off.p, sp.piece_off.data(), size_t(pieces + 1) * 8);
     GTK_CUDA(cudaMemcpyAsync(h->d_bytes.as<uint8_t>() + slice_dev_offset(sp, i), bytes + sp.byte_lo, size_t(sp.byte_hi - sp.byte_lo),
                              cudaMemcpyHostToDevice, h->in_stream));
-    GTK_CUDA(cudaMemcpyAsync(a.text_off.p, a.h_piece_off.p, size_t(pieces + 1) * 8, cudaMemcpyHostToDevice,
-                             h->in_stream));
     GTK_CUDA(cudaEventRecord(a.ev_in, h->in_stream));
     GTK_CUDA(cudaStreamWaitEvent(h->stream, a.ev_in, 0));
     if (i >= kSliceArenas) GTK_CUDA(cudaStreamWaitEvent(h->stream, a.ev_out, 0));  // its previous slice has left this arena
-    bufs[size_t(i)] = slice_buffers(h, a, sp, i, max_bytes);
-    run_front(h, bufs[size_t(i)], mode, &launches, a.ev, a.h_totals.as<int64_t>());
+    gtk::EncodeBuffers& b = bufs[size_t(i)];
+    b = slice_buffers(h, a, sp, i, max_bytes);
+    b.text_off     = h->d_piece_off.as<int64_t>() + piece_at[size_t(i)];
+    b.text_id_off  = h->d_piece_id_off.as<int64_t>() + piece_at[size_t(i)];
+    b.chunk_id_off = h->d_chunk_id_all.as<int64_t>() + chunk_at[size_t(i)];
+    // the four result words of the front are written into mapped host memory by a one-thread kernel
+    run_front(h, b, mode, &launches, a.ev, nullptr, static_cast<int64_t*>(a.h_totals.dp));
     GTK_CUDA(cudaEventRecord(a.ev_front, h->stream));
   };
-  auto finish = [&](int i) {  // results of slice i are on the host: stitch its text offsets
+  auto finish = [&](int i) {  // the ids of slice i are on the host
     SliceArena& a = h->slice[i % kSliceArenas];
     GTK_CUDA(cudaEventSynchronize(a.ev_out));
     collect_stage_times(h, a.ev);
-    const SlicePlan& sp = slices[size_t(i)];
-    const int64_t* pid = a.h_piece_id_off.as<int64_t>();
-    for (size_t p = 0; p < sp.first_text.size(); ++p)
-      if (sp.first_text[p] >= 0) h_text[sp.first_text[p]] = sl_r[size_t(i)] + pid[p];
+  };
+  auto sync_all = [&] {
+    cudaStreamSynchronize(h->in_stream);
+    cudaStreamSynchronize(h->stream);
+    cudaStreamSynchronize(h->pack_stream);
+    cudaStreamSynchronize(h->out_stream);
   };
 
-  // a text that starts exactly where the previous slice ended is handled by whichever slice holds its first piece
-  constexpr int kAhead = kSliceArenas - 1;  // kernel pipelines queued ahead of the slice being packed
+  constexpr int kAhead = kSliceArenas - 1;  // fronts queued ahead of the slice being packed
   for (int i = 0; i < std::min(ns, kAhead); ++i) issue_front(i);
   for (int i = 0; i < ns; ++i) {
     SliceArena& a = h->slice[i % kSliceArenas];
@@ -562,8 +601,7 @@ int encode_host_sliced(gtk_tokenizer* h, int mode, const uint8_t* bytes, const i
     const int64_t C = ht[0], N = ht[1];
     const int status = reinterpret_cast<const int32_t*>(ht + 2)[1];
     if (status != gtk::kStatusOk) {
-      cudaStreamSynchronize(h->stream);
-      cudaStreamSynchronize(h->out_stream);
+      sync_all();
       return h->fail(GTK_ERR_KERNEL, status_text(status));
     }
     if (size_t(R + N + 1) * 4 > h->h_ids.cap) {  // grow the pinned id buffer, keeping what has arrived
@@ -574,33 +612,42 @@ int encode_host_sliced(gtk_tokenizer* h, int mode, const uint8_t* bytes, const i
       h->h_ids.release();
       h->h_ids = bigger;
     }
-    run_pack(h, bufs[size_t(i)], mode, &launches, a.ev);
-    GTK_CUDA(cudaEventRecord(a.ev_packed, h->stream));
+    // the pack runs on a stream of its own: the compute stream already holds the fronts of later slices
+    GTK_CUDA(cudaStreamWaitEvent(h->pack_stream, a.ev_front, 0));
+    run_pack(h, bufs[size_t(i)], mode, &launches, a.ev, h->pack_stream);
+    GTK_CUDA(cudaEventRecord(a.ev_packed, h->pack_stream));
     GTK_CUDA(cudaStreamWaitEvent(h->out_stream, a.ev_packed, 0));
-    const gtk::EncodeBuffers& b = bufs[size_t(i)];
-    GTK_CUDA(cudaMemcpyAsync(h->h_ids.as<int32_t>() + R, b.out_ids, size_t(N) * 4, cudaMemcpyDeviceToHost,
-                             h->out_stream));
-    GTK_CUDA(cudaMemcpyAsync(h->h_chunk_id_off.as<int64_t>() + Cbase, b.chunk_id_off, size_t(C + 1) * 8,
-                             cudaMemcpyDeviceToHost, h->out_stream));
-    GTK_CUDA(cudaMemcpyAsync(a.h_piece_id_off.p, b.text_id_off, size_t(b.n_texts + 1) * 8, cudaMemcpyDeviceToHost,
+    GTK_CUDA(cudaMemcpyAsync(h->h_ids.as<int32_t>() + R, bufs[size_t(i)].out_ids, size_t(N) * 4, cudaMemcpyDeviceToHost,
                              h->out_stream));
     GTK_CUDA(cudaEventRecord(a.ev_out, h->out_stream));
-    sl_n[size_t(i)] = N;
-    sl_c[size_t(i)] = C;
-    sl_r[size_t(i)] = R;
+    sl_c[size_t(i)]     = C;
+    sl_r[size_t(i)]     = R;
     sl_cbase[size_t(i)] = Cbase;
     R += N;
     Cbase += C;
     if (i + kAhead < ns) issue_front(i + kAhead);
   }
+  // offsets of all slices in two copies behind the last ids
+  GTK_CUDA(cudaMemcpyAsync(h->h_piece_id_off.p, h->d_piece_id_off.p, size_t(piece_at[nsz]) * 8, cudaMemcpyDeviceToHost,
+                           h->out_stream));
+  GTK_CUDA(cudaMemcpyAsync(h->h_chunk_id_all.p, h->d_chunk_id_all.p, size_t(chunk_at[nsz]) * 8, cudaMemcpyDeviceToHost,
+                           h->out_stream));
   for (int i = std::max(0, ns - 2); i < ns; ++i) finish(i);
+  GTK_CUDA(cudaStreamSynchronize(h->out_stream));
   GTK_CUDA(cudaStreamSynchronize(h->stream));
-  // per-slice chunk offsets start at 0: add the ids that precede the slice
+  // per-slice offsets start at 0: add the ids that precede the slice.  A text that starts exactly where the
+  // previous slice ended belongs to the slice that holds its first piece.
+  int64_t* h_text  = h->h_text_id_off.as<int64_t>();
   int64_t* h_chunk = h->h_chunk_id_off.as<int64_t>();
   for (int i = 0; i < ns; ++i) {
-    const int64_t base = sl_r[size_t(i)];
-    if (base)
-      for (int64_t c = sl_cbase[size_t(i)]; c < sl_cbase[size_t(i)] + sl_c[size_t(i)]; ++c) h_chunk[c] += base;
+    const SlicePlan& sp = slices[size_t(i)];
+    const int64_t base  = sl_r[size_t(i)];
+    const int64_t* pid  = h->h_piece_id_off.as<int64_t>() + piece_at[size_t(i)];
+    for (size_t p = 0; p < sp.first_text.size(); ++p)
+      if (sp.first_text[p] >= 0) h_text[sp.first_text[p]] = base + pid[p];
+    const int64_t* src = h->h_chunk_id_all.as<int64_t>() + chunk_at[size_t(i)];
+    int64_t* dst       = h_chunk + sl_cbase[size_t(i)];
+    for (int64_t c = 0; c < sl_c[size_t(i)]; ++c) dst[c] = src[c] + base;
   }
   h_chunk[Cbase] = R;
   h_text[n_texts] = R;
@@ -785,12 +832,14 @@ GTK_API void gtk_destroy(gtk_tokenizer* h)
                       &h->d_unit_cnt, &h->d_chunk_cnt, &h->d_unit_base, &h->d_chunk_id_off, &h->d_text_id_off,
                       &h->d_out_ids, &h->d_seg_scratch, &h->d_scan_sums, &h->d_counters, &h->d_totals})
       b->release();
-    for (PinBuf* b : {&h->h_ids, &h->h_text_id_off, &h->h_chunk_id_off, &h->h_totals}) b->release();
+    for (PinBuf* b : {&h->h_ids, &h->h_text_id_off, &h->h_chunk_id_off, &h->h_totals, &h->h_piece_off, &h->h_piece_id_off, &h->h_chunk_id_all}) b->release();
+    for (DevBuf* b : {&h->d_piece_off, &h->d_piece_id_off, &h->d_chunk_id_all}) b->release();
     if (h->small_in_h) cudaFreeHost(h->small_in_h);
     if (h->small_out_h) cudaFreeHost(h->small_out_h);
     for (auto& sl : h->slice) sl.release();
     if (h->in_stream) cudaStreamDestroy(h->in_stream);
     if (h->out_stream) cudaStreamDestroy(h->out_stream);
+    if (h->pack_stream) cudaStreamDestroy(h->pack_stream);
     for (auto& ev : h->ev)
       if (ev) cudaEventDestroy(ev);
     if (h->own_stream) cudaStreamDestroy(h->own_stream);

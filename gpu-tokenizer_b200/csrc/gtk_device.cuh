@@ -102,6 +102,8 @@ int launch_merge_base(const EncodeBuffers& b, const DeviceTable& t, int grid, cu
 int launch_merge_localmin(const EncodeBuffers& b, const DeviceTable& t, int grid, int max_iters, cudaStream_t stream);
 int launch_output_scans(const EncodeBuffers& b, int mode_base, cudaStream_t stream);
 int launch_pack(const EncodeBuffers& b, int mode_base, int grid, cudaStream_t stream);
+// totals[0..1] and counters[0..3] to `mapped` (page-locked host memory as the device sees it), laid out as 4 x int64
+int launch_publish_totals(const EncodeBuffers& b, int64_t* mapped, cudaStream_t stream);
 // Whole pipeline in one single-CTA kernel for small batches; totals[0..2] receive n_chunks, n_ids, status.
 int launch_encode_small(const EncodeBuffers& b, const DeviceTable& t, cudaStream_t stream);
 constexpr int64_t kSmallMaxBytes = 32768;

@@ -2145,6 +2145,26 @@ extern "C" __attribute__((visibility("default"))) void gtk_debug_phase_cycles(un
 }
 #endif
 
+__global__ void k_publish_totals(const int64_t* totals, const int32_t* counters, int64_t* mapped)
+{
+  if (threadIdx.x == 0) {
+    mapped[0] = totals[0];
+    mapped[1] = totals[1];
+    int32_t* c = reinterpret_cast<int32_t*>(mapped + 2);
+    c[0] = counters[0];
+    c[1] = counters[1];
+    c[2] = counters[2];
+    c[3] = counters[3];
+    __threadfence_system();
+  }
+}
+
+int launch_publish_totals(const EncodeBuffers& b, int64_t* mapped, cudaStream_t stream)
+{
+  k_publish_totals<<<1, 32, 0, stream>>>(b.totals, b.counters, mapped);
+  return 1;
+}
+
 int opt_kernel_max_blocks_per_sm()
 {
   int nb = 0;
