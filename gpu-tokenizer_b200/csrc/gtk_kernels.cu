@@ -308,49 +308,6 @@ __device__ __forceinline__ bool thread_merge_step(uint16_t* tok_all, uint16_t* r
   return true;
 }
 
-// Every lane merges its own segment [s, s+L) to the end (s < 0: no segment).  Kept out of line so that
-// the loop gets registers of its own instead of sharing them with the tile code around the call.
-__device__ __noinline__ uint32_t thread_merge_segments(uint16_t* tok, uint16_t* rk, int s, int L, PairTable P)
-{
-  uint32_t alive = 0, best = 0xFFFFFFFFu;
-  if (s >= 0) {
-    alive = (L >= 32) ? 0xFFFFFFFFu : ((1u << L) - 1u);
-    best  = segment_argmin(rk, s, L);
-  }
-#ifdef GTK_PHASE_TIMING
-  if (threadIdx.x == 0) {  // in-situ latency of one table load and of one rank scan
-    const long long a0 = clock64();
-    const uint4 v      = __ldg(P.buckets + (uint32_t(a0) * 2654435761u >> 16));
-    const long long a1 = clock64() + (v.x == 0x12345u);
-    atomicAdd(&g_phase_cycles[16], (unsigned long long)(a1 - a0));
-    atomicAdd(&g_phase_cycles[17], 1ull);
-    if (s >= 0) {
-      const long long b0 = clock64();
-      const uint32_t bb  = segment_argmin(rk, s, L);
-      const long long b1 = clock64() + (bb == 0x12345u);
-      atomicAdd(&g_phase_cycles[18], (unsigned long long)(b1 - b0));
-      atomicAdd(&g_phase_cycles[19], 1ull);
-      atomicAdd(&g_phase_cycles[20], (unsigned long long)L);
-    }
-  }
-  const long long t0 = clock64();
-  int steps          = 0;
-#endif
-  while (__any_sync(0xFFFFFFFFu, best < (SEL << 16))) {
-    if (best < (SEL << 16)) thread_merge_step(tok, rk, s, L, alive, best, P);
-#ifdef GTK_PHASE_TIMING
-    ++steps;
-#endif
-  }
-#ifdef GTK_PHASE_TIMING
-  if (threadIdx.x == 0) {  // warp 0: loop trips and their wall cycles
-    atomicAdd(&g_phase_cycles[14], (unsigned long long)(clock64() - t0));
-    atomicAdd(&g_phase_cycles[15], (unsigned long long)steps);
-  }
-#endif
-  return alive;
-}
-
 // ------------------------------------------------------------------------------------------------
 // A group of NW warps (one warp, or the whole CTA) merges one sequence pass by
 // pass.  tok/rk may point to shared memory or to an HBM workspace.
@@ -768,6 +725,54 @@ struct OptSmem {
   int end_owned;
 };
 
+// One instance per CTA; the kernels below and the out-of-line merge loop name it directly.
+__shared__ OptSmem g_tile;
+
+// Every lane merges its own segment [s, s+L) to the end (s < 0: no segment).  Kept out of line so that
+// the loop gets registers of its own instead of sharing them with the tile code around the call.
+__device__ __noinline__ uint32_t thread_merge_segments(int s, int L, PairTable P)
+{
+  uint16_t* tok = g_tile.tok;  // named directly so that the accesses compile to shared-memory instructions
+  uint16_t* rk  = g_tile.rk;
+  uint32_t alive = 0, best = 0xFFFFFFFFu;
+  if (s >= 0) {
+    alive = (L >= 32) ? 0xFFFFFFFFu : ((1u << L) - 1u);
+    best  = segment_argmin(rk, s, L);
+  }
+#ifdef GTK_PHASE_TIMING
+  if (threadIdx.x == 0) {  // in-situ latency of one table load and of one rank scan
+    const long long a0 = clock64();
+    const uint4 v      = __ldg(P.buckets + (uint32_t(a0) * 2654435761u >> 16));
+    const long long a1 = clock64() + (v.x == 0x12345u);
+    atomicAdd(&g_phase_cycles[16], (unsigned long long)(a1 - a0));
+    atomicAdd(&g_phase_cycles[17], 1ull);
+    if (s >= 0) {
+      const long long b0 = clock64();
+      const uint32_t bb  = segment_argmin(rk, s, L);
+      const long long b1 = clock64() + (bb == 0x12345u);
+      atomicAdd(&g_phase_cycles[18], (unsigned long long)(b1 - b0));
+      atomicAdd(&g_phase_cycles[19], 1ull);
+      atomicAdd(&g_phase_cycles[20], (unsigned long long)L);
+    }
+  }
+  const long long t0 = clock64();
+  int steps          = 0;
+#endif
+  while (__any_sync(0xFFFFFFFFu, best < (SEL << 16))) {
+    if (best < (SEL << 16)) thread_merge_step(tok, rk, s, L, alive, best, P);
+#ifdef GTK_PHASE_TIMING
+    ++steps;
+#endif
+  }
+#ifdef GTK_PHASE_TIMING
+  if (threadIdx.x == 0) {  // warp 0: loop trips and their wall cycles
+    atomicAdd(&g_phase_cycles[14], (unsigned long long)(clock64() - t0));
+    atomicAdd(&g_phase_cycles[15], (unsigned long long)steps);
+  }
+#endif
+  return alive;
+}
+
 // first segment start strictly after window position s (words past the window are all ones)
 __device__ __forceinline__ int next_cut(const uint32_t* cut, int s)
 {
@@ -889,13 +894,22 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
 #pragma unroll
       for (int k = 0; k < 5; ++k) info[k] = __ldg(T.byte_pair_info + ((by[k] << 8) | by[k + 1]));
       uint32_t nib = 0, t[4], r[4];
+      if (i0 + 5 <= wlen && lo + i0 > 0) {  // the four positions and their right neighbours all hold text
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int i      = i0 + k;
-        const bool start = (i >= wlen) || (lo + i == 0) || (info[k] == 0xFFFFu);
-        nib |= uint32_t(start) << k;
-        t[k] = (i < wlen) ? (identity_ids ? by[k + 1] : uint32_t(__ldg(T.byte_to_id + by[k + 1]))) : DEAD;
-        r[k] = ((i + 1 < wlen) && info[k + 1] < SEL) ? info[k + 1] : NONE;
+        for (int k = 0; k < 4; ++k) {
+          nib |= uint32_t(info[k] == 0xFFFFu) << k;
+          t[k] = identity_ids ? by[k + 1] : uint32_t(__ldg(T.byte_to_id + by[k + 1]));
+          r[k] = (info[k + 1] < SEL) ? info[k + 1] : NONE;
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int i      = i0 + k;
+          const bool start = (i >= wlen) || (lo + i == 0) || (info[k] == 0xFFFFu);
+          nib |= uint32_t(start) << k;
+          t[k] = (i < wlen) ? (identity_ids ? by[k + 1] : uint32_t(__ldg(T.byte_to_id + by[k + 1]))) : DEAD;
+          r[k] = ((i + 1 < wlen) && info[k + 1] < SEL) ? info[k + 1] : NONE;
+        }
       }
       const uint32_t word = __reduce_or_sync(0xFFu << (lane & 24), nib << (4 * (lane & 7)));
       if ((lane & 7) == 0) S.cut[g >> 3] = word;
@@ -1110,7 +1124,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
         s = S.seg[tid];
         L = next_cut(S.cut, s) - s;
       }
-      const uint32_t alive = thread_merge_segments(S.tok, S.rk, s, L, pair_table(T));
+      const uint32_t alive = thread_merge_segments(s, L, pair_table(T));
       if (!SPLIT && s >= 0) mark_alive(S.cut, s, alive);
       if (!SPLIT && b.memo && s >= 0) {
         uint32_t k[8];
@@ -1369,7 +1383,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
 
 __global__ void __launch_bounds__(kOptThreads, 8) k_merge_opt(EncodeBuffers b, DeviceTable T)
 {
-  __shared__ OptSmem S;
+  OptSmem& S = g_tile;
   const int tid   = threadIdx.x;
   const int64_t C = b.totals[0];
   opt_tile_setup(S, T);
@@ -1391,7 +1405,7 @@ __global__ void __launch_bounds__(kOptThreads, 8) k_merge_opt(EncodeBuffers b, D
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kOptThreads) k_front_split(EncodeBuffers b, DeviceTable T)
 {
-  __shared__ OptSmem S;
+  OptSmem& S = g_tile;
   const int tid   = threadIdx.x;
   const int64_t C = b.totals[0];
   opt_tile_setup(S, T);
@@ -1786,7 +1800,7 @@ __device__ int64_t cta_exclusive_scan(F f, int64_t n, int64_t* out, int* scanbuf
 
 __global__ void __launch_bounds__(kOptThreads) k_encode_small(EncodeBuffers b, DeviceTable T)
 {
-  __shared__ OptSmem S;
+  OptSmem& S = g_tile;
   __shared__ int64_t carry_s;
   const int tid = threadIdx.x;
   opt_tile_setup(S, T);
