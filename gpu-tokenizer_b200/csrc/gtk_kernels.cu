@@ -94,15 +94,14 @@ __device__ __forceinline__ uint32_t probe_rank(const DeviceTable& T, uint32_t le
 // Whole-segment table: id of the vocabulary string (k0,k1,k2 = bytes zero padded, L = length)
 // if the greedy rule turns exactly that string into one token, else 0xFFFFFFFF.  Two-choice cuckoo
 // table: both candidate slots are loaded at once.
-__device__ __forceinline__ uint32_t word_lookup(const DeviceTable& T, uint32_t k0, uint32_t k1, uint32_t k2,
-                                                uint32_t L)
+__device__ __forceinline__ uint32_t word_lookup(const uint4* word_slots, uint32_t sh, uint32_t k0, uint32_t k1,
+                                                uint32_t k2, uint32_t L)
 {
   uint32_t m = (k0 * 0x9E3779B1u) ^ (k1 * 0x85EBCA77u) ^ (k2 * 0xC2B2AE3Du);
   m ^= m >> 15;
   m *= 0x2C1B3C6Du;
-  const uint32_t sh = 32 - T.word_log2_capacity;
-  const uint4 a = __ldg(T.word_slots + (m >> sh));
-  const uint4 c = __ldg(T.word_slots + (((m ^ (m >> 13)) * 0x165667B1u) >> sh));
+  const uint4 a = __ldg(word_slots + (m >> sh));
+  const uint4 c = __ldg(word_slots + (((m ^ (m >> 13)) * 0x165667B1u) >> sh));
   const uint32_t meta = (L << 16);
   if (a.x == k0 && a.y == k1 && a.z == k2 && (a.w & 0xFFFF0000u) == meta) return a.w & 0xFFFFu;
   if (c.x == k0 && c.y == k1 && c.z == k2 && (c.w & 0xFFFF0000u) == meta) return c.w & 0xFFFFu;
@@ -782,6 +781,64 @@ __device__ __forceinline__ int next_cut(const uint32_t* cut, int s)
   return w * 32 + __ffs(int(x)) - 1;
 }
 
+// Step D/E1 of a tile, out of line so that it gets registers of its own: every thread walks the multi-byte
+// segments that start in its 16 positions (window positions [16*tid, 16*tid+16), owned ones only).
+template <bool SPLIT>
+__device__ __noinline__ void walk_segments(const uint4* word_slots, uint32_t word_shift, int own, int wlen,
+                                           int* status)
+{
+  OptSmem& S     = g_tile;
+  const int tid  = threadIdx.x, lane = tid & 31;
+  const uint32_t lt = lanemask_lt();
+  const int base = tid * 16;
+  uint32_t m16   = 0;
+  if (base < own) {
+    const uint32_t w32     = __funnelshift_r(S.cut[tid >> 1], S.cut[(tid >> 1) + 1], (tid & 1) * 16);
+    const uint32_t ownmask = (base + 16 <= own) ? 0xFFFFu : ((1u << (own - base)) - 1u);
+    m16 = w32 & ~(w32 >> 1) & ownmask;  // starts whose next position is not a start
+  }
+#ifdef GTK_PHASE_TIMING
+  atomicAdd(&S.nseg, __popc(m16));
+#endif
+  while (__any_sync(0xFFFFFFFFu, m16 != 0)) {
+    bool miss = false;
+    int ss    = 0;
+    if (m16) {
+      ss = base + __ffs(int(m16)) - 1;
+      m16 &= m16 - 1;
+      const int e  = next_cut(S.cut, ss);
+      const int LL = e - ss;
+      if (e >= kWindow && wlen == kWindow) {
+        S.over_start = ss;  // runs past the window: finished in the HBM workspace
+      } else if (LL > kThreadSegMax) {
+        const int q = atomicAdd(&S.nlong, 1);
+        if (q < kLongCap) S.longq[q] = uint16_t(ss);
+        else atomicMax(status, int(kStatusLongQueueOverflow));
+      } else {
+        miss = true;
+        if (LL <= 12) {
+          uint32_t k0, k1, k2;
+          segment_key(S.bytes, 16 + ss, LL, k0, k1, k2);
+          const uint32_t id = word_lookup(word_slots, word_shift, k0, k1, k2, uint32_t(LL));
+          if (id != 0xFFFFFFFFu) {
+            miss      = false;
+            S.tok[ss] = uint16_t(id);
+            if (SPLIT)  // the split pipeline stores tokens by position, tombstones included
+              for (int i = 1; i < LL; ++i) S.tok[ss + i] = uint16_t(DEAD);
+          }
+        }
+      }
+    }
+    const uint32_t bal = __ballot_sync(0xFFFFFFFFu, miss);
+    if (bal) {
+      int wbase = 0;
+      if (lane == 0) wbase = atomicAdd(&S.nmiss, __popc(bal));
+      wbase = __shfl_sync(0xFFFFFFFFu, wbase, 0);
+      if (miss) S.seg[wbase + __popc(bal & lt)] = uint16_t(ss);
+    }
+  }
+}
+
 // The segment-start bitmap turns into the bitmap of live tokens as segments finish: the first token of a
 // segment is always live, so a finished segment adds the bits of its other live slots (`a`, relative to
 // its start s; bit 0 is ignored).  Only bits inside the segment change, so next_cut() of any other
@@ -953,55 +1010,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
           atomicMax(&S.end_owned, next_cut(S.cut, last));
         }
       }
-      const int base = tid * 16;
-      uint32_t m16   = 0;
-      if (base < own) {
-        const uint32_t w32     = __funnelshift_r(S.cut[tid >> 1], S.cut[(tid >> 1) + 1], (tid & 1) * 16);
-        const uint32_t ownmask = (base + 16 <= own) ? 0xFFFFu : ((1u << (own - base)) - 1u);
-        m16 = w32 & ~(w32 >> 1) & ownmask;  // starts whose next position is not a start
-      }
-      int nseg_mine = 0;
-      while (__any_sync(0xFFFFFFFFu, m16 != 0)) {
-        bool miss = false;
-        int ss    = 0;
-        if (m16) {
-          ss = base + __ffs(int(m16)) - 1;
-          m16 &= m16 - 1;
-          ++nseg_mine;
-          const int e  = next_cut(S.cut, ss);
-          const int LL = e - ss;
-          if (e >= kWindow && wlen == kWindow) {
-            S.over_start = ss;  // runs past the window: finished in the HBM workspace below
-          } else if (LL > kThreadSegMax) {
-            const int q = atomicAdd(&S.nlong, 1);
-            if (q < kLongCap) S.longq[q] = uint16_t(ss);
-            else atomicMax(status, int(kStatusLongQueueOverflow));
-          } else {
-            miss = true;
-            if (LL <= 12) {
-              uint32_t k0, k1, k2;
-              segment_key(S.bytes, 16 + ss, LL, k0, k1, k2);
-              const uint32_t id = word_lookup(T, k0, k1, k2, uint32_t(LL));
-              if (id != 0xFFFFFFFFu) {
-                miss      = false;
-                S.tok[ss] = uint16_t(id);
-                if (SPLIT)  // the split pipeline stores tokens by position, tombstones included
-                  for (int i = 1; i < LL; ++i) S.tok[ss + i] = uint16_t(DEAD);
-              }
-            }
-          }
-        }
-        const uint32_t bal = __ballot_sync(0xFFFFFFFFu, miss);
-        if (bal) {
-          int wbase = 0;
-          if (lane == 0) wbase = atomicAdd(&S.nmiss, __popc(bal));
-          wbase = __shfl_sync(0xFFFFFFFFu, wbase, 0);
-          if (miss) S.seg[wbase + __popc(bal & lt)] = uint16_t(ss);
-        }
-      }
-#ifdef GTK_PHASE_TIMING
-      atomicAdd(&S.nseg, nseg_mine);
-#endif
+      walk_segments<SPLIT>(T.word_slots, 32u - T.word_log2_capacity, own, wlen, status);
     }
     __syncthreads();
     GTK_PHASE(3);
