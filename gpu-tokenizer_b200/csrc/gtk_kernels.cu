@@ -2020,21 +2020,36 @@ __global__ void __launch_bounds__(kBaseThreads) k_merge_localmin(EncodeBuffers b
 // ------------------------------------------------------------------------------------------------
 // output: pack staged 16-bit tokens of every unit into the int32 id buffer
 // ------------------------------------------------------------------------------------------------
+// One warp per unit (a tile's or a chunk's compacted tokens): the ids of a unit are written in groups of
+// four as one 16-byte store once the destination is aligned; the 16-bit source tokens are read through L1.
 __global__ void __launch_bounds__(256) k_pack(const uint16_t* __restrict__ staging, const int64_t* __restrict__ first,
                                               const int32_t* __restrict__ cnt, const int64_t* __restrict__ base,
                                               int64_t n_units_imm, const int64_t* n_units_ptr,
                                               int32_t* __restrict__ out, int64_t capacity,
                                               const uint16_t* __restrict__ low_id_map)
 {
-  const int64_t U = n_units_ptr ? *n_units_ptr : n_units_imm;
-  for (int64_t u = blockIdx.x; u < U; u += gridDim.x) {
+  const int64_t U    = n_units_ptr ? *n_units_ptr : n_units_imm;
+  const int lane     = threadIdx.x & 31;
+  const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nw   = (int64_t(gridDim.x) * blockDim.x) >> 5;
+  for (int64_t u = warp; u < U; u += nw) {
     const int64_t src = first[u], dst = base[u];
-    const int m = cnt[u];
-    for (int j = threadIdx.x; j < m; j += blockDim.x)
-      if (dst + j < capacity) {
-        const uint32_t t = staging[src + j];
-        out[dst + j]     = int32_t((low_id_map && t < 256u) ? uint32_t(__ldg(low_id_map + t)) : t);
-      }
+    int64_t m = cnt[u];
+    if (dst + m > capacity) m = capacity > dst ? capacity - dst : 0;
+    const uint16_t* sp = staging + src;
+    int32_t* dp        = out + dst;
+    auto conv = [&](uint32_t t) { return int32_t((low_id_map && t < 256u) ? uint32_t(__ldg(low_id_map + t)) : t); };
+    // head: up to three ids until the destination is 16-byte aligned
+    const int64_t head = min(m, int64_t(((16u - uint32_t(reinterpret_cast<uintptr_t>(dp) & 15u)) >> 2) & 3u));
+    if (lane < head) dp[lane] = conv(sp[lane]);
+    const int64_t quads = (m - head) >> 2;
+    for (int64_t q = lane; q < quads; q += 32) {
+      const uint16_t* s4 = sp + head + 4 * q;
+      const int4 v = make_int4(conv(s4[0]), conv(s4[1]), conv(s4[2]), conv(s4[3]));
+      *reinterpret_cast<int4*>(dp + head + 4 * q) = v;
+    }
+    const int64_t done = head + 4 * quads;
+    if (done + lane < m) dp[done + lane] = conv(sp[done + lane]);
   }
 }
 

@@ -149,6 +149,7 @@ HostTable::HostTable(const std::string& merges_path)
   build_hash();
   build_derived();
   build_words();
+  if (fits_u16) verify_device_tables();
 }
 
 void HostTable::build_hash()
@@ -238,6 +239,39 @@ void HostTable::build_pair_buckets()
       pair_overflow[h] = e;
     }
   }
+}
+
+// The kernels' probe sequences, replayed on the host over the arrays that will be uploaded: every merge
+// must come back with its rank, every placed string with its id.
+void HostTable::verify_device_tables() const
+{
+  for (const MergeRow& r : rows) {
+    const uint32_t key = (uint32_t(r.left) << 16) | uint32_t(r.right);
+    const uint32_t h   = key * kPairMul;
+    const PairBucket& b = pair_buckets[h >> 16];
+    uint32_t got = 0xFFFFu;
+    for (int i = 0; i < 4; ++i)
+      if ((b.w[i] & 0xFFFFu) == (h & 0xFFFFu)) got = b.w[i] >> 16;
+    if (got >= kSelRank16 && (b.w[3] >> 16) != 0xFFFFu && !pair_overflow.empty()) {
+      const size_t mask = pair_overflow.size() - 1;
+      size_t at = ((key * 0x85EBCA77u) >> 7) & mask;
+      for (size_t d = 0; d <= mask && pair_overflow[at].key != 0xFFFFFFFFu; ++d, at = (at + 1) & mask)
+        if (pair_overflow[at].key == key) { got = pair_overflow[at].rank; break; }
+    }
+    if (got != r.rank) throw std::runtime_error("internal error: device pair table does not return a merge's rank");
+  }
+  uint32_t found = 0;
+  for (const WordSlot& w : word_slots) {
+    if (w.meta == 0) continue;
+    const uint32_t m = word_mix(w.k0, w.k1, w.k2);
+    const WordSlot& a = word_slots[word_hash_a(m, word_log2_capacity)];
+    const WordSlot& c = word_slots[word_hash_b(m, word_log2_capacity)];
+    const bool at_a = a.k0 == w.k0 && a.k1 == w.k1 && a.k2 == w.k2 && a.meta == w.meta;
+    const bool at_c = c.k0 == w.k0 && c.k1 == w.k1 && c.k2 == w.k2 && c.meta == w.meta;
+    if (!at_a && !at_c) throw std::runtime_error("internal error: whole-segment table entry is not at either of its slots");
+    ++found;
+  }
+  if (found + word_dropped != word_count) throw std::runtime_error("internal error: whole-segment table lost entries");
 }
 
 bool HostTable::find(int32_t left, int32_t right, uint32_t* rank, int32_t* merged) const

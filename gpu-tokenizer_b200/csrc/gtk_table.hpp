@@ -146,6 +146,7 @@ class HostTable {
   void build_derived();
   void build_words();
   void build_pair_buckets();
+  void verify_device_tables() const;
 };
 
 }  // namespace gtk

@@ -77,3 +77,39 @@ def first_mismatch(a: np.ndarray, b: np.ndarray) -> str:
         i = int(d[0])
         return f"first difference at {i}: {a[max(0, i - 4):i + 6].tolist()} vs {b[max(0, i - 4):i + 6].tolist()}"
     return f"lengths {len(a)} vs {len(b)}"
+
+
+def crowded_bucket_merges(merges_path: str, out_path: str):
+    """A merges file whose pair table has a crowded bucket, and text that probes it.
+
+    The device pair table hashes key = left << 16 | right with h = key * 0x9E3779B1 (mod 2**32) into
+    bucket h >> 16, four entries per bucket; further keys of a bucket go to a side table.  1024
+    first-level merges of byte pairs (ranks 0..1023, ids 256..1279) are followed by second-level
+    merges (first-level id, byte) that all fall into the fullest bucket, so at least two of them
+    live in the side table.  Returns (text bytes, number of second-level merges).
+    """
+    from gputok_b200 import Tokenizer
+
+    base = Tokenizer(merges_path, 2048, 50, device=-1)
+    sym = [base.token_symbols(b).decode("utf-8") for b in range(256)]
+    first = [(a, (a + d) % 256) for d in (3, 50, 101, 200) for a in range(256)]
+    assert len(set(first)) == len(first)
+    buckets: dict[int, list[tuple[int, int]]] = {}
+    for i in range(len(first)):
+        for x in range(256):
+            key = ((256 + i) << 16) | x
+            buckets.setdefault(((key * 0x9E3779B1) & 0xFFFFFFFF) >> 16, []).append((i, x))
+    crowd = max(buckets.values(), key=len)
+    assert len(crowd) >= 6
+    lines = ["#version: 0.2"] + [f"{sym[a]} {sym[b]}" for a, b in first]
+    lines += [f"{sym[first[i][0]]}{sym[first[i][1]]} {sym[x]}" for i, x in crowd]
+    with open(out_path, "w", encoding="utf-8") as f:
+        f.write("\n".join(lines) + "\n")
+    rng = np.random.default_rng(5)
+    parts = []
+    for _ in range(4000):
+        i, x = crowd[int(rng.integers(len(crowd)))]
+        parts.append(bytes([first[i][0], first[i][1], x]))
+        if rng.random() < 0.3:
+            parts.append(bytes(rng.integers(0, 256, int(rng.integers(1, 4)), dtype=np.uint8)))
+    return b"".join(parts), len(crowd)

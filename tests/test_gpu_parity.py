@@ -216,6 +216,28 @@ def test_long_and_huge_segments_in_a_large_batch(lib, merges_path, oracle):
     assert t.decode(ids[:coff[20]]) == filler[:chunk_off[20]].tobytes()
 
 
+def test_crowded_pair_bucket(lib, merges_path, tmp_path):
+    """More than four pairs in one bucket of the device pair table: the fifth and later ones are found in
+    the side table (second load), in every kernel that probes."""
+    from conftest import crowded_bucket_merges
+    from oracle.loader import Oracle
+
+    path = str(tmp_path / "crowded_merges.txt")
+    text, n_second = crowded_bucket_merges(merges_path, path)
+    data = np.frombuffer(text, np.uint8)
+    want, woff = Oracle(path).encode_fixed(data, 512)
+    assert (want >= 1280).sum() > 100
+    t = lib.Tokenizer(path, 512, 50, device=0)
+    assert t.table_info()["hash_overflow_entries"] >= 2
+    for mode in (lib.GTK_MODE_OPT, lib.GTK_MODE_BASE):
+        ids, _, coff, _ = t.encode(data, mode=mode)
+        check_chunks(ids, coff, want, woff, f"crowded bucket, mode {mode}")
+    big = np.tile(data, 40)  # a batch large enough for the multi-CTA tile kernel (not the single-CTA path)
+    want, woff = Oracle(path).encode_fixed(big, 512, threads=NCPU)
+    ids, _, coff, _ = t.encode(big)
+    check_chunks(ids, coff, want, woff, "crowded bucket, tiled")
+
+
 def test_random_small_batches(lib, merges_path, oracle):
     """Many short texts of assorted lengths in one batch (latency-mode strings, ragged)."""
     rng = np.random.default_rng(11)

@@ -41,6 +41,23 @@ def test_table_info(native_built, merges_path):
     assert ti["device"] == -1
 
 
+def test_crowded_pair_bucket_on_the_host(native_built, merges_path, tmp_path):
+    """Pairs beyond the fourth of a bucket live in the side table; the host rule does not care."""
+    from conftest import crowded_bucket_merges
+    from gputok_b200 import Tokenizer
+    from oracle.loader import Oracle
+
+    path = str(tmp_path / "crowded_merges.txt")
+    text, n_second = crowded_bucket_merges(merges_path, path)
+    t = Tokenizer(path, 512, 50, device=-1)
+    ti = t.table_info()
+    assert ti["num_merges"] == 1024 + n_second and ti["hash_overflow_entries"] >= n_second - 4 >= 2
+    ids, _, coff = t.encode_cpu(np.frombuffer(text, np.uint8))
+    want, woff = Oracle(path).encode_fixed(np.frombuffer(text, np.uint8), 512)
+    assert np.array_equal(coff, woff) and np.array_equal(ids, want)
+    assert (want >= 1280).sum() > 100  # second-level merges do happen in this text
+
+
 def test_constructor_errors(native_built, merges_path, tmp_path):
     from gputok_b200 import GtkError, Tokenizer
 
