@@ -1315,7 +1315,13 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
     // ---- I. per-chunk token counts from the alive bitmap ----
     {
       const int64_t region_end = lo + end_owned;
-      for (int64_t c = b.tile_chunk0[k] + warp; c < C; c += kOptThreads / 32) {
+      const int64_t c0         = b.tile_chunk0[k];
+      if (c0 < C && region_end <= b.chunk_off[c0 + 1]) {
+        // the owned region lies inside the chunk that holds the tile's first byte (CTA-uniform test):
+        // the count is the tile's total
+        if (tid == 0 && total > 0) atomicAdd(b.chunk_cnt + c0, total);
+      } else
+      for (int64_t c = c0 + warp; c < C; c += kOptThreads / 32) {
         const int64_t cs_g = b.chunk_off[c];
         if (cs_g >= region_end) break;
         const int64_t ce_g = b.chunk_off[c + 1];
