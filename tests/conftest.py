@@ -113,3 +113,19 @@ def crowded_bucket_merges(merges_path: str, out_path: str):
         if rng.random() < 0.3:
             parts.append(bytes(rng.integers(0, 256, int(rng.integers(1, 4)), dtype=np.uint8)))
     return b"".join(parts), len(crowd)
+
+
+def irregular_merges(merges_path: str, out_path: str, n_lines: int = 4000, seed: int = 9) -> None:
+    """A merge table without the regularities of GPT-2's file: the first ``n_lines`` merges in shuffled
+    order (a merge may outrank the merges that create its parts, and name parts that no earlier line
+    produced) with some lines repeated (a repeated pair keeps its first rank but still consumes one, so
+    merged ids stop being 256 + rank)."""
+    with open(merges_path, encoding="utf-8") as f:
+        lines = f.read().split("\n")
+    head, body = lines[0], [ln for ln in lines[1:n_lines + 1] if ln]
+    rng = np.random.default_rng(seed)
+    body = [body[i] for i in rng.permutation(len(body))]
+    for at in sorted(rng.integers(10, len(body), 60).tolist(), reverse=True):
+        body.insert(at, body[int(rng.integers(0, at))])
+    with open(out_path, "w", encoding="utf-8") as f:
+        f.write("\n".join([head] + body) + "\n")

@@ -238,6 +238,33 @@ def test_crowded_pair_bucket(lib, merges_path, tmp_path):
     check_chunks(ids, coff, want, woff, "crowded bucket, tiled")
 
 
+def test_irregular_table(lib, merges_path, novel, tmp_path):
+    """A table that is not monotone and whose merged ids are not 256 + rank: the pass kernels merge one
+    occurrence per pass, merged ids come from the per-rank array, every mode and every batch path."""
+    from conftest import irregular_merges
+    from oracle.loader import MODE_LOCALMIN, Oracle
+
+    path = str(tmp_path / "irregular_merges.txt")
+    irregular_merges(merges_path, path)
+    orc = Oracle(path)
+    t = lib.Tokenizer(path, 1000, 50, device=0)
+    ti = t.table_info()
+    assert ti["monotone"] == 0 and ti["merged_is_256_plus_rank"] == 0
+    stress = lib.TextGen(7).text(1 << 20, mix=lib.MIX_STRESS)
+    for name, data in (("novel", np.frombuffer(novel[:300_000], np.uint8)), ("stress", stress)):
+        want, woff = orc.encode_fixed(data, 1000, threads=NCPU)
+        for mode in (lib.GTK_MODE_OPT, lib.GTK_MODE_BASE):
+            ids, _, coff, _ = t.encode(data, mode=mode)
+            check_chunks(ids, coff, want, woff, f"irregular table, {name}, mode {mode}")
+    small = np.frombuffer(novel[5000:9000], np.uint8)  # single-CTA path
+    want, woff = orc.encode_fixed(small, 1000)
+    ids, _, coff, _ = t.encode(small)
+    check_chunks(ids, coff, want, woff, "irregular table, small batch")
+    want, woff = orc.encode_fixed(small, 1000, mode=MODE_LOCALMIN)
+    ids, _, coff, _ = t.encode(small, mode=lib.GTK_MODE_LOCALMIN)
+    check_chunks(ids, coff, want, woff, "irregular table, local-minimum rule")
+
+
 def test_random_small_batches(lib, merges_path, oracle):
     """Many short texts of assorted lengths in one batch (latency-mode strings, ragged)."""
     rng = np.random.default_rng(11)

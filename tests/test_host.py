@@ -58,6 +58,22 @@ def test_crowded_pair_bucket_on_the_host(native_built, merges_path, tmp_path):
     assert (want >= 1280).sum() > 100  # second-level merges do happen in this text
 
 
+def test_irregular_table_on_the_host(native_built, merges_path, novel, tmp_path):
+    from conftest import irregular_merges
+    from gputok_b200 import Tokenizer
+    from oracle.loader import Oracle
+
+    path = str(tmp_path / "irregular_merges.txt")
+    irregular_merges(merges_path, path)
+    t = Tokenizer(path, 1000, 50, device=-1)
+    ti = t.table_info()
+    assert ti["monotone"] == 0 and ti["merged_is_256_plus_rank"] == 0 and ti["byte_ids_identity"] == 1
+    data = np.frombuffer(novel[:200_000], np.uint8)
+    ids, _, coff = t.encode_cpu(data)
+    want, woff = Oracle(path).encode_fixed(data, 1000, threads=os.cpu_count() or 1)
+    assert np.array_equal(coff, woff) and np.array_equal(ids, want)
+
+
 def test_constructor_errors(native_built, merges_path, tmp_path):
     from gputok_b200 import GtkError, Tokenizer
 
