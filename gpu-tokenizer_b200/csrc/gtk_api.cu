@@ -897,12 +897,25 @@ GTK_API int gtk_encode_device(gtk_tokenizer* h, int mode, const uint8_t* d_bytes
     Plan p = plan_batch(h, d_bytes, n_bytes, d_text_offsets, n_texts, d_out_ids, out_capacity, chunk_dst, false);
     int launches = 0;
     run_front(h, p.b, mode, &launches);
+    // When the chunk offsets are scanned straight into the caller's buffer (or not wanted), the pack follows
+    // the front without a host round trip: the pack kernel itself never writes past out_capacity, and the
+    // totals are checked once at the end.
+    const bool one_sync = (!d_out_chunk_offsets || chunk_dst) && !use_split(p.b, mode);
+    if (one_sync) run_pack(h, p.b, mode, &launches);
     GTK_CUDA(cudaStreamSynchronize(h->stream));
     const int64_t* ht = h->h_totals.as<int64_t>();
     const int64_t C = ht[0], N = ht[1];
     const int status = reinterpret_cast<const int32_t*>(ht + 2)[1];
     if (status != gtk::kStatusOk) return h->fail(GTK_ERR_KERNEL, status_text(status));
     if (N > out_capacity) return h->fail(GTK_ERR_CAPACITY, "d_out_ids too small: need " + std::to_string(N) + " ids");
+    if (one_sync) {
+      collect_stage_times(h);
+      h->last_launches = launches;
+      if (n_ids) *n_ids = N;
+      if (n_chunks) *n_chunks = C;
+      if (kernel_ms) *kernel_ms = h->stage_ms[4];
+      return GTK_OK;
+    }
     if (d_out_chunk_offsets && !chunk_dst) {
       if (chunk_capacity < C + 1)
         return h->fail(GTK_ERR_CAPACITY, "d_out_chunk_offsets too small: need " + std::to_string(C + 1));

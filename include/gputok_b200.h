@@ -150,7 +150,9 @@ GTK_API int gtk_result_copy(const gtk_tokenizer* h, int32_t* ids, int64_t ids_ca
  * d_bytes (16-byte aligned for full speed), d_text_offsets[n_texts+1] (int64),
  * d_out_ids[out_capacity] and d_out_chunk_offsets[chunk_capacity] (>= number
  * of chunks + 1, may be NULL) are device pointers on the handle's device.
- * *n_ids / *n_chunks are host outputs.  Synchronous on return. */
+ * *n_ids / *n_chunks are host outputs.  Synchronous on return.  GTK_ERR_CAPACITY
+ * if a buffer is too small: nothing is written past a capacity, what was
+ * written before the error is unspecified. */
 GTK_API int gtk_encode_device(gtk_tokenizer* h, int mode, const uint8_t* d_bytes, int64_t n_bytes,
                               const int64_t* d_text_offsets, int64_t n_texts, int32_t* d_out_ids,
                               int64_t out_capacity, int64_t* d_out_chunk_offsets, int64_t chunk_capacity,
