@@ -21,6 +21,7 @@
 #include "gtk_device.cuh"
 
 #include <algorithm>
+#include <cstddef>
 
 namespace gtk {
 namespace {
@@ -705,10 +706,12 @@ constexpr int kLongCap  = 128;
 #endif
 
 struct OptSmem {
+  // seg and bytes are adjacent on purpose: once the segments have been looked up, bytes and the unused tail of
+  // seg (entries from kOptThreads on) are the rank scratch of the merge loop (lane_scratch below)
+  alignas(16) uint16_t seg[kSegCap];  // starts of the segments that missed the lookup (length = distance to the next start)
   alignas(16) uint8_t bytes[kWindow + 32];  // [15] = byte before the window, [16+i] = window position i
   alignas(8) uint16_t tok[kWindow];
   alignas(8) uint16_t rk[kWindow];  // reused as the compacted output buffer after merging
-  uint16_t seg[kSegCap];  // starts of owned short segments, longest first (length = distance to the next start)
   int hist[34];
   uint32_t cut[kCutWords + 2];  // segment-start bits; reused as the alive bitmap
   uint16_t woff[kCutWords + 2];
@@ -726,6 +729,18 @@ struct OptSmem {
 
 // One instance per CTA; the kernels below and the out-of-line merge loop name it directly.
 __shared__ OptSmem g_tile;
+
+static_assert(kSegCap % 8 == 0 && offsetof(OptSmem, bytes) == offsetof(OptSmem, seg) + kSegCap * 2,
+              "seg and bytes must be adjacent");
+// Rank scratch of the one-segment-per-thread merge loop: 32-bit words from seg[kOptThreads] to the end of bytes.
+// Warp w owns kLaneWords words per lane at word offset w * 32 * kLaneWords, lane-interleaved (word k of lane l at
+// k * 32 + l), so the 32 lanes of a rank scan hit 32 different banks.  The last warp gets what is left.
+constexpr int kLaneWords        = 8;  // 16 ranks: segments of up to 16 tokens
+constexpr int kLaneScratchWords = ((kSegCap - kOptThreads) * 2 + kWindow + 32) / 4;
+__device__ __forceinline__ uint32_t* lane_scratch()
+{
+  return reinterpret_cast<uint32_t*>(g_tile.seg + kOptThreads);
+}
 
 // Every lane merges its own segment [s, s+L) to the end (s < 0: no segment).  Kept out of line so that
 // the loop gets registers of its own instead of sharing them with the tile code around the call.
@@ -769,6 +784,75 @@ __device__ __noinline__ uint32_t thread_merge_segments(int s, int L, PairTable P
     atomicAdd(&g_phase_cycles[15], (unsigned long long)steps);
   }
 #endif
+  return alive;
+}
+
+// The same loop with the ranks of every segment copied into the lane-interleaved scratch first (WW words =
+// 2 * WW ranks per lane, uniform over the warp): the rank scan is unrolled, needs no alignment handling and is
+// free of bank conflicts; the tokens stay in place.
+template <int WW>
+__device__ __noinline__ uint32_t thread_merge_segments_lanes(int s, int L, PairTable P, int area)
+{
+  uint32_t* scr = lane_scratch() + area + (threadIdx.x & 31);
+  uint16_t* tok = g_tile.tok + max(s, 0);
+  uint32_t alive = 0;
+  if (s >= 0) alive = (L >= 32) ? 0xFFFFFFFFu : ((1u << L) - 1u);
+#pragma unroll
+  for (int k = 0; k < WW; ++k) {
+    uint32_t lo = NONE, hi = NONE;
+    if (s >= 0 && 2 * k < L) lo = g_tile.rk[s + 2 * k];
+    if (s >= 0 && 2 * k + 1 < L) hi = g_tile.rk[s + 2 * k + 1];
+    scr[k * 32] = lo | (hi << 16);
+  }
+  auto scan = [&]() {
+    uint32_t b = 0xFFFFFFFFu;
+#pragma unroll
+    for (int k = 0; k < WW; ++k) {
+      const uint32_t x = scr[k * 32];
+      b = min(b, min((x << 16) | uint32_t(2 * k), (x & 0xFFFF0000u) | uint32_t(2 * k + 1)));
+    }
+    return b;
+  };
+  auto set_rank = [&](int i, uint32_t v) { reinterpret_cast<uint16_t*>(scr + (i >> 1) * 32)[i & 1] = uint16_t(v); };
+  uint32_t best = scan();
+  while (__any_sync(0xFFFFFFFFu, best < (SEL << 16))) {
+    if (best < (SEL << 16)) {
+      const uint32_t r = best >> 16;
+      const int j      = int(best & 0xFFFFu);
+      const int q      = j + __ffs(int(alive >> (j + 1)));
+      const uint32_t c = P.merged_of_rank ? __ldg(P.merged_of_rank + r) : 256u + r;
+      alive &= ~(1u << q);
+      const uint32_t right = (q >= 31) ? 0u : (alive >> (q + 1));
+      const uint32_t left  = alive & ((1u << j) - 1u);
+      const int p          = left ? 31 - __clz(int(left)) : j;
+      uint32_t keyR = 0xFFFFFFFFu, keyL = 0xFFFFFFFFu;
+      uint4 vR = make_uint4(0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu), vL = vR;
+      if (right) {
+        keyR = (c << 16) | uint32_t(tok[q + __ffs(int(right))]);
+        vR   = __ldg(P.buckets + ((keyR * 0x9E3779B1u) >> 16));
+      }
+      if (left) {
+        keyL = (uint32_t(tok[p]) << 16) | c;
+        vL   = __ldg(P.buckets + ((keyL * 0x9E3779B1u) >> 16));
+      }
+      tok[j] = uint16_t(c);
+      tok[q] = uint16_t(DEAD);
+      set_rank(q, NONE);
+      set_rank(j, NONE);
+      set_rank(p, NONE);
+      best = scan();  // every pair but the two new ones
+      const uint32_t rr = resolve_rank(vR, keyR, P.overflow, P.overflow_mask);
+      const uint32_t rl = resolve_rank(vL, keyL, P.overflow, P.overflow_mask);
+      if (rr < SEL) {
+        set_rank(j, rr);
+        best = min(best, (rr << 16) | uint32_t(j));
+      }
+      if (rl < SEL) {
+        set_rank(p, rl);
+        best = min(best, (rl << 16) | uint32_t(p));
+      }
+    }
+  }
   return alive;
 }
 
@@ -1133,7 +1217,18 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
         s = S.seg[tid];
         L = next_cut(S.cut, s) - s;
       }
-      const uint32_t alive = thread_merge_segments(s, L, pair_table(T));
+      // ranks go to the lane-interleaved scratch when the warp's longest segment fits its area and nobody
+      // needs the staged bytes any more (the memo reads them after the merge; split mode before its stores)
+      const int wmax  = __reduce_max_sync(0xFFFFFFFFu, L);
+      const int words = (wmax + 1) >> 1;
+      const int area  = warp * 32 * kLaneWords;
+      const int room  = min(kLaneWords, (kLaneScratchWords - area) / 32);
+      uint32_t alive;
+      if (SPLIT || b.memo || words > room) alive = thread_merge_segments(s, L, pair_table(T));
+      else if (words <= 2) alive = thread_merge_segments_lanes<2>(s, L, pair_table(T), area);
+      else if (words <= 4) alive = thread_merge_segments_lanes<4>(s, L, pair_table(T), area);
+      else if (words <= 6) alive = thread_merge_segments_lanes<6>(s, L, pair_table(T), area);
+      else alive = thread_merge_segments_lanes<8>(s, L, pair_table(T), area);
       if (!SPLIT && s >= 0) mark_alive(S.cut, s, alive);
       if (!SPLIT && b.memo && s >= 0) {
         uint32_t k[8];
