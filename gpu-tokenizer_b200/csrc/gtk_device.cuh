@@ -24,7 +24,7 @@ constexpr int kThreadSegMax = 32;      // longest segment a single thread merges
 
 // Pointers into HBM, passed by value to every kernel.
 struct DeviceTable {
-  const uint4* pair_buckets;       // PairBucket[65536]: four words rank << 16 | low16(key * kPairMul), empty = all ones
+  const uint4* pair_buckets;       // PairBucket[65536]: four words low16(key * kPairMul) << 16 | rank, empty = all ones
   const uint2* pair_overflow;      // {key, rank} open addressing, or nullptr when no bucket overflowed
   uint32_t pair_overflow_mask;     // capacity - 1
   const uint16_t* byte_pair_rank;  // [65536]

@@ -65,24 +65,28 @@ __device__ __noinline__ uint32_t probe_overflow(const uint2* overflow, uint32_t 
   return NONE;
 }
 
-// rank of the key whose hash is h in its home bucket v, NONE if it is not there (an empty word can only
-// "match" with rank NONE, which is the right answer for a bucket that is not full)
+// Rank of the key whose hash is h in its home bucket v.  An entry is low16(h) << 16 | rank, so XOR with
+// low16(h) << 16 leaves the bare rank (< 65536) for the key's own entry and something larger for every other
+// entry: the minimum over the four words is the rank, or a value >= 65536 when the key is not there (an empty
+// word can only "match" with rank 0xFFFF, which is the right answer for a bucket that is not full).
 __device__ __forceinline__ uint32_t bucket_rank(const uint4& v, uint32_t h)
 {
-  const uint32_t f = h & 0xFFFFu;
-  uint32_t r       = NONE;
-  if ((v.x & 0xFFFFu) == f) r = v.x >> 16;
-  if ((v.y & 0xFFFFu) == f) r = v.y >> 16;
-  if ((v.z & 0xFFFFu) == f) r = v.z >> 16;
-  if ((v.w & 0xFFFFu) == f) r = v.w >> 16;
+  const uint32_t f = h << 16;
+  return min(min(v.x ^ f, v.y ^ f), min(v.z ^ f, v.w ^ f));
+}
+
+// any value >= SEL means "no such merge"
+__device__ __forceinline__ uint32_t resolve_rank_raw(const uint4& v, uint32_t key, const uint2* overflow,
+                                                     uint32_t mask)
+{
+  uint32_t r = bucket_rank(v, key * 0x9E3779B1u);
+  if (r >= SEL && overflow != nullptr && v.w != 0xFFFFFFFFu) r = probe_overflow(overflow, mask, key);
   return r;
 }
 
 __device__ __forceinline__ uint32_t resolve_rank(const uint4& v, uint32_t key, const uint2* overflow, uint32_t mask)
 {
-  uint32_t r = bucket_rank(v, key * 0x9E3779B1u);
-  if (r >= SEL && overflow != nullptr && (v.w >> 16) != NONE) r = probe_overflow(overflow, mask, key);
-  return r;
+  return min(resolve_rank_raw(v, key, overflow, mask), NONE);
 }
 
 __device__ __forceinline__ uint32_t probe_rank(const DeviceTable& T, uint32_t left, uint32_t right)
@@ -295,8 +299,8 @@ __device__ __forceinline__ bool thread_merge_step(uint16_t* tok_all, uint16_t* r
   rk[j]  = uint16_t(NONE);
   rk[p]  = uint16_t(NONE);
   best   = segment_argmin(rk_all, s, L);  // every pair but the two new ones
-  const uint32_t rr = resolve_rank(vR, keyR, P.overflow, P.overflow_mask);
-  const uint32_t rl = resolve_rank(vL, keyL, P.overflow, P.overflow_mask);
+  const uint32_t rr = resolve_rank_raw(vR, keyR, P.overflow, P.overflow_mask);
+  const uint32_t rl = resolve_rank_raw(vL, keyL, P.overflow, P.overflow_mask);
   if (rr < SEL) {
     rk[j] = uint16_t(rr);
     best  = min(best, (rr << 16) | uint32_t(j));
@@ -841,8 +845,8 @@ __device__ __noinline__ uint32_t thread_merge_segments_lanes(int s, int L, PairT
       set_rank(j, NONE);
       set_rank(p, NONE);
       best = scan();  // every pair but the two new ones
-      const uint32_t rr = resolve_rank(vR, keyR, P.overflow, P.overflow_mask);
-      const uint32_t rl = resolve_rank(vL, keyL, P.overflow, P.overflow_mask);
+      const uint32_t rr = resolve_rank_raw(vR, keyR, P.overflow, P.overflow_mask);
+      const uint32_t rl = resolve_rank_raw(vL, keyL, P.overflow, P.overflow_mask);
       if (rr < SEL) {
         set_rank(j, rr);
         best = min(best, (rr << 16) | uint32_t(j));

@@ -224,7 +224,7 @@ void HostTable::build_pair_buckets()
     PairBucket& b      = pair_buckets[h >> 16];
     int i = 0;
     while (i < 4 && b.w[i] != 0xFFFFFFFFu) ++i;
-    if (i < 4) b.w[i] = (r.rank << 16) | (h & 0xFFFFu);
+    if (i < 4) b.w[i] = (h << 16) | r.rank;
     else spilled.push_back(PairSlot{key, r.rank});
   }
   pair_overflow_count = uint32_t(spilled.size());
@@ -249,10 +249,9 @@ void HostTable::verify_device_tables() const
     const uint32_t key = (uint32_t(r.left) << 16) | uint32_t(r.right);
     const uint32_t h   = key * kPairMul;
     const PairBucket& b = pair_buckets[h >> 16];
-    uint32_t got = 0xFFFFu;
-    for (int i = 0; i < 4; ++i)
-      if ((b.w[i] & 0xFFFFu) == (h & 0xFFFFu)) got = b.w[i] >> 16;
-    if (got >= kSelRank16 && (b.w[3] >> 16) != 0xFFFFu && !pair_overflow.empty()) {
+    uint32_t got = 0xFFFFFFFFu;
+    for (int i = 0; i < 4; ++i) got = std::min(got, b.w[i] ^ (h << 16));
+    if (got >= kSelRank16 && b.w[3] != 0xFFFFFFFFu && !pair_overflow.empty()) {
       const size_t mask = pair_overflow.size() - 1;
       size_t at = ((key * 0x85EBCA77u) >> 7) & mask;
       for (size_t d = 0; d <= mask && pair_overflow[at].key != 0xFFFFFFFFu; ++d, at = (at + 1) & mask)

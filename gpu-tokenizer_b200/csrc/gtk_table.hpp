@@ -29,7 +29,7 @@ struct alignas(16) HashSlot {
 
 // Device form of the pair table when ids and ranks fit 16 bits.  key = left << 16 | right; h = key * kPairMul is a
 // bijection on 32 bits, so inside bucket (h >> 16) the low 16 bits of h identify the key exactly.  A bucket is
-// four 32-bit words (rank << 16 | low16(h)), filled front to back, 0xFFFFFFFF = empty: one 128-bit load answers
+// four 32-bit words (low16(h) << 16 | rank), filled front to back, 0xFFFFFFFF = empty: one 128-bit load answers
 // a probe, found or not.  Keys whose bucket already holds four entries go to a small open-addressing overflow
 // table of {key, rank} (empty = all ones), looked at only when the home bucket is full and has no match.
 constexpr uint32_t kPairMul = 0x9E3779B1u;
