@@ -795,12 +795,10 @@ __device__ __noinline__ uint32_t thread_merge_segments(int s, int L, PairTable P
 // 2 * WW ranks per lane, uniform over the warp): the rank scan is unrolled, needs no alignment handling and is
 // free of bank conflicts; the tokens stay in place.
 template <int WW>
-__device__ __noinline__ uint32_t thread_merge_segments_lanes(int s, int L, PairTable P, int area)
+__device__ __noinline__ uint32_t thread_merge_segments_lanes(int s, int L, PairTable P, int area, uint32_t alive)
 {
   uint32_t* scr = lane_scratch() + area + (threadIdx.x & 31);
   uint16_t* tok = g_tile.tok + max(s, 0);
-  uint32_t alive = 0;
-  if (s >= 0) alive = (L >= 32) ? 0xFFFFFFFFu : ((1u << L) - 1u);
 #pragma unroll
   for (int k = 0; k < WW; ++k) {
     uint32_t lo = NONE, hi = NONE;
@@ -1221,18 +1219,18 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
         s = S.seg[tid];
         L = next_cut(S.cut, s) - s;
       }
-      // ranks go to the lane-interleaved scratch when the warp's longest segment fits its area and nobody
-      // needs the staged bytes any more (the memo reads them after the merge; split mode before its stores)
+      // The ranks go to the lane-interleaved scratch when the warp's longest segment fits its area and nobody
+      // needs the staged bytes any more (the memo reads them after the merge, split mode before its stores).
+      // Two sizes only: every further copy of the loop costs instruction-cache hits on text with many long runs.
       const int wmax  = __reduce_max_sync(0xFFFFFFFFu, L);
       const int words = (wmax + 1) >> 1;
       const int area  = warp * 32 * kLaneWords;
       const int room  = min(kLaneWords, (kLaneScratchWords - area) / 32);
+      const uint32_t all = (s < 0) ? 0u : ((L >= 32) ? 0xFFFFFFFFu : ((1u << L) - 1u));
       uint32_t alive;
       if (SPLIT || b.memo || words > room) alive = thread_merge_segments(s, L, pair_table(T));
-      else if (words <= 2) alive = thread_merge_segments_lanes<2>(s, L, pair_table(T), area);
-      else if (words <= 4) alive = thread_merge_segments_lanes<4>(s, L, pair_table(T), area);
-      else if (words <= 6) alive = thread_merge_segments_lanes<6>(s, L, pair_table(T), area);
-      else alive = thread_merge_segments_lanes<8>(s, L, pair_table(T), area);
+      else if (words <= 4) alive = thread_merge_segments_lanes<4>(s, L, pair_table(T), area, all);
+      else alive = thread_merge_segments_lanes<8>(s, L, pair_table(T), area, all);
       if (!SPLIT && s >= 0) mark_alive(S.cut, s, alive);
       if (!SPLIT && b.memo && s >= 0) {
         uint32_t k[8];
