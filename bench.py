@@ -45,9 +45,9 @@ for _p in (ROOT, PKG):
 BLOCK = 65536  # generator block size
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per input byte of one k_merge_opt launch, from the
-# ncu capture summarised in profiles/k_merge_opt_cfg2_128MiB.md (202.6 MB for 128 MiB of config-2 text);
+# ncu capture summarised in profiles/k_merge_opt_cfg2_128MiB.md (202.3 MB for 128 MiB of config-2 text);
 # traffic grows in proportion to the tile count, so a launch over n bytes moves this x n.
-MERGE_OPT_DRAM_BYTES_PER_INPUT_BYTE = 202.6e6 / (128 << 20)
+MERGE_OPT_DRAM_BYTES_PER_INPUT_BYTE = 202.3e6 / (128 << 20)
 
 WORKLOADS = {
     #        seed  bytes per GPU   chunk   mix  lognormal
