@@ -4,9 +4,12 @@
 //                offsets (replaces the host chunk/flatten loops of the
 //                reference, gputok_binding.cu:718-752)
 //   merge (opt)  persistent CTAs walk the byte stream in tiles; a tile is cut
-//                into never-merge segments, short segments are merged by one
-//                thread each, long ones by a warp, oversize ones by the CTA
-//                in an HBM workspace (replaces bpe_merge_kernel_optimized's
+//                into never-merge segments; a segment that is a vocabulary
+//                string of its own is answered by a table lookup, the other
+//                short segments are merged by one thread each, long ones by a
+//                warp, oversize ones by the CTA in an HBM workspace; the
+//                segment-start bitmap ends up as the bitmap of live tokens
+//                that drives compaction (replaces bpe_merge_kernel_optimized's
 //                role as the fast entry point, gputok_binding.cu:704-846, with
 //                the greedy rule of gputok_blockbpe.cu:248-300)
 //   merge (base) one CTA per chunk runs Algorithm 1 pass by pass on the whole

@@ -3,8 +3,10 @@
 //
 // Behaviour follows the reference's ByteEncoder / BPEVocab /
 // build_vocab_and_merges (gputok_blockbpe.cu:64-236); the data layout is new:
-// an open-addressing hash table with 16-byte slots, a dense 256x256 rank table
-// for byte pairs, per-rank merged ids and a never-merge bigram bitmap.
+// an open-addressing table with 16-byte slots for host lookups, and for the
+// kernels a bucketed pair table answered by one 128-bit load, a dense 256x256
+// table for byte pairs, per-rank merged ids, a never-merge bigram bitmap and a
+// two-choice cuckoo table of vocabulary strings that are their own tokenisation.
 #pragma once
 #include <cstdint>
 #include <string>
