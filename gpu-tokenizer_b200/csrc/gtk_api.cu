@@ -144,8 +144,6 @@ struct gtk_tokenizer {
   gtk::DeviceTable dtab{};
 
   // arenas
-  DevBuf d_memo;  // call-local memo of segment results, cleared by every call
-  DevBuf d_q_short, d_q_long, d_q_huge;  // split pipeline queues (shared by all slices: kernels of one stream)
   DevBuf d_bytes, d_text_off, d_text_chunk_base, d_chunk_off, d_tile_chunk0, d_staging, d_unit_first, d_unit_cnt,
       d_chunk_cnt, d_unit_base, d_chunk_id_off, d_text_id_off, d_out_ids, d_seg_scratch, d_scan_sums, d_counters,
       d_totals;
@@ -159,8 +157,6 @@ struct gtk_tokenizer {
   uint8_t* small_out_h = nullptr;  // [totals | text id offsets | chunk id offsets | ids]
   uint8_t* small_out_d = nullptr;
   bool result_is_small = false;
-  int tune_pipeline = GTK_PIPELINE_AUTO;  // AUTO currently means FUSED: fastest measured on B200
-  int tune_memo = 0;
   // sliced host path: copy streams and two slice arenas
   cudaStream_t in_stream = nullptr, out_stream = nullptr, pack_stream = nullptr;
   SliceArena slice[kSliceArenas];
@@ -223,36 +219,6 @@ void upload_table(gtk_tokenizer* h)
 int64_t chunk_upper_bound(int64_t n_bytes, int64_t n_texts, int chunk_tokens)
 {
   return n_bytes / chunk_tokens + n_texts + 1;
-}
-
-// Batches of at least this many tiles take the split pipeline (queues + separate merge kernels);
-// smaller ones run the single tile kernel, whose per-tile barriers do not matter at that size.
-constexpr int64_t kSplitMinTiles = 1024;
-constexpr uint32_t kMemoLog2 = 17;          // 131 072 slots x 64 bytes = 8 MiB
-constexpr int64_t kMemoMinTiles = 64;       // batches below 256 KiB skip the memo (clearing it would dominate)
-
-bool use_split(const gtk::EncodeBuffers& b, int mode) { return mode == GTK_MODE_OPT && b.q_short != nullptr; }
-
-void attach_queues(gtk_tokenizer* h, gtk::EncodeBuffers& b, int64_t reserve_bytes)
-{
-  if (h->tune_memo && b.n_tiles >= kMemoMinTiles) {
-    h->d_memo.reserve((size_t(1) << kMemoLog2) * 64);
-    b.memo = h->d_memo.as<uint4>();
-    b.memo_log2 = kMemoLog2;
-  }
-  if (h->tune_pipeline != GTK_PIPELINE_SPLIT || b.n_tiles < kSplitMinTiles) return;
-  const int64_t n = std::max(reserve_bytes, b.n_bytes);
-  const int64_t cap_short = std::min<int64_t>(n / 8 + 4096, (int64_t(1) << 31) - (int64_t(1) << 24));
-  const int64_t cap_long = n / 33 + 1024, cap_huge = n / (gtk::kLongSegMax + 1) + 16;
-  h->d_q_short.reserve(size_t(cap_short) * 48);
-  h->d_q_long.reserve(size_t(cap_long) * 8);
-  h->d_q_huge.reserve(size_t(cap_huge) * 16);
-  b.q_short = h->d_q_short.as<uint4>();
-  b.q_long = h->d_q_long.as<unsigned long long>();
-  b.q_huge = h->d_q_huge.as<unsigned long long>();
-  b.q_short_cap = cap_short;
-  b.q_long_cap = cap_long;
-  b.q_huge_cap = cap_huge;
 }
 
 struct Plan {
@@ -319,7 +285,6 @@ Plan plan_batch(gtk_tokenizer* h, const uint8_t* d_bytes, int64_t n_bytes, const
   b.counters = h->d_counters.as<int32_t>();
   b.totals = h->d_totals.as<int64_t>();
   b.low_id_map = (h->id_space == GTK_IDS_GPT2) ? h->d_low_map.as<uint16_t>() : nullptr;
-  attach_queues(h, b, 0);
   return p;
 }
 
@@ -342,13 +307,11 @@ void run_front(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* lau
   if (!ev) ev = h->ev;
   GTK_CUDA(cudaMemsetAsync(b.counters, 0, 64, s));
   GTK_CUDA(cudaMemsetAsync(b.chunk_cnt, 0, size_t(b.chunk_cap + 1) * 4, s));
-  if (b.memo && mode == GTK_MODE_OPT) GTK_CUDA(cudaMemsetAsync(b.memo, 0, (size_t(1) << b.memo_log2) * 64, s));
   GTK_CUDA(cudaEventRecord(ev[0], s));
   *launches += gtk::launch_chunker(b, s);
   GTK_CUDA(cudaEventRecord(ev[1], s));
   if (mode == GTK_MODE_BASE) *launches += gtk::launch_merge_base(b, h->dtab, h->base_grid, s);
   else if (mode == GTK_MODE_LOCALMIN) *launches += gtk::launch_merge_localmin(b, h->dtab, h->base_grid, h->max_iters, s);
-  else if (use_split(b, mode)) *launches += gtk::launch_merge_split(b, h->dtab, h->sm_count, h->opt_grid, s);
   else *launches += gtk::launch_merge_opt(b, h->dtab, h->opt_grid, s);
   GTK_CUDA(cudaEventRecord(ev[2], s));
   *launches += gtk::launch_output_scans(b, mode != GTK_MODE_OPT, s);
@@ -369,8 +332,7 @@ void run_pack(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* laun
   cudaStream_t s = on ? on : h->stream;
   if (!ev) ev = h->ev;
   GTK_CUDA(cudaEventRecord(ev[5], s));
-  if (use_split(b, mode)) *launches += gtk::launch_pack_split(b, h->sm_count * 8, s);
-  else *launches += gtk::launch_pack(b, mode != GTK_MODE_OPT, h->sm_count * 8, s);
+  *launches += gtk::launch_pack(b, mode != GTK_MODE_OPT, h->sm_count * 8, s);
   GTK_CUDA(cudaEventRecord(ev[4], s));
   GTK_CUDA(cudaGetLastError());
 }
@@ -500,7 +462,6 @@ gtk::EncodeBuffers slice_buffers(gtk_tokenizer* h, SliceArena& a, const SlicePla
   b.counters = a.counters.as<int32_t>();
   b.totals = a.totals.as<int64_t>();
   b.low_id_map = (h->id_space == GTK_IDS_GPT2) ? h->d_low_map.as<uint16_t>() : nullptr;
-  attach_queues(h, b, max_bytes);
   return b;
 }
 
@@ -827,7 +788,7 @@ GTK_API void gtk_destroy(gtk_tokenizer* h)
   if (h->device >= 0) {
     cudaSetDevice(h->device);
     if (h->stream) cudaStreamSynchronize(h->stream);
-    for (DevBuf* b : {&h->d_bpi, &h->d_slots, &h->d_overflow, &h->d_bpr, &h->d_mor, &h->d_sor, &h->d_adj, &h->d_b2i, &h->d_words, &h->d_low_map, &h->d_memo, &h->d_q_short, &h->d_q_long, &h->d_q_huge, &h->d_bytes, &h->d_text_off,
+    for (DevBuf* b : {&h->d_bpi, &h->d_slots, &h->d_overflow, &h->d_bpr, &h->d_mor, &h->d_sor, &h->d_adj, &h->d_b2i, &h->d_words, &h->d_low_map, &h->d_bytes, &h->d_text_off,
                       &h->d_text_chunk_base, &h->d_chunk_off, &h->d_tile_chunk0, &h->d_staging, &h->d_unit_first,
                       &h->d_unit_cnt, &h->d_chunk_cnt, &h->d_unit_base, &h->d_chunk_id_off, &h->d_text_id_off,
                       &h->d_out_ids, &h->d_seg_scratch, &h->d_scan_sums, &h->d_counters, &h->d_totals})
@@ -900,7 +861,7 @@ GTK_API int gtk_encode_device(gtk_tokenizer* h, int mode, const uint8_t* d_bytes
     // When the chunk offsets are scanned straight into the caller's buffer (or not wanted), the pack follows
     // the front without a host round trip: the pack kernel itself never writes past out_capacity, and the
     // totals are checked once at the end.
-    const bool one_sync = (!d_out_chunk_offsets || chunk_dst) && !use_split(p.b, mode);
+    const bool one_sync = !d_out_chunk_offsets || chunk_dst;
     if (one_sync) run_pack(h, p.b, mode, &launches);
     GTK_CUDA(cudaStreamSynchronize(h->stream));
     const int64_t* ht = h->h_totals.as<int64_t>();
@@ -1159,16 +1120,6 @@ GTK_API int gtk_write_token_strings(const gtk_tokenizer* h, const char* path, co
     std::fwrite(line.data(), 1, line.size(), f);
   }
   std::fclose(f);
-  return GTK_OK;
-}
-
-GTK_API int gtk_set_tuning(gtk_tokenizer* h, int pipeline, int memo)
-{
-  if (!h) return GTK_ERR_INVALID_ARG;
-  std::lock_guard<std::mutex> lock(h->mu);
-  if (pipeline < GTK_PIPELINE_AUTO || pipeline > GTK_PIPELINE_SPLIT) return h->fail(GTK_ERR_INVALID_ARG, "unknown pipeline");
-  h->tune_pipeline = pipeline;
-  h->tune_memo = memo ? 1 : 0;
   return GTK_OK;
 }
 

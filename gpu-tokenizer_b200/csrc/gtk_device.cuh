@@ -19,7 +19,6 @@ constexpr int kWindow = kTile + kHalo;
 constexpr int kOptThreads = 256;
 constexpr int kBaseThreads = 512;
 constexpr int kBaseSmemTokens = 8192;  // chunks up to this length stay in shared memory in the base kernel
-constexpr int kLongSegMax = 2048;     // longest segment one warp merges in shared memory (split mode)
 constexpr int kThreadSegMax = 32;      // longest segment a single thread merges on its own
 
 // Pointers into HBM, passed by value to every kernel.
@@ -77,27 +76,13 @@ struct EncodeBuffers {
   uint16_t* seg_scratch;     // per-CTA workspace for segments that do not fit in shared memory
   int64_t seg_scratch_tokens;  // tokens per CTA (two arrays of this length per CTA)
   int64_t* scan_block_sums;  // workspace of the multi-block scan
-  int32_t* counters;         // [0] tile ticket, [1] status word, [2] base-mode chunk ticket,
-                             // split mode: [4] short-queue entries, [5] long, [6] huge, [8..10] consumer tickets
-  // split mode (large batches): segments that need real merging leave the tile kernel through queues
-  uint4* q_short;               // 48-byte entries: (byte position | length << 48) + the segment's first 32 bytes
-  unsigned long long* q_long;   // length 33..kLongSegMax
-  unsigned long long* q_huge;   // longer
-  int64_t q_short_cap, q_long_cap, q_huge_cap;
-  // call-local memo of finished short segments: 64-byte slots {key 32 B ; state|len|count, 12 x u16 ids},
-  // direct mapped, written once (empty -> busy -> ready) and cleared at the start of every call
-  uint4* memo;
-  uint32_t memo_log2;
+  int32_t* counters;         // [0] tile ticket, [1] status word, [2] base-mode chunk ticket
   int64_t* totals;           // device: [0] n_chunks, [1] n_ids
 };
 
 // Launchers (all asynchronous on `stream`; return the number of kernels launched).
 int launch_chunker(const EncodeBuffers& b, cudaStream_t stream);
 int launch_merge_opt(const EncodeBuffers& b, const DeviceTable& t, int grid, cudaStream_t stream);
-// Split pipeline for large batches: tile kernel (lookup + queues) -> short / long / huge segment kernels ->
-// positional count.  Ends with unit_cnt / chunk_cnt filled, like launch_merge_opt.
-int launch_merge_split(const EncodeBuffers& b, const DeviceTable& t, int sm_count, int grid_front, cudaStream_t stream);
-int launch_pack_split(const EncodeBuffers& b, int grid, cudaStream_t stream);
 int launch_merge_base(const EncodeBuffers& b, const DeviceTable& t, int grid, cudaStream_t stream);
 int launch_merge_localmin(const EncodeBuffers& b, const DeviceTable& t, int grid, int max_iters, cudaStream_t stream);
 int launch_output_scans(const EncodeBuffers& b, int mode_base, cudaStream_t stream);

@@ -116,31 +116,6 @@ __device__ __forceinline__ uint32_t word_lookup(const uint4* word_slots, uint32_
   return 0xFFFFFFFFu;
 }
 
-// ------------------------------------------------------------------------------------------------
-// Call-local memo: a short segment (<= 32 bytes, <= 12 resulting ids) that has been merged once is
-// stored under its bytes, so a later occurrence of the same bytes in the same call copies the ids
-// instead of repeating the merge chain.  The ids stored are the output of the merge loop on exactly
-// these bytes, so a hit cannot change any result.  A slot is 64 bytes = two 32-byte sectors:
-// sector 0 holds the key (bytes, zero padded), sector 1 the state word and the ids.  Slots are
-// written once -- empty -> busy (CAS) -> key and ids -> fence -> ready -- and never replaced (a
-// collision is a miss); the table is cleared at the start of every call.  Readers bypass L1.  A
-// reader that sees `ready` has the ids of that entry (same sector); if its copy of the key sector
-// is older than the entry it can only be the cleared, all-zero state, which either fails the
-// comparison (a miss) or is the true key of an all-zero segment.
-// ------------------------------------------------------------------------------------------------
-constexpr uint32_t kMemoReady = 0xA5000000u, kMemoBusy = 0x5A000000u, kMemoStateMask = 0xFF000000u;
-constexpr int kMemoMaxIds = 12;
-
-__device__ __forceinline__ uint32_t memo_slot(const uint32_t k[8], uint32_t L, uint32_t log2)
-{
-  uint32_t h = (k[0] * 0x85EBCA77u) ^ (k[1] * 0xC2B2AE3Du) ^ (k[2] * 0x27D4EB2Fu) ^ (k[3] * 0x165667B1u);
-  h ^= (k[4] * 0x9E3779B1u) ^ (k[5] * 0xD3A2646Du) ^ (k[6] * 0xFD7046C5u) ^ (k[7] * 0xB55A4F09u);
-  h ^= L * 0x68E31DA4u;
-  h ^= h >> 16;
-  h *= 0x9E3779B1u;
-  return h >> (32 - log2);
-}
-
 // segment bytes at shared-memory offset `at` (any alignment), zero padded to three words
 __device__ __forceinline__ void segment_key(const uint8_t* bytes, int at, int LL, uint32_t& k0, uint32_t& k1,
                                             uint32_t& k2)
@@ -154,75 +129,6 @@ __device__ __forceinline__ void segment_key(const uint8_t* bytes, int at, int LL
   k0 &= (LL >= 4) ? 0xFFFFFFFFu : ((1u << (8 * LL)) - 1u);
   k1 &= (LL >= 8) ? 0xFFFFFFFFu : ((LL <= 4) ? 0u : ((1u << (8 * (LL - 4))) - 1u));
   k2 &= (LL >= 12) ? 0xFFFFFFFFu : ((LL <= 8) ? 0u : ((1u << (8 * (LL - 8))) - 1u));
-}
-
-// the same for up to 32 bytes, eight words
-__device__ __forceinline__ void segment_key8(const uint8_t* bytes, int at, int LL, uint32_t k[8])
-{
-  const uint32_t* wp = reinterpret_cast<const uint32_t*>(bytes + (at & ~3));
-  const uint32_t sh  = uint32_t(at & 3) * 8u;
-  uint32_t prev = wp[0];
-#pragma unroll
-  for (int q = 0; q < 8; ++q) {
-    uint32_t v = 0;
-    if (4 * q < LL) {
-      const uint32_t next = wp[q + 1];
-      v    = __funnelshift_r(prev, next, sh);
-      prev = next;
-      const int rem = LL - 4 * q;
-      if (rem < 4) v &= (1u << (8 * rem)) - 1u;
-    }
-    k[q] = v;
-  }
-}
-
-// returns the number of ids (written to tok[0..n), tombstones behind them), 0 on a miss
-__device__ __forceinline__ int memo_lookup(const uint4* memo, uint32_t log2, const uint32_t k[8], int LL,
-                                           uint16_t* tok)
-{
-  const uint4* slot = memo + 4 * size_t(memo_slot(k, uint32_t(LL), log2));
-  const uint4 m0    = __ldcg(slot + 2);
-  if ((m0.x & kMemoStateMask) != kMemoReady || ((m0.x >> 16) & 0xFFu) != uint32_t(LL)) return 0;
-  const uint4 m1 = __ldcg(slot + 3);
-  const uint4 a  = __ldcg(slot);
-  const uint4 c  = __ldcg(slot + 1);
-  if (a.x != k[0] || a.y != k[1] || a.z != k[2] || a.w != k[3] || c.x != k[4] || c.y != k[5] || c.z != k[6] ||
-      c.w != k[7])
-    return 0;
-  const int n = int(m0.x & 0xFFu);
-  const uint32_t w[6] = {m0.y, m0.z, m0.w, m1.x, m1.y, m1.z};
-#pragma unroll
-  for (int i = 0; i < kMemoMaxIds; ++i)
-    if (i < n) tok[i] = uint16_t(w[i >> 1] >> ((i & 1) * 16));
-  for (int i = n; i < LL; ++i) tok[i] = uint16_t(DEAD);
-  return n;
-}
-
-// store the finished segment tok[0..LL) (tombstones skipped) under its bytes
-__device__ __forceinline__ void memo_insert(uint4* memo, uint32_t log2, const uint32_t k[8], int LL,
-                                            const uint16_t* tok)
-{
-  uint32_t w[6] = {0, 0, 0, 0, 0, 0};
-  int n = 0;
-  for (int i = 0; i < LL; ++i) {
-    const uint32_t t = tok[i];
-    if (t == DEAD) continue;
-    if (n < kMemoMaxIds) w[n >> 1] |= t << ((n & 1) * 16);
-    ++n;
-  }
-  if (n > kMemoMaxIds) return;
-  uint4* slot    = memo + 4 * size_t(memo_slot(k, uint32_t(LL), log2));
-  uint32_t* meta = reinterpret_cast<uint32_t*>(slot + 2);
-  if (atomicCAS(meta, 0u, kMemoBusy) != 0u) return;  // taken (or being written): never replaced
-  slot[0] = make_uint4(k[0], k[1], k[2], k[3]);
-  slot[1] = make_uint4(k[4], k[5], k[6], k[7]);
-  uint32_t* p = reinterpret_cast<uint32_t*>(slot + 2);
-  p[1] = w[0];
-  p[2] = w[1];
-  p[3] = w[2];
-  slot[3] = make_uint4(w[3], w[4], w[5], 0u);
-  __threadfence();
-  atomicExch(meta, kMemoReady | (uint32_t(LL) << 16) | uint32_t(n));
 }
 
 __device__ __forceinline__ uint32_t merged_id(const DeviceTable& T, uint32_t rank)
@@ -726,7 +632,7 @@ struct OptSmem {
   GroupScratch gs;
   int scanbuf[33];
   int ticket;
-  int nseg, nlong, seg_next, nmiss, qbase, nbig, qfill;
+  int nseg, nlong, seg_next, nmiss;
   int first_start, last_start, over_start;
   int over_len;
   long long over_end;
@@ -872,7 +778,6 @@ __device__ __forceinline__ int next_cut(const uint32_t* cut, int s)
 
 // Step D/E1 of a tile, out of line so that it gets registers of its own: every thread walks the multi-byte
 // segments that start in its 16 positions (window positions [16*tid, 16*tid+16), owned ones only).
-template <bool SPLIT>
 __device__ __noinline__ void walk_segments(const uint4* word_slots, uint32_t word_shift, int own, int wlen,
                                            int* status)
 {
@@ -912,8 +817,6 @@ __device__ __noinline__ void walk_segments(const uint4* word_slots, uint32_t wor
           if (id != 0xFFFFFFFFu) {
             miss      = false;
             S.tok[ss] = uint16_t(id);
-            if (SPLIT)  // the split pipeline stores tokens by position, tombstones included
-              for (int i = 1; i < LL; ++i) S.tok[ss + i] = uint16_t(DEAD);
           }
         }
       }
@@ -967,8 +870,6 @@ __device__ __forceinline__ void opt_tile_reset(OptSmem& S)
   S.nseg        = 0;
   S.seg_next    = 0;
   S.nmiss       = 0;
-  S.nbig        = 0;
-  S.qfill       = 0;
   S.first_start = kWindow;
   S.last_start  = -1;
   S.over_start  = -1;
@@ -978,7 +879,6 @@ __device__ __forceinline__ void opt_tile_reset(OptSmem& S)
 
 // One tile of the byte stream: tokenises every segment that starts in bytes [k*kTile, (k+1)*kTile),
 // writes the tokens compacted to staging, the unit record and the per-chunk counts.
-template <bool SPLIT>
 __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, const DeviceTable& T, int64_t k,
                                          int64_t C)
 {
@@ -1099,42 +999,15 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
           atomicMax(&S.end_owned, next_cut(S.cut, last));
         }
       }
-      walk_segments<SPLIT>(T.word_slots, 32u - T.word_log2_capacity, own, wlen, status);
+      walk_segments(T.word_slots, 32u - T.word_log2_capacity, own, wlen, status);
     }
     __syncthreads();
     GTK_PHASE(3);
-    // ---- E1b. call-local memo, on the dense list of misses: a segment whose bytes were merged earlier
-    //           in this call copies the ids; what is left is compacted once more ----
-    int nmiss = S.nmiss;
-    if (!SPLIT && b.memo) {
-      for (int r0 = 0; r0 < nmiss; r0 += kOptThreads) {
-        const int j  = r0 + tid;
-        uint32_t ent = 0;
-        bool miss    = false;
-        if (j < nmiss) {
-          ent          = S.seg[j];
-          const int ss = int(ent);
-          const int LL = next_cut(S.cut, ss) - ss;
-          uint32_t k[8];
-          segment_key8(S.bytes, 16 + ss, LL, k);
-          const int got = memo_lookup(b.memo, b.memo_log2, k, LL, S.tok + ss);  // ids at the front of the segment
-          miss          = got <= 0;
-          if (got > 1) mark_alive(S.cut, ss, (got >= 32) ? 0xFFFFFFFFu : ((1u << got) - 1u));
-        }
-        const uint32_t bal = __ballot_sync(0xFFFFFFFFu, miss);
-        int wbase          = 0;
-        if (lane == 0 && bal) wbase = atomicAdd(&S.nbig, __popc(bal));
-        wbase = __shfl_sync(0xFFFFFFFFu, wbase, 0);
-        __syncthreads();
-        if (miss) S.seg[wbase + __popc(bal & lt)] = uint16_t(ent);
-      }
-      __syncthreads();
-      nmiss = S.nbig;
-    }
+    const int nmiss = S.nmiss;
 
     // ---- E1c. the misses, sorted by length (longest first) so that the lanes of a warp work on segments of
     //           similar length in step E2: thread j keeps entry j in registers while the list is rewritten ----
-    if (!SPLIT && nmiss > 32 && nmiss <= kOptThreads) {
+    if (nmiss > 32 && nmiss <= kOptThreads) {
       if (tid < 34) S.hist[tid] = 0;
       __syncthreads();
       int ss = 0, LL = 0, slot = 0;
@@ -1166,64 +1039,19 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
       atomicAdd(&g_phase_cycles[11], (unsigned long long)S.nseg);
     }
 #endif
-    // ---- E. short segments that missed the lookup.  Split mode: hand them to the batch-wide queue
-    //         (one reservation per tile).  Otherwise, or if the queue is full: every lane pulls
-    //         segments from a CTA-wide list and does one merge step per loop trip ----
-    // Split mode: segments of more than 12 bytes (long merge chains, not covered by the memo) leave
-    // through the batch-wide queue, one reservation per tile; the rest is merged here.
-    bool queued = false;
-    if (SPLIT) {
-      const int nm = S.nmiss;
-      int mybig    = 0;
-      // with the memo every miss leaves through the queue (the consumer owns the memo); without it only
-      // segments of more than 12 bytes do
-      const int keep_max = b.memo ? 1 : 12;
-      for (int j = tid; j < nm; j += kOptThreads) mybig += int(next_cut(S.cut, S.seg[j]) - int(S.seg[j]) > keep_max);
-      if (mybig) atomicAdd(&S.nbig, mybig);
-      __syncthreads();
-      const int nbig = S.nbig;
-      if (tid == 0) S.qbase = nbig ? atomicAdd(b.counters + 4, nbig) : 0;
-      __syncthreads();
-      const int64_t qb = S.qbase;
-      queued           = qb + nbig <= b.q_short_cap;
-      for (int j = tid; j < nm; j += kOptThreads) {
-        const int ss0 = S.seg[j];
-        const int LL0 = next_cut(S.cut, ss0) - ss0;
-        const uint32_t ent = uint32_t(ss0) | (uint32_t(LL0) << 16);
-        if (LL0 <= keep_max) continue;
-        const int64_t at = qb + atomicAdd(&S.qfill, 1);
-        if (at >= b.q_short_cap) continue;  // a reservation that does not fit is filled with null entries
-        uint4* e = b.q_short + 3 * at;
-        if (!queued) {
-          e[0] = make_uint4(0, 0, 0, 0);
-          continue;
-        }
-        const int ss = int(ent & 0xFFFFu);
-        const unsigned long long head = (unsigned long long)(lo + ss) | ((unsigned long long)(ent >> 16) << 48);
-        // the segment's bytes travel with the entry, so the consumer needs one contiguous read
-        const int at8      = 16 + ss;
-        const uint32_t* wp = reinterpret_cast<const uint32_t*>(&S.bytes[at8 & ~3]);
-        const uint32_t sh  = uint32_t(at8 & 3) * 8u;
-        uint32_t w[9];
-#pragma unroll
-        for (int q = 0; q < 9; ++q) w[q] = wp[q];
-        e[0] = make_uint4(uint32_t(head), uint32_t(head >> 32), __funnelshift_r(w[0], w[1], sh),
-                          __funnelshift_r(w[1], w[2], sh));
-        e[1] = make_uint4(__funnelshift_r(w[2], w[3], sh), __funnelshift_r(w[3], w[4], sh),
-                          __funnelshift_r(w[4], w[5], sh), __funnelshift_r(w[5], w[6], sh));
-        e[2] = make_uint4(__funnelshift_r(w[6], w[7], sh), __funnelshift_r(w[7], w[8], sh), 0u, 0u);
-      }
-    }
+    // ---- E2. short segments that missed the lookup: one thread per segment (the usual case), or, when a
+    //          tile has more misses than threads, every lane pulls segments from a CTA-wide list and does one
+    //          merge step per loop trip ----
     GTK_PHASE(12);
-    if (!queued && nmiss <= kOptThreads) {
+    if (nmiss <= kOptThreads) {
       // at most one segment per thread (the usual case): no queue, thread t takes entry t of the sorted list
       int s = -1, L = 0;
       if (tid < nmiss) {
         s = S.seg[tid];
         L = next_cut(S.cut, s) - s;
       }
-      // The ranks go to the lane-interleaved scratch when the warp's longest segment fits its area and nobody
-      // needs the staged bytes any more (the memo reads them after the merge, split mode before its stores).
+      // The ranks go to the lane-interleaved scratch when the warp's longest segment fits its area (nobody
+      // needs the staged bytes any more).
       // Two sizes only: every further copy of the loop costs instruction-cache hits on text with many long runs.
       const int wmax  = __reduce_max_sync(0xFFFFFFFFu, L);
       const int words = (wmax + 1) >> 1;
@@ -1231,15 +1059,10 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
       const int room  = min(kLaneWords, (kLaneScratchWords - area) / 32);
       const uint32_t all = (s < 0) ? 0u : ((L >= 32) ? 0xFFFFFFFFu : ((1u << L) - 1u));
       uint32_t alive;
-      if (SPLIT || b.memo || words > room) alive = thread_merge_segments(s, L, pair_table(T));
+      if (words > room) alive = thread_merge_segments(s, L, pair_table(T));
       else if (words <= 4) alive = thread_merge_segments_lanes<4>(s, L, pair_table(T), area, all);
       else alive = thread_merge_segments_lanes<8>(s, L, pair_table(T), area, all);
-      if (!SPLIT && s >= 0) mark_alive(S.cut, s, alive);
-      if (!SPLIT && b.memo && s >= 0) {
-        uint32_t k[8];
-        segment_key8(S.bytes, 16 + s, L, k);
-        memo_insert(b.memo, b.memo_log2, k, L, S.tok + s);
-      }
+      if (s >= 0) mark_alive(S.cut, s, alive);
     } else {
       const int nseg   = nmiss;
       int s            = -1, L = 0;
@@ -1261,12 +1084,10 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
             } else {
               const int ss0 = S.seg[j];
               const int LL0 = next_cut(S.cut, ss0) - ss0;
-              if (!(queued && LL0 > (b.memo ? 1 : 12))) {  // queued segments are merged by a later kernel
-                s     = ss0;
-                L     = LL0;
-                alive = (L >= 32) ? 0xFFFFFFFFu : ((1u << L) - 1u);
-                best  = segment_argmin(S.rk, s, L);
-              }
+              s     = ss0;
+              L     = LL0;
+              alive = (L >= 32) ? 0xFFFFFFFFu : ((1u << L) - 1u);
+              best  = segment_argmin(S.rk, s, L);
             }
           }
         }
@@ -1275,12 +1096,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
           continue;
         }
         if (s >= 0 && !thread_merge_step(S.tok, S.rk, s, L, alive, best, P)) {
-          if (!SPLIT) mark_alive(S.cut, s, alive);
-          if (!SPLIT && b.memo) {
-            uint32_t k[8];
-            segment_key8(S.bytes, 16 + s, L, k);
-            memo_insert(b.memo, b.memo_log2, k, L, S.tok + s);
-          }
+          mark_alive(S.cut, s, alive);
           s = -1;
         }
       }
@@ -1288,78 +1104,6 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
     __syncthreads();
 
     GTK_PHASE(13);
-    if (SPLIT) {
-      // ---- split mode: long segments go to their queues, the tile stores its tokens position by
-      //      position (tombstones included); counting and packing happen in later kernels ----
-      const int nl = min(S.nlong, kLongCap);
-      for (int q = tid; q < nl; q += kOptThreads) {
-        const int ss = S.longq[q];
-        const int LL = next_cut(S.cut, ss) - ss;
-        if (LL <= kLongSegMax) {
-          const int64_t at = atomicAdd(b.counters + 5, 1);
-          if (at < b.q_long_cap) b.q_long[at] = (unsigned long long)(lo + ss) | ((unsigned long long)LL << 48);
-          else atomicMax(status, int(kStatusLongQueueOverflow));
-        } else {
-          const int64_t at = atomicAdd(b.counters + 6, 1);
-          if (at < b.q_huge_cap) {
-            b.q_huge[2 * at]     = (unsigned long long)(lo + ss);
-            b.q_huge[2 * at + 1] = (unsigned long long)LL;
-          } else atomicMax(status, int(kStatusLongQueueOverflow));
-        }
-      }
-      if (S.over_start >= 0) {  // CTA-uniform: the segment that runs past the window
-        const int64_t gs0 = lo + S.over_start;
-        if (tid == 0) {
-          int64_t c = b.tile_chunk0[k];
-          while (c + 1 < C && b.chunk_off[c + 1] <= gs0) ++c;
-          S.over_end = b.chunk_off[c + 1];
-        }
-        __syncthreads();
-        const int64_t cend = S.over_end;
-        int64_t ge         = cend;
-        for (int64_t pos = lo + kWindow; pos < cend; pos += kOptThreads) {
-          const int64_t p = pos + tid;
-          const bool cutp = (p < cend) && !adj_bit(T.adj, b.bytes[p - 1], b.bytes[p]);
-          if (__syncthreads_or(cutp)) {
-            if (cutp) atomicMin(reinterpret_cast<unsigned long long*>(&S.over_end), (unsigned long long)p);
-            __syncthreads();
-            ge = S.over_end;
-            break;
-          }
-        }
-        if (tid == 0) {
-          const int64_t LL = ge - gs0;
-          if (LL <= kLongSegMax) {
-            const int64_t at = atomicAdd(b.counters + 5, 1);
-            if (at < b.q_long_cap) b.q_long[at] = (unsigned long long)gs0 | ((unsigned long long)LL << 48);
-            else atomicMax(status, int(kStatusLongQueueOverflow));
-          } else {
-            const int64_t at = atomicAdd(b.counters + 6, 1);
-            if (at < b.q_huge_cap) {
-              b.q_huge[2 * at]     = (unsigned long long)gs0;
-              b.q_huge[2 * at + 1] = (unsigned long long)LL;
-            } else atomicMax(status, int(kStatusLongQueueOverflow));
-          }
-        }
-      }
-      GTK_PHASE(14);
-      const int first = S.first_start;
-      int end_owned   = 0;
-      if (S.last_start >= 0) end_owned = (S.over_start >= 0) ? S.over_start : next_cut(S.cut, S.last_start);
-      if (end_owned > wlen) end_owned = wlen;
-      for (int g = tid; g < used_groups; g += kOptThreads) {
-        const int i0 = g * 4;
-        if (i0 + 4 <= first || i0 >= end_owned) continue;
-        if (i0 >= first && i0 + 4 <= end_owned) {
-          *reinterpret_cast<uint2*>(b.staging + lo + i0) = *reinterpret_cast<const uint2*>(&S.tok[i0]);
-        } else {
-          for (int i = max(i0, first); i < min(i0 + 4, end_owned); ++i) b.staging[lo + i] = S.tok[i];
-        }
-      }
-      GTK_PHASE(15);
-      return;
-    }
-
     GTK_PHASE(4);
     // ---- F. one warp per long segment ----
     {
@@ -1511,376 +1255,7 @@ __global__ void __launch_bounds__(kOptThreads, 8) k_merge_opt(EncodeBuffers b, D
     __syncthreads();
     const int64_t k = S.ticket;
     if (k >= b.n_tiles) break;
-    opt_tile<false>(S, b, T, k, C);
-  }
-}
-
-// ------------------------------------------------------------------------------------------------
-// split pipeline, stage 1: the tile kernel in split mode (lookup + queues + positional store)
-// ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kOptThreads) k_front_split(EncodeBuffers b, DeviceTable T)
-{
-  OptSmem& S = g_tile;
-  const int tid   = threadIdx.x;
-  const int64_t C = b.totals[0];
-  opt_tile_setup(S, T);
-  for (;;) {
-    __syncthreads();
-    if (tid == 0) {
-      S.ticket = atomicAdd(b.counters + 0, 1);
-      opt_tile_reset(S);
-    }
-    __syncthreads();
-    const int64_t k = S.ticket;
-    if (k >= b.n_tiles) break;
-    opt_tile<true>(S, b, T, k, C);
-  }
-}
-
-// ------------------------------------------------------------------------------------------------
-// split pipeline, stage 2: one thread per queued short segment (2..32 bytes).  No CTA barrier:
-// a warp reserves 256 queue entries at a time, its lanes take the next entry whenever they finish
-// one, so a long merge chain delays nobody but its own lane.  Tokens and ranks of a lane live in
-// shared memory, interleaved by lane so that lanes working on the same index hit different banks.
-// ------------------------------------------------------------------------------------------------
-constexpr int kShortThreads = 256;
-constexpr int kShortBatch   = 256;  // queue entries a warp reserves with one global atomic
-
-struct LaneArrays {  // view of one lane's 32 tokens / ranks inside the interleaved arrays
-  uint16_t* base;
-  __device__ __forceinline__ uint16_t& operator[](int i) const { return base[i * kShortThreads]; }
-};
-
-__device__ __forceinline__ bool lane_merge_step(LaneArrays tok, LaneArrays rk, int L, uint32_t& alive,
-                                                const DeviceTable& T)
-{
-  if ((alive & (alive - 1u)) == 0u) return false;
-  uint32_t best = 0xFFFFFFFFu;
-  for (int i = 0; i < L - 1; ++i) best = min(best, (uint32_t(rk[i]) << 16) | uint32_t(i));
-  const uint32_t r = best >> 16;
-  if (r >= SEL) return false;
-  const int j = int(best & 0xFFFFu);
-  const int q = j + __ffs(int(alive >> (j + 1)));
-  const uint32_t c = merged_id(T, r);
-  tok[j] = uint16_t(c);
-  tok[q] = uint16_t(DEAD);
-  rk[q]  = uint16_t(NONE);
-  alive &= ~(1u << q);
-  const uint32_t right = (q >= 31) ? 0u : (alive >> (q + 1));
-  uint32_t rr          = NONE;
-  if (right) rr = probe_rank(T, c, tok[q + __ffs(int(right))]);
-  rk[j] = uint16_t(rr);
-  const uint32_t left = alive & ((1u << j) - 1u);
-  if (left) {
-    const int p = 31 - __clz(int(left));
-    rk[p]       = uint16_t(probe_rank(T, tok[p], c));
-  }
-  return true;
-}
-
-__global__ void __launch_bounds__(kShortThreads) k_merge_short(EncodeBuffers b, DeviceTable T)
-{
-  __shared__ uint16_t s_tok[32 * kShortThreads];
-  __shared__ uint16_t s_rk[32 * kShortThreads];
-  const int tid = threadIdx.x, lane = tid & 31;
-  const uint32_t lt = lanemask_lt();
-  const int64_t count = min(int64_t(b.counters[4]), b.q_short_cap);
-  const LaneArrays tok{s_tok + tid}, rk{s_rk + tid};
-  const bool identity_ids = T.byte_ids_identity != 0;
-  int64_t batch_next = 0, batch_end = 0;  // warp-uniform cursor over the reserved queue range
-  int64_t pos = -1;
-  int L = 0;
-  uint32_t alive = 0;
-  bool drained = false;
-  uint32_t key[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // bytes of the current segment (memo key)
-  for (;;) {
-    // lanes without a segment take the next queue entry (bytes travel with the entry) and set up
-    // their token and rank arrays; the entries the warp will take next are prefetched into L1
-    const bool need   = (pos < 0) && !drained;
-    const uint32_t nb = __ballot_sync(0xFFFFFFFFu, need);
-    if (nb) {
-      const int want = __popc(nb);
-      if (batch_next >= batch_end) {  // reserve a new range for the warp
-        long long base = 0;
-        if (lane == 0) base = (long long)atomicAdd(reinterpret_cast<unsigned long long*>(b.counters + 12),
-                                                   (unsigned long long)kShortBatch);
-        base       = __shfl_sync(0xFFFFFFFFu, base, 0);
-        batch_next = base;
-        batch_end  = min(int64_t(base) + kShortBatch, count);
-      }
-      if (need) {
-        const int64_t j = batch_next + __popc(nb & lt);
-        if (j < batch_end) {
-          const uint4* e = b.q_short + 3 * j;
-          if (j + want < batch_end) asm volatile("prefetch.global.L1 [%0];" ::"l"(e + 3 * want));
-          const uint4 e0 = __ldg(e);
-          L = int(e0.y >> 16);
-          if (L >= 2) {
-            pos = int64_t(e0.x) | (int64_t(e0.y & 0xFFFFu) << 32);
-            bool hit = false;
-            if (b.memo) {  // an earlier occurrence of the same bytes in this call: copy its ids
-              const uint4 e1 = __ldg(e + 1), e2 = __ldg(e + 2);
-              key[0] = e0.z; key[1] = e0.w; key[2] = e1.x; key[3] = e1.y;
-              key[4] = e1.z; key[5] = e1.w; key[6] = e2.x; key[7] = e2.y;
-#pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                const int rem = L - 4 * q;
-                if (rem <= 0) key[q] = 0u;
-                else if (rem < 4) key[q] &= (1u << (8 * rem)) - 1u;
-              }
-              const uint4* slot = b.memo + 4 * size_t(memo_slot(key, uint32_t(L), b.memo_log2));
-              const uint4 m0    = __ldcg(slot + 2);
-              if ((m0.x & kMemoStateMask) == kMemoReady && ((m0.x >> 16) & 0xFFu) == uint32_t(L)) {
-                const uint4 m1 = __ldcg(slot + 3), a = __ldcg(slot), c = __ldcg(slot + 1);
-                if (a.x == key[0] && a.y == key[1] && a.z == key[2] && a.w == key[3] && c.x == key[4] &&
-                    c.y == key[5] && c.z == key[6] && c.w == key[7]) {
-                  const int n = int(m0.x & 0xFFu);
-                  const uint32_t w[6] = {m0.y, m0.z, m0.w, m1.x, m1.y, m1.z};
-#pragma unroll
-                  for (int i = 0; i < kMemoMaxIds; ++i)
-                    if (i < n) b.staging[pos + i] = uint16_t(w[i >> 1] >> ((i & 1) * 16));
-                  for (int i = n; i < L; ++i) b.staging[pos + i] = uint16_t(DEAD);
-                  hit = true;
-                }
-              }
-            }
-            if (hit) {
-              pos = -1;
-            } else {
-              alive = (L >= 32) ? 0xFFFFFFFFu : ((1u << L) - 1u);
-              const uint8_t* pb = reinterpret_cast<const uint8_t*>(e) + 8;
-              uint32_t prev     = __ldg(pb);
-              tok[0] = identity_ids ? uint16_t(prev) : __ldg(T.byte_to_id + prev);
-              for (int i = 1; i < L; ++i) {
-                const uint32_t cur = __ldg(pb + i);
-                tok[i]    = identity_ids ? uint16_t(cur) : __ldg(T.byte_to_id + cur);
-                rk[i - 1] = __ldg(T.byte_pair_rank + ((prev << 8) | cur));
-                prev      = cur;
-              }
-              rk[L - 1] = uint16_t(NONE);
-            }
-          }
-        } else if (batch_next >= count) {
-          drained = true;
-        }
-      }
-      batch_next = min(batch_next + want, batch_end);
-    }
-    if (!__any_sync(0xFFFFFFFFu, pos >= 0)) {
-      if (__all_sync(0xFFFFFFFFu, drained)) break;
-      continue;
-    }
-    if (pos >= 0 && !lane_merge_step(tok, rk, L, alive, T)) {
-      uint32_t w[6] = {0, 0, 0, 0, 0, 0};
-      int n = 0;
-      for (int i = 0; i < L; ++i) {  // tokens and tombstones, position by position
-        const uint32_t t = tok[i];
-        b.staging[pos + i] = uint16_t(t);
-        if (t != DEAD) {
-          if (n < kMemoMaxIds) w[n >> 1] |= t << ((n & 1) * 16);
-          ++n;
-        }
-      }
-      if (b.memo && n <= kMemoMaxIds) {  // publish for later occurrences (write-once slot)
-        uint4* slot    = b.memo + 4 * size_t(memo_slot(key, uint32_t(L), b.memo_log2));
-        uint32_t* meta = reinterpret_cast<uint32_t*>(slot + 2);
-        if (atomicCAS(meta, 0u, kMemoBusy) == 0u) {
-          slot[0] = make_uint4(key[0], key[1], key[2], key[3]);
-          slot[1] = make_uint4(key[4], key[5], key[6], key[7]);
-          meta[1] = w[0];
-          meta[2] = w[1];
-          meta[3] = w[2];
-          slot[3] = make_uint4(w[3], w[4], w[5], 0u);
-          __threadfence();
-          atomicExch(meta, kMemoReady | (uint32_t(L) << 16) | uint32_t(n));
-        }
-      }
-      pos = -1;
-    }
-  }
-}
-
-// ------------------------------------------------------------------------------------------------
-// split pipeline, stage 3: one warp per long segment (33..kLongSegMax bytes) in shared memory, and
-// one CTA per huge segment in shared memory or the HBM workspace.  Tokens are written compacted at
-// the start of the segment's byte range, tombstones fill the rest.
-// ------------------------------------------------------------------------------------------------
-constexpr int kLongWarps = 4;
-
-__global__ void __launch_bounds__(kLongWarps * 32) k_merge_long(EncodeBuffers b, DeviceTable T)
-{
-  __shared__ uint16_t s_tok[kLongWarps][kLongSegMax];
-  __shared__ uint16_t s_rk[kLongWarps][kLongSegMax];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t count = min(int64_t(b.counters[5]), b.q_long_cap);
-  int* status = b.counters + 1;
-  uint16_t* tok = s_tok[warp];
-  uint16_t* rk  = s_rk[warp];
-  for (;;) {
-    int at = 0;
-    if (lane == 0) at = atomicAdd(b.counters + 9, 1);
-    at = __shfl_sync(0xFFFFFFFFu, at, 0);
-    if (at >= count) break;
-    const unsigned long long ent = b.q_long[at];
-    const int64_t pos = int64_t(ent & 0xFFFFFFFFFFFFull);
-    const int L       = int(ent >> 48);
-    for (int i = lane; i < L; i += 32) {
-      const uint32_t cur = b.bytes[pos + i];
-      tok[i] = __ldg(T.byte_to_id + cur);
-      rk[i]  = (i + 1 < L) ? __ldg(T.byte_pair_rank + ((cur << 8) | b.bytes[pos + i + 1])) : uint16_t(NONE);
-    }
-    __syncwarp();
-    const int len = group_merge<1>(tok, rk, L, T, nullptr, status);
-    for (int i = lane; i < L; i += 32) b.staging[pos + i] = (i < len) ? tok[i] : uint16_t(DEAD);
-    __syncwarp();
-  }
-}
-
-__global__ void __launch_bounds__(kBaseThreads) k_merge_huge(EncodeBuffers b, DeviceTable T)
-{
-  __shared__ uint16_t s_tok[kBaseSmemTokens];
-  __shared__ uint16_t s_rk[kBaseSmemTokens];
-  __shared__ GroupScratch gs;
-  __shared__ int ticket;
-  const int tid = threadIdx.x;
-  const int64_t count = min(int64_t(b.counters[6]), b.q_huge_cap);
-  int* status = b.counters + 1;
-  for (;;) {
-    __syncthreads();
-    if (tid == 0) ticket = atomicAdd(b.counters + 10, 1);
-    __syncthreads();
-    const int at = ticket;
-    if (at >= count) break;
-    const int64_t pos = int64_t(b.q_huge[2 * at]);
-    const int64_t L64 = int64_t(b.q_huge[2 * at + 1]);
-    uint16_t *tok = s_tok, *rk = s_rk;
-    if (L64 > kBaseSmemTokens) {
-      if (L64 > b.seg_scratch_tokens || b.seg_scratch == nullptr) {
-        if (tid == 0) atomicMax(status, int(kStatusScratchTooSmall));
-        continue;
-      }
-      tok = b.seg_scratch + int64_t(blockIdx.x) * 2 * b.seg_scratch_tokens;
-      rk  = tok + b.seg_scratch_tokens;
-    }
-    const int L = int(L64);
-    for (int i = tid; i < L; i += kBaseThreads) {
-      const uint32_t cur = b.bytes[pos + i];
-      tok[i] = __ldg(T.byte_to_id + cur);
-      rk[i]  = (i + 1 < L) ? __ldg(T.byte_pair_rank + ((cur << 8) | b.bytes[pos + i + 1])) : uint16_t(NONE);
-    }
-    __syncthreads();
-    const int len = group_merge<kBaseThreads / 32>(tok, rk, L, T, &gs, status);
-    for (int i = tid; i < L; i += kBaseThreads) b.staging[pos + i] = (i < len) ? tok[i] : uint16_t(DEAD);
-  }
-}
-
-// ------------------------------------------------------------------------------------------------
-// split pipeline, stages 4 and 5: positional tiles of kTile tokens slots.  k_count_tiles builds the
-// alive bitmap of a tile (slot != tombstone), stores the tile's token count and adds the per-chunk
-// counts; after the scans k_pack_tiles rebuilds the bitmap and writes the int32 ids back to back.
-// ------------------------------------------------------------------------------------------------
-struct PosTileSmem {
-  uint32_t alive[kTile / 32];
-  uint16_t woff[kTile / 32];
-  int scanbuf[33];
-  int32_t out[kTile];
-};
-
-// alive bitmap of tile k into S.alive; every thread handles 16 consecutive slots
-__device__ __forceinline__ void pos_tile_bitmap(const EncodeBuffers& b, int64_t k, uint32_t* alive, uint32_t tok16[8])
-{
-  const int tid = threadIdx.x, lane = tid & 31;
-  const int64_t lo = k * kTile + int64_t(tid) * 16;
-  uint32_t bits = 0;
-  if (lo + 16 <= b.n_bytes && ((reinterpret_cast<uintptr_t>(b.staging + lo) & 15u) == 0)) {
-    const uint4 a = *reinterpret_cast<const uint4*>(b.staging + lo);
-    const uint4 c = *reinterpret_cast<const uint4*>(b.staging + lo + 8);
-    tok16[0] = a.x; tok16[1] = a.y; tok16[2] = a.z; tok16[3] = a.w;
-    tok16[4] = c.x; tok16[5] = c.y; tok16[6] = c.z; tok16[7] = c.w;
-  } else {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const uint32_t t0 = (lo + 2 * j < b.n_bytes) ? b.staging[lo + 2 * j] : DEAD;
-      const uint32_t t1 = (lo + 2 * j + 1 < b.n_bytes) ? b.staging[lo + 2 * j + 1] : DEAD;
-      tok16[j] = t0 | (t1 << 16);
-    }
-  }
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    bits |= uint32_t((tok16[j] & 0xFFFFu) != DEAD) << (2 * j);
-    bits |= uint32_t((tok16[j] >> 16) != DEAD) << (2 * j + 1);
-  }
-  const uint32_t other = __shfl_xor_sync(0xFFFFFFFFu, bits, 1);
-  if ((lane & 1) == 0) alive[tid >> 1] = bits | (other << 16);
-}
-
-__global__ void __launch_bounds__(kOptThreads) k_count_tiles(EncodeBuffers b)
-{
-  __shared__ PosTileSmem S;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int64_t C = b.totals[0];
-  for (int64_t k = blockIdx.x; k < b.n_tiles; k += gridDim.x) {
-    uint32_t tok16[8];
-    __syncthreads();
-    pos_tile_bitmap(b, k, S.alive, tok16);
-    __syncthreads();
-    int total;
-    block_exclusive_scan((tid < kTile / 32) ? __popc(S.alive[tid]) : 0, S.scanbuf, &total);
-    if (tid == 0) {
-      b.unit_cnt[k]   = total;
-      b.unit_first[k] = k * kTile;
-    }
-    const int64_t lo = k * kTile, region_end = min(lo + kTile, b.n_bytes);
-    for (int64_t c = b.tile_chunk0[k] + warp; c < C; c += kOptThreads / 32) {
-      const int64_t cs_g = b.chunk_off[c];
-      if (cs_g >= region_end) break;
-      const int cs = int(max(cs_g, lo) - lo);
-      const int ce = int(min(b.chunk_off[c + 1], region_end) - lo);
-      if (ce <= cs) continue;
-      int cnt = 0;
-      for (int w = (cs >> 5) + lane; w <= ((ce - 1) >> 5); w += 32) {
-        uint32_t x = S.alive[w];
-        if (w == (cs >> 5)) x &= 0xFFFFFFFFu << (cs & 31);
-        if (w == ((ce - 1) >> 5)) x &= 0xFFFFFFFFu >> (31 - ((ce - 1) & 31));
-        cnt += __popc(x);
-      }
-      cnt = __reduce_add_sync(0xFFFFFFFFu, cnt);
-      if (lane == 0 && cnt) atomicAdd(b.chunk_cnt + c, cnt);
-    }
-  }
-}
-
-__global__ void __launch_bounds__(kOptThreads) k_pack_tiles(EncodeBuffers b)
-{
-  __shared__ PosTileSmem S;
-  const int tid = threadIdx.x;
-  for (int64_t k = blockIdx.x; k < b.n_tiles; k += gridDim.x) {
-    uint32_t tok16[8];
-    __syncthreads();
-    pos_tile_bitmap(b, k, S.alive, tok16);
-    __syncthreads();
-    int total;
-    {
-      const int off = block_exclusive_scan((tid < kTile / 32) ? __popc(S.alive[tid]) : 0, S.scanbuf, &total);
-      if (tid < kTile / 32) S.woff[tid] = uint16_t(off);
-    }
-    __syncthreads();
-    {
-      const uint32_t word = S.alive[tid >> 1];
-      const int sh        = (tid & 1) * 16;
-      int d               = S.woff[tid >> 1] + __popc(word & ((1u << sh) - 1u));
-      const uint32_t mine = (word >> sh) & 0xFFFFu;
-#pragma unroll
-      for (int j = 0; j < 16; ++j)
-        if ((mine >> j) & 1u) S.out[d++] = int32_t((tok16[j >> 1] >> ((j & 1) * 16)) & 0xFFFFu);
-    }
-    __syncthreads();
-    const int64_t dst = b.unit_base[k];
-    for (int j = tid; j < total; j += kOptThreads)
-      if (dst + j < b.out_capacity) {
-        const uint32_t t = uint32_t(S.out[j]);
-        b.out_ids[dst + j] = int32_t((b.low_id_map && t < 256u) ? uint32_t(__ldg(b.low_id_map + t)) : t);
-      }
+    opt_tile(S, b, T, k, C);
   }
 }
 
@@ -1956,7 +1331,7 @@ __global__ void __launch_bounds__(kOptThreads) k_encode_small(EncodeBuffers b, D
     __syncthreads();
     if (tid == 0) opt_tile_reset(S);
     __syncthreads();
-    opt_tile<false>(S, b, T, k, C);
+    opt_tile(S, b, T, k, C);
   }
   __syncthreads();
   // output: offsets of units, chunks and texts, then the packed ids
@@ -2249,25 +1624,6 @@ int launch_pack(const EncodeBuffers& b, int mode_base, int grid, cudaStream_t st
     k_pack<<<grid, 256, 0, stream>>>(b.staging, b.unit_first, b.unit_cnt, b.unit_base, b.n_tiles, nullptr, b.out_ids,
                                      b.out_capacity, b.low_id_map);
   }
-  return 1;
-}
-
-int launch_merge_split(const EncodeBuffers& b, const DeviceTable& t, int sm_count, int grid_front, cudaStream_t stream)
-{
-  if (b.n_tiles <= 0) return 0;
-  if (grid_front > b.n_tiles) grid_front = int(b.n_tiles);
-  k_front_split<<<grid_front, kOptThreads, 0, stream>>>(b, t);
-  k_merge_short<<<sm_count * 6, kShortThreads, 0, stream>>>(b, t);
-  k_merge_long<<<sm_count * 4, kLongWarps * 32, 0, stream>>>(b, t);
-  k_merge_huge<<<sm_count, kBaseThreads, 0, stream>>>(b, t);
-  k_count_tiles<<<unsigned(std::min<int64_t>(b.n_tiles, int64_t(sm_count) * 8)), kOptThreads, 0, stream>>>(b);
-  return 5;
-}
-
-int launch_pack_split(const EncodeBuffers& b, int grid, cudaStream_t stream)
-{
-  if (b.n_tiles <= 0) return 0;
-  k_pack_tiles<<<unsigned(std::min<int64_t>(b.n_tiles, int64_t(grid))), kOptThreads, 0, stream>>>(b);
   return 1;
 }
 

@@ -67,7 +67,6 @@ def load_library() -> C.CDLL:
     lib.gtk_token_symbols.argtypes = [vp, i32, C.c_char_p, i32]
     lib.gtk_token_symbols.restype = i32
     lib.gtk_set_stream.argtypes = [vp, vp]
-    lib.gtk_set_tuning.argtypes = [vp, C.c_int, C.c_int]
     lib.gtk_set_id_space.argtypes = [vp, C.c_int]
     lib.gtk_write_token_strings.argtypes = [vp, C.c_char_p, vp, vp, i64]
     lib.gtk_encode_chunks_noalloc.argtypes = [vp, vp, i64, vp, i64, i32, vp, vp]
@@ -168,11 +167,6 @@ class Tokenizer:
         off = np.ascontiguousarray(chunk_id_offsets, dtype=np.int64)
         self._check(self._lib.gtk_write_token_strings(self._h, os.fsencode(path), a.ctypes.data, off.ctypes.data,
                                                       len(off) - 1))
-
-    def set_tuning(self, pipeline: int = 0, memo: bool = False) -> None:
-        """pipeline: 0 auto, 1 fused tile kernel, 2 split (queues + per-segment kernels); memo: call-local
-        memo of finished segments.  Results never depend on these."""
-        self._check(self._lib.gtk_set_tuning(self._h, int(pipeline), int(bool(memo))))
 
     # ------------------------------------------------------------------ host buffers
     def _result(self, copy: bool = True):

@@ -195,14 +195,6 @@ GTK_API int gtk_set_id_space(gtk_tokenizer* h, int id_space);
 GTK_API int gtk_write_token_strings(const gtk_tokenizer* h, const char* path, const int32_t* ids,
                                     const int64_t* chunk_id_offsets, int64_t n_chunks);
 
-/* Tuning knobs of GTK_MODE_OPT (no counterpart in the reference; results never depend on them).
- *   pipeline  GTK_PIPELINE_AUTO (default), GTK_PIPELINE_FUSED: one tile kernel merges everything;
- *             GTK_PIPELINE_SPLIT: segments of more than 12 bytes leave the tile kernel through a
- *             queue and are merged by barrier-free per-segment kernels (batches >= 4 MiB only)
- *   memo      0 / 1: call-local memo of finished short segments (off by default)            */
-enum { GTK_PIPELINE_AUTO = 0, GTK_PIPELINE_FUSED = 1, GTK_PIPELINE_SPLIT = 2 };
-GTK_API int gtk_set_tuning(gtk_tokenizer* h, int pipeline, int memo);
-
 /* Longest chunk, in bytes, that gtk_encode_chunks_noalloc accepts. */
 #define GTK_NOALLOC_MAX_CHUNK_BYTES 16384
 

@@ -116,10 +116,8 @@ def test_config2_full_size(lib, merges_path, oracle):
         got = ids[coff[c]:coff[c + 1]]
         assert np.array_equal(got, lit), f"config2 chunk {c}: {first_mismatch(got, lit)}"
     assert t.decode(ids[:coff[256]]) == data[:256 * 4096].tobytes()
-    for pipeline, memo in ((2, True), (1, True)):       # every tuning gives the same ids
-        t.set_tuning(pipeline, memo)
-        ids_t, _, coff_t, _ = t.encode(data)
-        assert np.array_equal(ids_t, ids) and np.array_equal(coff_t, coff), f"pipeline {pipeline} memo {memo}"
+    ids_t, _, coff_t, _ = t.encode(data)                # a second run gives the same bits
+    assert np.array_equal(ids_t, ids) and np.array_equal(coff_t, coff), "config2: two runs differ"
     lens = np.array([len(oracle.token_bytes(i)) for i in range(oracle.vocab_size)], dtype=np.int64)
     per_chunk = np.add.reduceat(lens[ids], coff[:-1])
     assert np.array_equal(per_chunk, np.diff(off))        # every chunk decodes to exactly its own bytes
@@ -209,10 +207,8 @@ def test_long_and_huge_segments_in_a_large_batch(lib, merges_path, oracle):
     for s, e in zip(toff_in[:-1], toff_in[1:]):
         chunk_off.extend(list(range(int(s) + 65536, int(e), 65536)) + ([int(e)] if e > s else []))
     want, woff = oracle.encode_chunks(filler, np.array(chunk_off, np.int64), mode=MODE_SEGMENTED, threads=NCPU)
-    for pipeline, memo in ((0, False), (1, True), (2, False), (2, True)):
-        t.set_tuning(pipeline, memo)
-        ids, toff, coff, _ = t.encode(filler, toff_in)
-        check_chunks(ids, coff, want, woff, f"pipeline {pipeline} memo {memo}, all segment classes")
+    ids, toff, coff, _ = t.encode(filler, toff_in)
+    check_chunks(ids, coff, want, woff, "all segment classes")
     assert t.decode(ids[:coff[20]]) == filler[:chunk_off[20]].tobytes()
 
 
