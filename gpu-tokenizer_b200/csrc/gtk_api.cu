@@ -294,6 +294,7 @@ const char* status_text(int s)
     case gtk::kStatusLongQueueOverflow: return "long-segment queue overflow";
     case gtk::kStatusScratchTooSmall: return "segment workspace too small";
     case gtk::kStatusBadSegment: return "merge pass made no progress";
+    case gtk::kStatusBadOffsets: return "chunk offsets outside the text";
     default: return "unknown kernel status";
   }
 }
@@ -337,17 +338,34 @@ void run_pack(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* laun
   GTK_CUDA(cudaGetLastError());
 }
 
-// adds the stage times of one pipeline run (one batch, or one slice) to h->stage_ms
-void collect_stage_times(gtk_tokenizer* h, cudaEvent_t* ev = nullptr)
+// Adds the stage times of one pipeline run (one batch, or one slice) to h->stage_ms.  The events must have
+// completed and must not have been recorded again since: the sliced path therefore reads the front events
+// of a slice as soon as its front has finished (its arena's events are recorded again for a later slice
+// soon after) and the pack events when its ids have arrived.
+void collect_front_times(gtk_tokenizer* h, cudaEvent_t* ev = nullptr)
 {
   if (!ev) ev = h->ev;
   float ms = 0;
   for (int i = 0; i < 3; ++i) {
-    if (cudaEventElapsedTime(&ms, ev[i], ev[i + 1]) == cudaSuccess) h->stage_ms[i] += ms;
+    GTK_CUDA(cudaEventElapsedTime(&ms, ev[i], ev[i + 1]));
+    h->stage_ms[i] += ms;
   }
-  if (cudaEventElapsedTime(&ms, ev[5], ev[4]) == cudaSuccess) h->stage_ms[3] += ms;
+}
+
+void collect_pack_time(gtk_tokenizer* h, cudaEvent_t* ev = nullptr)
+{
+  if (!ev) ev = h->ev;
+  float ms = 0;
+  GTK_CUDA(cudaEventElapsedTime(&ms, ev[5], ev[4]));
+  h->stage_ms[3] += ms;
   // the pipeline time excludes the host round trip between scans and pack
   h->stage_ms[4] = h->stage_ms[0] + h->stage_ms[1] + h->stage_ms[2] + h->stage_ms[3];
+}
+
+void collect_stage_times(gtk_tokenizer* h)
+{
+  collect_front_times(h);
+  collect_pack_time(h);
 }
 
 
@@ -543,7 +561,7 @@ int encode_host_sliced(gtk_tokenizer* h, int mode, const uint8_t* bytes, const i
   auto finish = [&](int i) {  // the ids of slice i are on the host
     SliceArena& a = h->slice[i % kSliceArenas];
     GTK_CUDA(cudaEventSynchronize(a.ev_out));
-    collect_stage_times(h, a.ev);
+    collect_pack_time(h, a.ev);
   };
   auto sync_all = [&] {
     cudaStreamSynchronize(h->in_stream);
@@ -558,6 +576,7 @@ int encode_host_sliced(gtk_tokenizer* h, int mode, const uint8_t* bytes, const i
     SliceArena& a = h->slice[i % kSliceArenas];
     if (i >= 2) finish(i - 2);
     GTK_CUDA(cudaEventSynchronize(a.ev_front));
+    collect_front_times(h, a.ev);
     const int64_t* ht = a.h_totals.as<int64_t>();
     const int64_t C = ht[0], N = ht[1];
     const int status = reinterpret_cast<const int32_t*>(ht + 2)[1];
@@ -679,6 +698,31 @@ int encode_host_small(gtk_tokenizer* h, const uint8_t* bytes, const int64_t* tex
   return GTK_OK;
 }
 
+// frees every device / pinned buffer, stream and event of a handle (also used when gtk_create fails half way)
+void release_handle(gtk_tokenizer* h)
+{
+  if (h->device >= 0) {
+    cudaSetDevice(h->device);
+    if (h->stream) cudaStreamSynchronize(h->stream);
+    for (DevBuf* b : {&h->d_bpi, &h->d_slots, &h->d_overflow, &h->d_bpr, &h->d_mor, &h->d_sor, &h->d_adj, &h->d_b2i, &h->d_words, &h->d_low_map, &h->d_bytes, &h->d_text_off,
+                      &h->d_text_chunk_base, &h->d_chunk_off, &h->d_tile_chunk0, &h->d_staging, &h->d_unit_first,
+                      &h->d_unit_cnt, &h->d_chunk_cnt, &h->d_unit_base, &h->d_chunk_id_off, &h->d_text_id_off,
+                      &h->d_out_ids, &h->d_seg_scratch, &h->d_scan_sums, &h->d_counters, &h->d_totals})
+      b->release();
+    for (PinBuf* b : {&h->h_ids, &h->h_text_id_off, &h->h_chunk_id_off, &h->h_totals, &h->h_piece_off, &h->h_piece_id_off, &h->h_chunk_id_all}) b->release();
+    for (DevBuf* b : {&h->d_piece_off, &h->d_piece_id_off, &h->d_chunk_id_all}) b->release();
+    if (h->small_in_h) cudaFreeHost(h->small_in_h);
+    if (h->small_out_h) cudaFreeHost(h->small_out_h);
+    for (auto& sl : h->slice) sl.release();
+    if (h->in_stream) cudaStreamDestroy(h->in_stream);
+    if (h->out_stream) cudaStreamDestroy(h->out_stream);
+    if (h->pack_stream) cudaStreamDestroy(h->pack_stream);
+    for (auto& ev : h->ev)
+      if (ev) cudaEventDestroy(ev);
+    if (h->own_stream) cudaStreamDestroy(h->own_stream);
+  }
+}
+
 int validate_offsets(gtk_tokenizer* h, const int64_t* text_offsets, int64_t n_texts)
 {
   if (n_texts < 0) return h->fail(GTK_ERR_INVALID_ARG, "n_texts must be >= 0");
@@ -698,6 +742,7 @@ bool handle_view(gtk_tokenizer* h, HandleView* out)
   out->device = h->device;
   out->stream = h->stream;
   out->table = h->dtab;
+  out->low_id_map = (h->device >= 0 && h->id_space == GTK_IDS_GPT2) ? h->d_low_map.as<uint16_t>() : nullptr;
   out->pinned_words = h->device >= 0 ? h->h_totals.as<int32_t>() + 8 : nullptr;
   out->mu = &h->mu;
   out->last_error = &h->last_error;
@@ -773,10 +818,12 @@ GTK_API int gtk_create(const char* merges_path, int chunk_tokens, int max_iters,
     return GTK_OK;
   } catch (const CudaFail& f) {
     g_global_error = f.what;
+    if (h) release_handle(h);
     delete h;
     return GTK_ERR_CUDA;
   } catch (const std::bad_alloc&) {
     g_global_error = "out of host memory";
+    if (h) release_handle(h);
     delete h;
     return GTK_ERR_INVALID_ARG;
   }
@@ -785,26 +832,7 @@ GTK_API int gtk_create(const char* merges_path, int chunk_tokens, int max_iters,
 GTK_API void gtk_destroy(gtk_tokenizer* h)
 {
   if (!h) return;
-  if (h->device >= 0) {
-    cudaSetDevice(h->device);
-    if (h->stream) cudaStreamSynchronize(h->stream);
-    for (DevBuf* b : {&h->d_bpi, &h->d_slots, &h->d_overflow, &h->d_bpr, &h->d_mor, &h->d_sor, &h->d_adj, &h->d_b2i, &h->d_words, &h->d_low_map, &h->d_bytes, &h->d_text_off,
-                      &h->d_text_chunk_base, &h->d_chunk_off, &h->d_tile_chunk0, &h->d_staging, &h->d_unit_first,
-                      &h->d_unit_cnt, &h->d_chunk_cnt, &h->d_unit_base, &h->d_chunk_id_off, &h->d_text_id_off,
-                      &h->d_out_ids, &h->d_seg_scratch, &h->d_scan_sums, &h->d_counters, &h->d_totals})
-      b->release();
-    for (PinBuf* b : {&h->h_ids, &h->h_text_id_off, &h->h_chunk_id_off, &h->h_totals, &h->h_piece_off, &h->h_piece_id_off, &h->h_chunk_id_all}) b->release();
-    for (DevBuf* b : {&h->d_piece_off, &h->d_piece_id_off, &h->d_chunk_id_all}) b->release();
-    if (h->small_in_h) cudaFreeHost(h->small_in_h);
-    if (h->small_out_h) cudaFreeHost(h->small_out_h);
-    for (auto& sl : h->slice) sl.release();
-    if (h->in_stream) cudaStreamDestroy(h->in_stream);
-    if (h->out_stream) cudaStreamDestroy(h->out_stream);
-    if (h->pack_stream) cudaStreamDestroy(h->pack_stream);
-    for (auto& ev : h->ev)
-      if (ev) cudaEventDestroy(ev);
-    if (h->own_stream) cudaStreamDestroy(h->own_stream);
-  }
+  release_handle(h);
   delete h;
 }
 

@@ -45,6 +45,7 @@ enum : int {
   kStatusLongQueueOverflow = 1,
   kStatusScratchTooSmall = 2,
   kStatusBadSegment = 3,
+  kStatusBadOffsets = 4,  // caller-provided chunk offsets point outside the text or decrease
 };
 
 struct EncodeBuffers {
@@ -98,6 +99,7 @@ struct HandleView {
   int device;
   cudaStream_t stream;
   DeviceTable table;
+  const uint16_t* low_id_map;  // nullptr, or the 256-entry remap of ids < 256 (GPT-2 id space selected)
   int32_t* pinned_words;  // 8 ints of page-locked host memory owned by the handle
   std::mutex* mu;
   std::string* last_error;

@@ -1702,9 +1702,10 @@ constexpr int kMaxDevices         = 64;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
 
 __global__ void __launch_bounds__(gtk::kBaseThreads)
-k_merge_chunks_noalloc(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ chunk_off, int64_t n_chunks,
-                       int max_chunk, int32_t* __restrict__ out_ids, int32_t* __restrict__ out_counts,
-                       gtk::DeviceTable T, unsigned char* scratch)
+k_merge_chunks_noalloc(const uint8_t* __restrict__ bytes, int64_t n_bytes, const int64_t* __restrict__ chunk_off,
+                       int64_t n_chunks, int max_chunk, int32_t* __restrict__ out_ids,
+                       int32_t* __restrict__ out_counts, gtk::DeviceTable T,
+                       const uint16_t* __restrict__ low_id_map, unsigned char* scratch)
 {
   using namespace gtk;
   __shared__ uint16_t s_tok[kBaseSmemTokens];
@@ -1724,10 +1725,14 @@ k_merge_chunks_noalloc(const uint8_t* __restrict__ bytes, const int64_t* __restr
     if (c >= n_chunks) break;
     const int64_t cs  = chunk_off[c];
     const int64_t L64 = chunk_off[c + 1] - cs;
-    if (L64 <= 0 || L64 > max_chunk) {
+    // The offsets come from the caller's device memory and are used as indices below: a chunk that is not
+    // inside bytes[0, n_bytes) is skipped (count 0) and reported through the status word, never touched.
+    const bool outside = cs < 0 || L64 < 0 || cs > n_bytes || L64 > n_bytes - cs;
+    if (outside || L64 == 0 || L64 > max_chunk) {
       if (tid == 0) {
         out_counts[c] = 0;
-        if (L64 != 0) atomicMax(status, int(kStatusScratchTooSmall));
+        if (outside) atomicMax(status, int(kStatusBadOffsets));
+        else if (L64 != 0) atomicMax(status, int(kStatusScratchTooSmall));
       }
       continue;
     }
@@ -1741,7 +1746,10 @@ k_merge_chunks_noalloc(const uint8_t* __restrict__ bytes, const int64_t* __restr
     }
     __syncthreads();
     const int len = group_merge<kBaseThreads / 32>(tok, rk, L, T, &gs, status);
-    for (int j = tid; j < len; j += kBaseThreads) out_ids[cs + j] = int32_t(tok[j]);
+    for (int j = tid; j < len; j += kBaseThreads) {
+      const uint32_t t = tok[j];
+      out_ids[cs + j]  = int32_t((low_id_map && t < 256u) ? uint32_t(__ldg(low_id_map + t)) : t);
+    }
     if (tid == 0) out_counts[c] = len;
   }
 }
@@ -1779,6 +1787,7 @@ extern "C" GTK_API int gtk_encode_chunks_noalloc(gtk_tokenizer* h, const uint8_t
   if (v.device < 0) return fail(GTK_ERR_NO_DEVICE, "host-only handle: no GPU entry points");
   if (v.device >= kMaxDevices) return fail(GTK_ERR_INVALID_ARG, "device ordinal beyond the supported range");
   if (n_chunks < 0 || n_bytes < 0 || max_chunk_bytes <= 0) return fail(GTK_ERR_INVALID_ARG, "negative or zero size");
+  if (n_chunks > int64_t(0x7FFFFFF0)) return fail(GTK_ERR_INVALID_ARG, "more than 2^31 chunks in one call");
   if (max_chunk_bytes > GTK_NOALLOC_MAX_CHUNK_BYTES)
     return fail(GTK_ERR_CAPACITY, "max_chunk_bytes " + std::to_string(max_chunk_bytes) +
                                       " exceeds the allocation-free limit of " +
@@ -1793,13 +1802,17 @@ extern "C" GTK_API int gtk_encode_chunks_noalloc(gtk_tokenizer* h, const uint8_t
   e = cudaMemsetAsync(scratch, 0, kNoAllocHeader, v.stream);
   if (e != cudaSuccess) return fail(GTK_ERR_CUDA, std::string("cudaMemsetAsync: ") + cudaGetErrorString(e));
   const int grid = int(n_chunks < kNoAllocCtas ? n_chunks : kNoAllocCtas);
-  k_merge_chunks_noalloc<<<grid, gtk::kBaseThreads, 0, v.stream>>>(d_bytes, d_chunk_offsets, n_chunks, max_chunk_bytes,
-                                                                   d_out_ids, d_out_counts, v.table, scratch);
+  k_merge_chunks_noalloc<<<grid, gtk::kBaseThreads, 0, v.stream>>>(d_bytes, n_bytes, d_chunk_offsets, n_chunks,
+                                                                   max_chunk_bytes, d_out_ids, d_out_counts, v.table,
+                                                                   v.low_id_map, scratch);
   e = cudaGetLastError();
   if (e == cudaSuccess) e = cudaMemcpyAsync(v.pinned_words, scratch, 8, cudaMemcpyDeviceToHost, v.stream);
   if (e == cudaSuccess) e = cudaStreamSynchronize(v.stream);
   if (e != cudaSuccess) return fail(GTK_ERR_CUDA, std::string("allocation-free merge kernel: ") + cudaGetErrorString(e));
   const int status = v.pinned_words[1];
+  if (status == gtk::kStatusBadOffsets)
+    return fail(GTK_ERR_INVALID_ARG, "d_chunk_offsets must be non-decreasing and stay inside [0, n_bytes]: the "
+                                     "offending chunks were skipped (count 0)");
   if (status == gtk::kStatusScratchTooSmall)
     return fail(GTK_ERR_CAPACITY, "a chunk is longer than max_chunk_bytes (" + std::to_string(max_chunk_bytes) + ")");
   if (status != gtk::kStatusOk) return fail(GTK_ERR_KERNEL, "merge pass made no progress");

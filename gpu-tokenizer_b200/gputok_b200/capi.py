@@ -152,8 +152,18 @@ class Tokenizer:
                 "kernel_launches": n.value}
 
     def set_stream(self, cuda_stream: int | None) -> None:
-        """Run later GPU work on the caller's stream (e.g. ``torch.cuda.current_stream().cuda_stream``)."""
-        self._check(self._lib.gtk_set_stream(self._h, cuda_stream or None))
+        """Run later GPU work on the caller's stream (e.g. ``torch.cuda.current_stream().cuda_stream``).
+
+        ``None`` restores the handle's own (non-blocking) stream.  The integer 0 -- what a framework
+        reports for the legacy default stream -- selects that stream (passed on as cudaStreamLegacy),
+        so work queued there by the caller is ordered before the tokenizer's kernels."""
+        if cuda_stream is None:
+            ptr = None
+        elif int(cuda_stream) == 0:
+            ptr = 1  # cudaStreamLegacy
+        else:
+            ptr = int(cuda_stream)
+        self._check(self._lib.gtk_set_stream(self._h, ptr))
 
     def set_id_space(self, gpt2: bool) -> None:
         """False (default): ids as the reference produces them (ids < 256 are byte values);

@@ -173,9 +173,15 @@ GTK_API int gtk_decode(const gtk_tokenizer* h, const int32_t* ids, int64_t n_ids
 GTK_API int32_t gtk_token_symbols(const gtk_tokenizer* h, int32_t id, char* buf, int32_t capacity);
 
 /* Run all later GPU work of this handle on the caller's CUDA stream (a cudaStream_t passed as
- * void*; NULL restores the handle's own stream).  The reference always uses the default stream
- * (gputok_binding.cu:794-799); this lets a caller order the tokenizer against its own kernels and
- * time it with its own events.  The entry points stay synchronous on return. */
+ * void*).  NULL restores the handle's own stream, which is created non-blocking: work on it is NOT
+ * ordered against the legacy default stream.  To run on the legacy default stream itself -- the
+ * stream the reference always uses (gputok_binding.cu:794-799) and the one a framework reports as
+ * handle 0 -- pass cudaStreamLegacy, i.e. (void*)0x1; cudaStreamPerThread is (void*)0x2.
+ * Ordering contract of the device-pointer entry points (gtk_encode_device,
+ * gtk_encode_chunks_noalloc): the kernels read d_bytes / offsets and write the outputs on the
+ * handle's current stream; whatever produces the inputs or reuses the outputs must be ordered
+ * against that stream (same stream, an event, or a synchronisation before the call).  The entry
+ * points stay synchronous on return. */
 GTK_API int gtk_set_stream(gtk_tokenizer* h, void* cuda_stream);
 
 /* Id space of the ids returned by the GPU encode entry points (no counterpart in the reference,
@@ -211,7 +217,8 @@ GTK_API int gtk_write_token_strings(const gtk_tokenizer* h, const char* path, co
  *
  *   d_bytes[n_bytes]              text on the handle's device
  *   d_chunk_offsets[n_chunks+1]   int64, on the device: chunk c is bytes[off[c] .. off[c+1]);
- *                                 non-decreasing, off[n_chunks] <= n_bytes
+ *                                 non-decreasing, 0 <= off[c] <= n_bytes.  A chunk that breaks this is
+ *                                 not touched (its count is 0) and the call returns GTK_ERR_INVALID_ARG
  *   max_chunk_bytes               the caller's bound on off[c+1]-off[c]; values above
  *                                 GTK_NOALLOC_MAX_CHUNK_BYTES are rejected with GTK_ERR_CAPACITY
  *                                 before anything is launched; a chunk that breaks the bound is
@@ -219,6 +226,7 @@ GTK_API int gtk_write_token_strings(const gtk_tokenizer* h, const char* path, co
  *   d_out_ids[n_bytes]            int32; the ids of chunk c start at d_out_ids[off[c]] (the layout
  *                                 of the reference kernel's d_tokens_out, gputok_blockbpe.cu:530-537)
  *   d_out_counts[n_chunks]        int32 ids produced per chunk
+ * The ids follow gtk_set_id_space like those of the other GPU entry points.
  *
  * The first call on a device looks up the device address of the fixed array
  * (cudaGetSymbolAddress); make that first call before any stream capture.  All calls on a

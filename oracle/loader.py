@@ -26,10 +26,19 @@ MODE_SEGMENTED = 1   # literal Algorithm 1 on never-merge segments (oracle only)
 MODE_LOCALMIN = 2    # the binding's bpe_merge_cpu rule (not the parity target)
 
 
-def build(ref: bool = True) -> None:
-    """Compile the checkers (gcc/g++ only)."""
+def reference_root() -> str:
+    """Where the reference checkout is expected: ``$GTK_REFERENCE_ROOT``, else a directory named
+    ``reference`` beside the repository.  It need not exist (the GPU box has none)."""
+    return os.environ.get("GTK_REFERENCE_ROOT") or os.path.abspath(os.path.join(HERE, "..", "..", "reference"))
+
+
+def build(ref: bool | None = None) -> None:
+    """Compile the checkers (gcc/g++ only).  ``ref=None``: also compile the reference's own host
+    functions when its checkout is present."""
+    if ref is None:
+        ref = os.path.isfile(os.path.join(reference_root(), "gputok_blockbpe.cu"))
     targets = ["oracle"] + (["ref"] if ref else [])
-    subprocess.run(["make", "-s", "-C", HERE] + targets, check=True)
+    subprocess.run(["make", "-s", "-C", HERE, "REF_ROOT=" + reference_root()] + targets, check=True)
 
 
 def _u8(a) -> np.ndarray:

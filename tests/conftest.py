@@ -44,7 +44,7 @@ def native_built():
 def oracle(merges_path):
     from oracle.loader import Oracle, build
 
-    build(ref=os.path.isdir("/root/reference"))
+    build()
     return Oracle(merges_path)
 
 

@@ -53,11 +53,13 @@ def adversarial_cases() -> list[bytes]:
 
 
 def main() -> None:
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
-    from oracle.loader import MODE_GREEDY, MODE_LOCALMIN, Oracle, RefGreedy, build
+    from oracle.loader import MODE_GREEDY, MODE_LOCALMIN, Oracle, RefGreedy, build, reference_root
+
+    ref = sys.argv[1] if len(sys.argv) > 1 else reference_root()
+    os.environ["GTK_REFERENCE_ROOT"] = ref
 
     build(ref=True)
-    manifest = {"reference_root": ref, "sources": {}, "products": {}}
+    manifest = {"reference": "venugopalkadamba/gpu-tokenizer", "sources": {}, "products": {}}
 
     merges_src = os.path.join(ref, "data/gpt2_tokenizer/merges.txt")
     merges_dst = os.path.join(HERE, "gpt2_merges.txt")
