@@ -130,7 +130,7 @@ struct gtk_tokenizer {
   int max_iters = 50;
   int device = -1;
   int sm_count = 0;
-  int opt_grid = 0, base_grid = 0;
+  int opt_grid = 0, base_grid = 0, localmin_grid = 0;
   cudaStream_t stream = nullptr;      // stream in use
   cudaStream_t own_stream = nullptr;  // created by gtk_create
   cudaEvent_t ev[6] = {};
@@ -257,7 +257,7 @@ Plan plan_batch(gtk_tokenizer* h, const uint8_t* d_bytes, int64_t n_bytes, const
   const int64_t longest = std::min<int64_t>(h->chunk_tokens, n_bytes);
   int64_t scratch_tokens = 0;
   if (longest > gtk::kHalo) scratch_tokens = (longest + 63) & ~int64_t(63);
-  const int ctas = std::max(h->opt_grid, h->base_grid);
+  const int ctas = std::max(h->opt_grid, std::max(h->base_grid, h->localmin_grid));
   if (scratch_tokens) h->d_seg_scratch.reserve(size_t(ctas) * 2 * size_t(scratch_tokens) * 2);
 
   b.bytes = d_bytes;
@@ -312,7 +312,7 @@ void run_front(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* lau
   *launches += gtk::launch_chunker(b, s);
   GTK_CUDA(cudaEventRecord(ev[1], s));
   if (mode == GTK_MODE_BASE) *launches += gtk::launch_merge_base(b, h->dtab, h->base_grid, s);
-  else if (mode == GTK_MODE_LOCALMIN) *launches += gtk::launch_merge_localmin(b, h->dtab, h->base_grid, h->max_iters, s);
+  else if (mode == GTK_MODE_LOCALMIN) *launches += gtk::launch_merge_localmin(b, h->dtab, h->localmin_grid, h->max_iters, s);
   else *launches += gtk::launch_merge_opt(b, h->dtab, h->opt_grid, s);
   GTK_CUDA(cudaEventRecord(ev[2], s));
   *launches += gtk::launch_output_scans(b, mode != GTK_MODE_OPT, s);
@@ -512,7 +512,7 @@ int encode_host_sliced(gtk_tokenizer* h, int mode, const uint8_t* bytes, const i
   {
     const int64_t longest = std::min<int64_t>(h->chunk_tokens, max_bytes);
     if (longest > gtk::kHalo)
-      h->d_seg_scratch.reserve(size_t(std::max(h->opt_grid, h->base_grid)) * 2 * size_t((longest + 63) & ~int64_t(63)) * 2);
+      h->d_seg_scratch.reserve(size_t(std::max(h->opt_grid, std::max(h->base_grid, h->localmin_grid))) * 2 * size_t((longest + 63) & ~int64_t(63)) * 2);
   }
   h->d_piece_off.reserve(size_t(piece_at[nsz]) * 8);
   h->d_piece_id_off.reserve(size_t(piece_at[nsz]) * 8);
@@ -810,7 +810,8 @@ GTK_API int gtk_create(const char* merges_path, int chunk_tokens, int max_iters,
       for (auto& ev : h->ev) GTK_CUDA(cudaEventCreate(&ev));
       upload_table(h);
       h->opt_grid = h->sm_count * std::max(1, gtk::opt_kernel_max_blocks_per_sm());
-      h->base_grid = h->sm_count * std::max(1, gtk::base_kernel_max_blocks_per_sm());
+      h->base_grid = h->sm_count * std::max(1, gtk::base_kernel_max_blocks_per_sm(chunk_tokens));
+      h->localmin_grid = h->sm_count * std::max(1, gtk::localmin_kernel_max_blocks_per_sm());
       h->h_totals.reserve(64);
       small_path_init(h);
     }

@@ -18,7 +18,8 @@ constexpr int kHalo = 256;
 constexpr int kWindow = kTile + kHalo;
 constexpr int kOptThreads = 256;
 constexpr int kBaseThreads = 512;
-constexpr int kBaseSmemTokens = 8192;  // chunks up to this length stay in shared memory in the base kernel
+constexpr int kBaseSmemTokens = 8192;  // chunks up to this length stay in shared memory in the local-minimum and allocation-free kernels
+constexpr int kBaseSmemMaxTokens = 49152;  // one-CTA-per-chunk kernel: longest chunk held in (dynamic) shared memory, 4 bytes per slot
 constexpr int kThreadSegMax = 32;      // longest segment a single thread merges on its own
 
 // Pointers into HBM, passed by value to every kernel.
@@ -107,6 +108,8 @@ struct HandleView {
 bool handle_view(gtk_tokenizer* h, HandleView* out);
 
 int opt_kernel_max_blocks_per_sm();
-int base_kernel_max_blocks_per_sm();
+int base_kernel_max_blocks_per_sm(int chunk_bytes);
+int localmin_kernel_max_blocks_per_sm();
+void base_kernel_geometry(int chunk_bytes, int* warps, int* smem_tokens);
 
 }  // namespace gtk

@@ -225,11 +225,20 @@ __device__ __forceinline__ bool thread_merge_step(uint16_t* tok_all, uint16_t* r
 // A group of NW warps (one warp, or the whole CTA) merges one sequence pass by
 // pass.  tok/rk may point to shared memory or to an HBM workspace.
 //
-// Pass = (1) group-wide minimum of the cached ranks, (2) select occurrences of
-// that pair, (3) write the merged id / a tombstone, (4) compact tokens and
-// ranks in place -- each thread keeps its elements in registers between the
-// read and the write, offsets come from warp ballots and popc plus a cross-warp
-// sum, (5) re-probe only the pairs that touch a new token.
+// Slots: tok[i] is a token id or the DEAD tombstone; for a live slot rk[i] is the
+// cached rank of the pair (tok[i], next live token), NONE when there is none; a
+// dead slot has rk NONE.  Tombstones stay where they are and the slots are
+// compacted only when an eighth of them is dead, so a pass costs two sweeps over
+// the cached ranks plus work proportional to the number of merges:
+//   (1) group-wide minimum of the cached ranks (four ranks per 64-bit load when
+//       VEC, i.e. when rk is 8-byte aligned; warp redux + cross-warp exchange);
+//   (2) selection of the occurrences of that pair;
+//   (3) every selected occurrence writes the merged id and a tombstone and
+//       remembers its slot;
+//   (4) the two pairs next to every new token are probed again (only those);
+//   (5) in-place compaction when due -- each thread keeps its elements in
+//       registers between the read and the write, offsets come from warp ballots
+//       and popc plus a cross-warp sum.
 //
 // With a monotone table all non-overlapping occurrences of the winning pair,
 // taken left to right, are merged in one pass; this is what Algorithm 1 does
@@ -239,6 +248,7 @@ __device__ __forceinline__ bool thread_merge_step(uint16_t* tok_all, uint16_t* r
 struct GroupScratch {
   uint32_t red[2][32];
   uint32_t wsum[32];
+  int dead;  // tombstones since the last compaction (CTA-wide groups)
 };
 
 template <int NW>
@@ -262,8 +272,242 @@ __device__ __forceinline__ uint32_t group_min(uint32_t v, GroupScratch* gs, int&
   return v;
 }
 
+// first live slot after i (n when there is none) / before i (-1 when there is none)
+__device__ __forceinline__ int next_live(const uint16_t* tok, int i, int n)
+{
+  int j = i + 1;
+  while (j < n && tok[j] == DEAD) ++j;
+  return j;
+}
+__device__ __forceinline__ int prev_live(const uint16_t* tok, int i)
+{
+  int p = i - 1;
+  while (p >= 0 && tok[p] == DEAD) --p;
+  return p;
+}
+
+// The four ranks of 64-bit word w of rk[0..n); slots at or behind n read as NONE.
+__device__ __forceinline__ void rank_word(const uint16_t* rk, int w, int n, uint32_t q[4])
+{
+  const uint2 x = reinterpret_cast<const uint2*>(rk)[w];
+  q[0] = x.x & 0xFFFFu;
+  q[1] = x.x >> 16;
+  q[2] = x.y & 0xFFFFu;
+  q[3] = x.y >> 16;
+  if (4 * w + 4 > n) {
+#pragma unroll
+    for (int k = 1; k < 4; ++k)
+      if (4 * w + k >= n) q[k] = NONE;
+  }
+}
+
+// calls f(i) for every slot i < n whose cached rank equals `pick`
+template <int NW, bool VEC, class F>
+__device__ __forceinline__ void for_each_rank(const uint16_t* rk, int n, int tid, uint32_t pick, F f)
+{
+  constexpr int G = NW * 32;
+  if (VEC) {
+    const int nw = (n + 3) >> 2;
+    for (int w = tid; w < nw; w += G) {
+      uint32_t q[4];
+      rank_word(rk, w, n, q);
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (q[k] == pick) f(4 * w + k);
+    }
+  } else {
+    for (int i = tid; i < n; i += G)
+      if (rk[i] == pick) f(i);
+  }
+}
+
+// In-place compaction of tok/rk[0..n): returns the number of live slots, which end up at the front in order.
 template <int NW>
+__device__ __forceinline__ int group_compact(uint16_t* tok, uint16_t* rk, int n, GroupScratch* gs, int lane, int warp,
+                                             uint32_t lt)
+{
+  constexpr int G = NW * 32;
+  constexpr int E = 4;
+  int out = 0;
+  for (int base = 0; base < n; base += G * E) {
+    uint16_t t[E], q[E];
+    uint32_t bal[E];
+    int wt = 0;
+#pragma unroll
+    for (int k = 0; k < E; ++k) {
+      const int i  = base + warp * 32 * E + k * 32 + lane;
+      const bool v = i < n;
+      t[k]   = v ? tok[i] : uint16_t(DEAD);
+      q[k]   = v ? rk[i] : uint16_t(NONE);
+      bal[k] = __ballot_sync(0xFFFFFFFFu, t[k] != DEAD);
+      wt += __popc(bal[k]);
+    }
+    int pre = 0, tot = wt;
+    if (NW > 1) {
+      if (lane == 0) gs->wsum[warp] = uint32_t(wt);
+      __syncthreads();  // all loads of the batch are done, warp totals visible
+      tot = 0;
+      for (int w = 0; w < NW; ++w) {
+        const int x = int(gs->wsum[w]);
+        if (w < warp) pre += x;
+        tot += x;
+      }
+    } else {
+      __syncwarp();
+    }
+    int o = out + pre;
+#pragma unroll
+    for (int k = 0; k < E; ++k) {
+      if (t[k] != DEAD) {
+        const int d = o + __popc(bal[k] & lt);
+        tok[d] = t[k];
+        rk[d]  = q[k];
+      }
+      o += __popc(bal[k]);
+    }
+    out += tot;
+    gsync<NW>();
+  }
+  return out;
+}
+
+template <int NW, bool VEC>
 __device__ int group_merge(uint16_t* tok, uint16_t* rk, int L, const DeviceTable& T, GroupScratch* gs,
+                           int* status)
+{
+  constexpr int G    = NW * 32;
+  constexpr int kMem = 4;  // merged slots a thread remembers per pass; more fall back to a sweep
+  const int lane  = threadIdx.x & 31;
+  const int warp  = (NW == 1) ? 0 : (threadIdx.x >> 5);
+  const int tid   = (NW == 1) ? lane : int(threadIdx.x);
+  const uint32_t lt = lanemask_lt();
+  const bool batch  = T.monotone != 0;
+  int parity = 0;
+  int n      = L;  // slots in use
+  int dead   = 0;  // tombstones among them
+  if (NW > 1) {
+    if (tid == 0) gs->dead = 0;
+    __syncthreads();
+  }
+  for (int pass = 0; pass < L && n - dead >= 2; ++pass) {
+    // (1) lowest cached rank
+    uint32_t m = NONE;
+    if (VEC) {
+      const int nw = (n + 3) >> 2;
+      for (int w = tid; w < nw; w += G) {
+        uint32_t q[4];
+        rank_word(rk, w, n, q);
+        m = min(m, min(min(q[0], q[1]), min(q[2], q[3])));
+      }
+    } else {
+      for (int i = tid; i < n; i += G) m = min(m, uint32_t(rk[i]));
+    }
+    m = group_min<NW>(m, gs, parity, lane, warp);
+    if (m >= SEL) break;
+    const uint32_t r = m;
+    const uint32_t c = merged_id(T, r);
+    const bool same  = batch && (__ldg(T.same_of_rank + r) != 0);
+    // (2) selection
+    if (!batch) {
+      uint32_t p = 0xFFFFFFFFu;
+      for_each_rank<NW, VEC>(rk, n, tid, r, [&](int i) { p = min(p, uint32_t(i)); });
+      p = group_min<NW>(p, gs, parity, lane, warp);
+      gsync<NW>();
+      if (tid == 0) rk[p] = uint16_t(SEL);
+      gsync<NW>();
+    } else if (same) {
+      // occurrences of (a,a) overlap inside a run a a a ...; left to right
+      // selection keeps the even offsets of every maximal run of matches
+      for_each_rank<NW, VEC>(rk, n, tid, r, [&](int i) {
+        const int pl = prev_live(tok, i);
+        if (pl >= 0) {
+          const uint32_t pv = rk[pl];
+          if (pv == r || pv == SEL) return;  // not the first match of its run
+        }
+        int j = i;
+        for (;;) {
+          rk[j] = uint16_t(SEL);
+          const int j1 = next_live(tok, j, n);
+          if (j1 >= n || rk[j1] != r) break;
+          const int j2 = next_live(tok, j1, n);
+          if (j2 >= n || rk[j2] != r) break;
+          j = j2;
+        }
+      });
+      gsync<NW>();
+    }
+    const uint32_t pick = (!batch || same) ? SEL : r;
+    // (3) apply: the selected occurrences never share a slot, so the writes are disjoint
+    int mine = 0;
+    int at[kMem];
+    for_each_rank<NW, VEC>(rk, n, tid, pick, [&](int i) {
+      const int j = next_live(tok, i, n);  // exists: the pair has a cached rank
+      tok[i] = uint16_t(c);
+      rk[i]  = uint16_t(NONE);
+      if (j < n) {
+        tok[j] = uint16_t(DEAD);
+        rk[j]  = uint16_t(NONE);
+      }
+#pragma unroll
+      for (int k = 0; k < kMem; ++k)
+        if (mine == k) at[k] = i;
+      ++mine;
+    });
+    bool sweep;
+    if (NW > 1) {
+      const int wsum = __reduce_add_sync(0xFFFFFFFFu, mine);
+      if (lane == 0 && wsum) atomicAdd(&gs->dead, wsum);
+      sweep = __syncthreads_or(mine > kMem) != 0;
+      const int now = gs->dead;
+      if (now == dead) {  // a pass must remove at least one token
+        if (tid == 0 && status) atomicMax(status, int(kStatusBadSegment));
+        break;
+      }
+      dead = now;
+    } else {
+      const int wsum = __reduce_add_sync(0xFFFFFFFFu, mine);
+      sweep          = __any_sync(0xFFFFFFFFu, mine > kMem) != 0;
+      if (wsum == 0) {
+        if (tid == 0 && status) atomicMax(status, int(kStatusBadSegment));
+        break;
+      }
+      dead += wsum;
+    }
+    // (4) ranks of the two pairs next to every new token
+    auto refresh = [&](int i) {
+      const int jn = next_live(tok, i, n);
+      rk[i] = uint16_t((jn < n) ? probe_rank(T, c, tok[jn]) : NONE);
+      const int pl = prev_live(tok, i);
+      if (pl >= 0) rk[pl] = uint16_t(probe_rank(T, tok[pl], c));
+    };
+    if (!sweep) {
+#pragma unroll
+      for (int k = 0; k < kMem; ++k)
+        if (k < mine) refresh(at[k]);
+    } else {
+      for (int i = tid; i < n; i += G)
+        if (tok[i] == c) refresh(i);
+    }
+    gsync<NW>();
+    // (5) compaction when an eighth of the slots is dead
+    if (dead * 8 >= n) {
+      n    = group_compact<NW>(tok, rk, n, gs, lane, warp, lt);
+      dead = 0;
+      if (NW > 1) {
+        if (tid == 0) gs->dead = 0;
+        __syncthreads();
+      }
+    }
+  }
+  if (dead) n = group_compact<NW>(tok, rk, n, gs, lane, warp, lt);
+  return n;
+}
+
+// The same merge with a compaction in every pass: cheaper for the short sequences a single warp handles
+// inside a tile (a few dozen to a few hundred tokens), where a sweep costs little and the tombstone searches of
+// the lazy variant do not pay.
+template <int NW>
+__device__ int group_merge_dense(uint16_t* tok, uint16_t* rk, int L, const DeviceTable& T, GroupScratch* gs,
                            int* status)
 {
   constexpr int G = NW * 32;
@@ -617,6 +861,7 @@ constexpr int kLongCap  = 128;
 #else
 #define GTK_PHASE(k) do { } while (0)
 #endif
+
 
 struct OptSmem {
   // seg and bytes are adjacent on purpose: once the segments have been looked up, bytes and the unused tail of
@@ -1111,7 +1356,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
       for (int q = warp; q < nl; q += kOptThreads / 32) {
         const int s   = S.longq[q];
         const int L   = next_cut(S.cut, s) - s;
-        const int len = group_merge<1>(S.tok + s, S.rk + s, L, T, nullptr, status);  // ids at the front
+        const int len = group_merge_dense<1>(S.tok + s, S.rk + s, L, T, nullptr, status);  // ids at the front
         mark_alive_range(S.cut, s + 1, s + len, lane);
         __syncwarp();
       }
@@ -1221,7 +1466,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
           wrk[i]  = (i + 1 < L) ? __ldg(T.byte_pair_rank + ((cur << 8) | b.bytes[gs0 + i + 1])) : uint16_t(NONE);
         }
         __syncthreads();
-        const int len = group_merge<kOptThreads / 32>(wtok, wrk, L, T, &S.gs, status);
+        const int len = group_merge<kOptThreads / 32, true>(wtok, wrk, L, T, &S.gs, status);
         for (int j = tid; j < len; j += kOptThreads) b.staging[region_start + total + j] = wtok[j];
         if (tid == 0) {
           atomicAdd(b.chunk_cnt + S.over_chunk, len);
@@ -1357,10 +1602,18 @@ __global__ void __launch_bounds__(kOptThreads) k_encode_small(EncodeBuffers b, D
 // ------------------------------------------------------------------------------------------------
 // merge kernel, one CTA per chunk ("base")
 // ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kBaseThreads) k_merge_base(EncodeBuffers b, DeviceTable T)
+extern __shared__ __align__(16) unsigned char g_dyn_smem[];
+
+// The chunk lives in dynamic shared memory (tokens and cached ranks, 16 bits each, `smem_tokens` slots per
+// array); a chunk longer than that takes the HBM workspace.  NW warps per CTA: few for short chunks (the cost
+// of a pass is dominated by its fixed part, so many small CTAs per SM give the best throughput), many for
+// long ones.
+template <int NW>
+__global__ void __launch_bounds__(NW * 32) k_merge_base(EncodeBuffers b, DeviceTable T, int smem_tokens)
 {
-  __shared__ uint16_t s_tok[kBaseSmemTokens];
-  __shared__ uint16_t s_rk[kBaseSmemTokens];
+  constexpr int G = NW * 32;
+  uint16_t* s_tok = reinterpret_cast<uint16_t*>(g_dyn_smem);
+  uint16_t* s_rk  = s_tok + smem_tokens;
   __shared__ GroupScratch gs;
   __shared__ int ticket;
   const int tid   = threadIdx.x;
@@ -1375,7 +1628,7 @@ __global__ void __launch_bounds__(kBaseThreads) k_merge_base(EncodeBuffers b, De
     const int64_t cs  = b.chunk_off[c];
     const int64_t L64 = b.chunk_off[c + 1] - cs;
     uint16_t *tok = s_tok, *rk = s_rk;
-    if (L64 > kBaseSmemTokens) {
+    if (L64 > smem_tokens) {
       if (L64 > b.seg_scratch_tokens || b.seg_scratch == nullptr) {
         if (tid == 0) {
           atomicMax(status, int(kStatusScratchTooSmall));
@@ -1387,14 +1640,14 @@ __global__ void __launch_bounds__(kBaseThreads) k_merge_base(EncodeBuffers b, De
       rk  = tok + b.seg_scratch_tokens;
     }
     const int L = int(L64);
-    for (int i = tid; i < L; i += kBaseThreads) {
+    for (int i = tid; i < L; i += G) {
       const uint32_t cur = b.bytes[cs + i];
       tok[i] = __ldg(T.byte_to_id + cur);
       rk[i]  = (i + 1 < L) ? __ldg(T.byte_pair_rank + ((cur << 8) | b.bytes[cs + i + 1])) : uint16_t(NONE);
     }
     __syncthreads();
-    const int len = group_merge<kBaseThreads / 32>(tok, rk, L, T, &gs, status);
-    for (int j = tid; j < len; j += kBaseThreads) b.staging[cs + j] = tok[j];
+    const int len = group_merge<NW, true>(tok, rk, L, T, &gs, status);
+    for (int j = tid; j < len; j += G) b.staging[cs + j] = tok[j];
     if (tid == 0) b.chunk_cnt[c] = len;
   }
 }
@@ -1447,8 +1700,8 @@ __device__ int compact_tokens(uint16_t* tok, int len, GroupScratch* gs)
 
 __global__ void __launch_bounds__(kBaseThreads) k_merge_localmin(EncodeBuffers b, DeviceTable T, int max_iters)
 {
-  __shared__ uint16_t s_tok[kBaseSmemTokens];
-  __shared__ uint16_t s_rk[kBaseSmemTokens];
+  __shared__ __align__(16) uint16_t s_tok[kBaseSmemTokens];
+  __shared__ __align__(16) uint16_t s_rk[kBaseSmemTokens];
   __shared__ GroupScratch gs;
   __shared__ int ticket;
   const int tid   = threadIdx.x;
@@ -1578,12 +1831,42 @@ int launch_merge_opt(const EncodeBuffers& b, const DeviceTable& t, int grid, cud
   return 1;
 }
 
+// Geometry of the one-CTA-per-chunk kernel for a chunk size: warps per CTA and slots of shared memory per array.
+void base_kernel_geometry(int chunk_bytes, int* warps, int* smem_tokens)
+{
+  const int c  = std::max(chunk_bytes, 1);
+  const int w  = (c + 1023) >> 10;  // one warp per KiB of chunk
+  *warps       = w <= 2 ? 2 : w <= 4 ? 4 : w <= 8 ? 8 : w <= 16 ? 16 : 32;
+  *smem_tokens = (std::min(c, kBaseSmemMaxTokens) + 63) & ~63;
+}
+
+namespace {
+template <int NW>
+int base_blocks_per_sm(int smem_tokens)
+{
+  const int bytes = smem_tokens * 4;
+  cudaFuncSetAttribute(k_merge_base<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  int nb = 0;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, k_merge_base<NW>, NW * 32, bytes);
+  return nb;
+}
+}  // namespace
+
 int launch_merge_base(const EncodeBuffers& b, const DeviceTable& t, int grid, cudaStream_t stream)
 {
   if (b.n_bytes <= 0) return 0;
   if (grid > b.chunk_cap) grid = int(b.chunk_cap);
   if (grid < 1) grid = 1;
-  k_merge_base<<<grid, kBaseThreads, 0, stream>>>(b, t);
+  int nw = 0, st = 0;
+  base_kernel_geometry(b.chunk_bytes, &nw, &st);
+  const size_t bytes = size_t(st) * 4;
+  switch (nw) {
+    case 2: k_merge_base<2><<<grid, 64, bytes, stream>>>(b, t, st); break;
+    case 4: k_merge_base<4><<<grid, 128, bytes, stream>>>(b, t, st); break;
+    case 8: k_merge_base<8><<<grid, 256, bytes, stream>>>(b, t, st); break;
+    case 16: k_merge_base<16><<<grid, 512, bytes, stream>>>(b, t, st); break;
+    default: k_merge_base<32><<<grid, 1024, bytes, stream>>>(b, t, st); break;
+  }
   return 1;
 }
 
@@ -1672,10 +1955,25 @@ int opt_kernel_max_blocks_per_sm()
   return nb;
 }
 
-int base_kernel_max_blocks_per_sm()
+// Call once per device and chunk size (that device current): opts the kernel in to its dynamic shared memory
+// and returns the resident CTAs per SM.
+int base_kernel_max_blocks_per_sm(int chunk_bytes)
+{
+  int nw = 0, st = 0;
+  base_kernel_geometry(chunk_bytes, &nw, &st);
+  switch (nw) {
+    case 2: return base_blocks_per_sm<2>(st);
+    case 4: return base_blocks_per_sm<4>(st);
+    case 8: return base_blocks_per_sm<8>(st);
+    case 16: return base_blocks_per_sm<16>(st);
+    default: return base_blocks_per_sm<32>(st);
+  }
+}
+
+int localmin_kernel_max_blocks_per_sm()
 {
   int nb = 0;
-  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, k_merge_base, kBaseThreads, 0);
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, k_merge_localmin, kBaseThreads, 0);
   return nb;
 }
 
@@ -1708,8 +2006,8 @@ k_merge_chunks_noalloc(const uint8_t* __restrict__ bytes, int64_t n_bytes, const
                        const uint16_t* __restrict__ low_id_map, unsigned char* scratch)
 {
   using namespace gtk;
-  __shared__ uint16_t s_tok[kBaseSmemTokens];
-  __shared__ uint16_t s_rk[kBaseSmemTokens];
+  __shared__ __align__(16) uint16_t s_tok[kBaseSmemTokens];
+  __shared__ __align__(16) uint16_t s_rk[kBaseSmemTokens];
   __shared__ GroupScratch gs;
   __shared__ int ticket;
   const int tid   = threadIdx.x;
@@ -1745,7 +2043,7 @@ k_merge_chunks_noalloc(const uint8_t* __restrict__ bytes, int64_t n_bytes, const
       rk[i]  = (i + 1 < L) ? __ldg(T.byte_pair_rank + ((cur << 8) | bytes[cs + i + 1])) : uint16_t(NONE);
     }
     __syncthreads();
-    const int len = group_merge<kBaseThreads / 32>(tok, rk, L, T, &gs, status);
+    const int len = group_merge<kBaseThreads / 32, true>(tok, rk, L, T, &gs, status);
     for (int j = tid; j < len; j += kBaseThreads) {
       const uint32_t t = tok[j];
       out_ids[cs + j]  = int32_t((low_id_map && t < 256u) ? uint32_t(__ldg(low_id_map + t)) : t);
@@ -1818,3 +2116,4 @@ extern "C" GTK_API int gtk_encode_chunks_noalloc(gtk_tokenizer* h, const uint8_t
   if (status != gtk::kStatusOk) return fail(GTK_ERR_KERNEL, "merge pass made no progress");
   return GTK_OK;
 }
+
