@@ -286,19 +286,11 @@ __device__ __forceinline__ int prev_live(const uint16_t* tok, int i)
   return p;
 }
 
-// The four ranks of 64-bit word w of rk[0..n); slots at or behind n read as NONE.
-__device__ __forceinline__ void rank_word(const uint16_t* rk, int w, int n, uint32_t q[4])
+// VEC sweeps read the cached ranks four at a time (one 64-bit load) and reduce them with the packed 16-bit
+// three-input minimum; the up to three slots between n and the next multiple of four hold NONE (pad_ranks).
+__device__ __forceinline__ void pad_ranks(uint16_t* rk, int n, int tid)
 {
-  const uint2 x = reinterpret_cast<const uint2*>(rk)[w];
-  q[0] = x.x & 0xFFFFu;
-  q[1] = x.x >> 16;
-  q[2] = x.y & 0xFFFFu;
-  q[3] = x.y >> 16;
-  if (4 * w + 4 > n) {
-#pragma unroll
-    for (int k = 1; k < 4; ++k)
-      if (4 * w + k >= n) q[k] = NONE;
-  }
+  if (tid < ((4 - (n & 3)) & 3)) rk[n + tid] = uint16_t(NONE);
 }
 
 // calls f(i) for every slot i < n whose cached rank equals `pick`
@@ -307,13 +299,18 @@ __device__ __forceinline__ void for_each_rank(const uint16_t* rk, int n, int tid
 {
   constexpr int G = NW * 32;
   if (VEC) {
-    const int nw = (n + 3) >> 2;
+    const int nw      = (n + 3) >> 2;
+    const uint32_t p2 = pick | (pick << 16);
     for (int w = tid; w < nw; w += G) {
-      uint32_t q[4];
-      rank_word(rk, w, n, q);
+      const uint2 x = reinterpret_cast<const uint2*>(rk)[w];
+      // a half-word of z is zero exactly when one of the four ranks equals pick
+      const uint32_t z = __vimin3_u16x2(x.x ^ p2, x.y ^ p2, 0xFFFFFFFFu);
+      if ((z & 0xFFFFu) == 0u || (z >> 16) == 0u) {
+        const uint32_t q[4] = {x.x & 0xFFFFu, x.x >> 16, x.y & 0xFFFFu, x.y >> 16};
 #pragma unroll
-      for (int k = 0; k < 4; ++k)
-        if (q[k] == pick) f(4 * w + k);
+        for (int k = 0; k < 4; ++k)
+          if (q[k] == pick) f(4 * w + k);
+      }
     }
   } else {
     for (int i = tid; i < n; i += G)
@@ -385,20 +382,24 @@ __device__ int group_merge(uint16_t* tok, uint16_t* rk, int L, const DeviceTable
   int parity = 0;
   int n      = L;  // slots in use
   int dead   = 0;  // tombstones among them
+  if (VEC) pad_ranks(rk, n, tid);
   if (NW > 1) {
     if (tid == 0) gs->dead = 0;
     __syncthreads();
+  } else {
+    __syncwarp();
   }
   for (int pass = 0; pass < L && n - dead >= 2; ++pass) {
     // (1) lowest cached rank
     uint32_t m = NONE;
     if (VEC) {
       const int nw = (n + 3) >> 2;
+      uint32_t m2  = 0xFFFFFFFFu;
       for (int w = tid; w < nw; w += G) {
-        uint32_t q[4];
-        rank_word(rk, w, n, q);
-        m = min(m, min(min(q[0], q[1]), min(q[2], q[3])));
+        const uint2 x = reinterpret_cast<const uint2*>(rk)[w];
+        m2 = __vimin3_u16x2(m2, x.x, x.y);
       }
+      m = min(m2 & 0xFFFFu, m2 >> 16);
     } else {
       for (int i = tid; i < n; i += G) m = min(m, uint32_t(rk[i]));
     }
@@ -493,9 +494,12 @@ __device__ int group_merge(uint16_t* tok, uint16_t* rk, int L, const DeviceTable
     if (dead * 8 >= n) {
       n    = group_compact<NW>(tok, rk, n, gs, lane, warp, lt);
       dead = 0;
+      if (VEC) pad_ranks(rk, n, tid);
       if (NW > 1) {
         if (tid == 0) gs->dead = 0;
         __syncthreads();
+      } else {
+        __syncwarp();
       }
     }
   }
