@@ -110,11 +110,14 @@ def test_config2_full_size(lib, merges_path, oracle):
     off = fixed_chunk_offsets(n, 4096)
     want, woff = oracle.encode_chunks(data, off, mode=MODE_SEGMENTED, threads=NCPU)
     check_chunks(ids, coff, want, woff, "config2/all")
+    # the literal rule on the seeded 1 % sample (655 chunks; ~40 ms per 4 KiB chunk and core)
     sample = np.sort(np.random.default_rng(1).choice(65536, size=655, replace=False))
-    for c in sample[:: max(1, len(sample) // 200)]:   # literal rule is ~40 ms per 4 KiB chunk on one core
-        lit, _ = oracle.encode_chunks(data, off[c:c + 2], mode=MODE_GREEDY)
-        got = ids[coff[c]:coff[c + 1]]
-        assert np.array_equal(got, lit), f"config2 chunk {c}: {first_mismatch(got, lit)}"
+    blob = np.concatenate([data[off[c]:off[c + 1]] for c in sample])
+    lit, loff = oracle.encode_chunks(blob, np.arange(0, len(blob) + 1, 4096, dtype=np.int64), mode=MODE_GREEDY,
+                                     threads=NCPU)
+    for k, c in enumerate(sample):
+        got, exp = ids[coff[c]:coff[c + 1]], lit[loff[k]:loff[k + 1]]
+        assert np.array_equal(got, exp), f"config2 chunk {c}: {first_mismatch(got, exp)}"
     assert t.decode(ids[:coff[256]]) == data[:256 * 4096].tobytes()
     ids_t, _, coff_t, _ = t.encode(data)                # a second run gives the same bits
     assert np.array_equal(ids_t, ids) and np.array_equal(coff_t, coff), "config2: two runs differ"
@@ -124,25 +127,31 @@ def test_config2_full_size(lib, merges_path, oracle):
 
 
 def test_config4_long_chunks_unicode_runs(lib, merges_path, oracle):
-    """Stress mix (seed 3), 32 KiB chunks: literal oracle on a sample, segmented oracle on all."""
-    n = 16 << 20
+    """Stress mix (seed 3), 64 MiB in 32 KiB chunks: segmented oracle on all chunks in the fast mode and on
+    8 MiB in the one-CTA-per-chunk mode, the literal rule on four chunks (seconds per chunk and core)."""
+    n = 64 << 20
     data = lib.TextGen(3).text(n, mix=lib.MIX_STRESS)
     off = fixed_chunk_offsets(n, 32768)
     want, woff = oracle.encode_chunks(data, off, mode=MODE_SEGMENTED, threads=NCPU)
     t = make_tok(lib, merges_path, 32768)
     ids, _, coff, _ = t.encode(data)
     check_chunks(ids, coff, want, woff, "config4/opt")
-    ids_b, _, coff_b, _ = t.encode(data[:2 << 20], mode=lib.GTK_MODE_BASE)
-    check_chunks(ids_b, coff_b, want[:woff[64]], woff[:65], "config4/base")
-    for c in (0, 7, 100, 511):
-        lit, _ = oracle.encode_chunks(data, off[c:c + 2], mode=MODE_SEGMENTED)
-        assert np.array_equal(ids[coff[c]:coff[c + 1]], lit)
+    ids_b, _, coff_b, _ = t.encode(data[:8 << 20], mode=lib.GTK_MODE_BASE)
+    check_chunks(ids_b, coff_b, want[:woff[256]], woff[:257], "config4/base")
+    picks = [0, 7, 100, 2047]
+    blob = np.concatenate([data[off[c]:off[c + 1]] for c in picks])
+    lit, loff = oracle.encode_chunks(blob, np.arange(0, len(blob) + 1, 32768, dtype=np.int64), mode=MODE_GREEDY,
+                                     threads=len(picks))
+    for k, c in enumerate(picks):
+        got, exp = ids[coff[c]:coff[c + 1]], lit[loff[k]:loff[k + 1]]
+        assert np.array_equal(got, exp), f"config4 chunk {c} against the literal rule: {first_mismatch(got, exp)}"
     assert t.decode(ids[:coff[8]]) == data[:8 * 32768].tobytes()
 
 
 def test_config5_lognormal_chunks(lib, merges_path, oracle):
-    """Variable-length texts (log-normal, 64 B .. 64 KiB), one chunk each."""
-    n = 64 << 20
+    """Variable-length texts (log-normal, 64 B .. 64 KiB), one chunk each; 512 MiB of the seed-4 text against
+    the segmented oracle, a seeded sample of texts against the literal rule."""
+    n = 512 << 20
     data = lib.TextGen(4).text(n, mix=lib.MIX_STRESS)
     toff_in = lib.TextGen.lognormal_offsets(4, n)
     want, woff = oracle.encode_chunks(data, toff_in, mode=MODE_SEGMENTED, threads=NCPU)
@@ -150,6 +159,17 @@ def test_config5_lognormal_chunks(lib, merges_path, oracle):
     ids, toff, coff, _ = t.encode(data, toff_in)
     check_chunks(ids, coff, want, woff, "config5")
     assert np.array_equal(toff, coff)                     # one chunk per text
+    lens = np.diff(toff_in)
+    rng = np.random.default_rng(4)
+    picks = np.sort(np.concatenate([rng.choice(np.flatnonzero(lens <= 4096), 200, replace=False),
+                                    rng.choice(np.flatnonzero(lens > 4096), 40, replace=False),
+                                    [int(np.argmax(lens)), int(np.argmin(lens))]]))
+    blob = np.concatenate([data[toff_in[c]:toff_in[c + 1]] for c in picks])
+    boff = np.concatenate([[0], np.cumsum(lens[picks])]).astype(np.int64)
+    lit, loff = oracle.encode_chunks(blob, boff, mode=MODE_GREEDY, threads=NCPU)
+    for k, c in enumerate(picks):
+        got, exp = ids[coff[c]:coff[c + 1]], lit[loff[k]:loff[k + 1]]
+        assert np.array_equal(got, exp), f"config5 text {c} ({lens[c]} bytes): {first_mismatch(got, exp)}"
 
 
 def test_sliced_host_path_boundaries(lib, merges_path, oracle):
@@ -304,14 +324,17 @@ def test_generated_adversarial_strings(lib, merges_path, oracle):
 
 
 def test_latency_strings_one_call_each(lib, merges_path, oracle):
-    """Config 3 in miniature: independent 512-byte strings, batch size 1, every string checked."""
-    gen = lib.TextGen(2)
+    """Config 3: 10 000 independent 512-byte strings (seed 2), one call each with batch size 1, every string
+    checked against the literal rule."""
+    count = 10000
+    data = lib.TextGen(2).blocks(count, 512)
+    off = np.arange(0, count * 512 + 1, 512, dtype=np.int64)
+    want, woff = oracle.encode_chunks(data, off, mode=MODE_GREEDY, threads=NCPU)
     t = make_tok(lib, merges_path, 2048)
-    for i in range(200):
-        s = gen.blocks(1, 512, first_block=i)
-        ids, _, _, _ = t.encode(s)
-        want, _ = oracle.encode_chunks(s, np.array([0, 512]), mode=MODE_GREEDY)
-        assert np.array_equal(ids, want), f"string {i}: {first_mismatch(ids, want)}"
+    for i in range(count):
+        ids, _, coff, _ = t.encode(data[off[i]:off[i + 1]])
+        exp = want[woff[i]:woff[i + 1]]
+        assert len(coff) == 2 and np.array_equal(ids, exp), f"string {i}: {first_mismatch(ids, exp)}"
 
 
 def test_device_resident_entry_point(lib, merges_path, oracle):
@@ -485,3 +508,65 @@ def test_pybind_methods_on_gpu(lib, merges_path, oracle):
     assert lm_gpu == tok.tokenize_batch_cpu(texts[:3], merge_rule="localmin")
     ids, toff, coff, ms = tok.encode_packed(texts)
     assert ids.dtype == np.int32 and toff.dtype == np.int64 and toff[-1] == len(ids)
+
+
+def test_stage_times_of_a_sliced_batch(lib, merges_path):
+    """A host batch large enough to be cut into slices reports the stage times of all its slices: the merge
+    time must be close to the device-resident figure for the same bytes, not that of one slice."""
+    import torch
+
+    n = 96 << 20
+    data = lib.TextGen(1).text(n)
+    t = make_tok(lib, merges_path, 4096)
+    t.encode(data)
+    t.encode(data)
+    sliced = t.stage_ms()
+    d_bytes = torch.from_numpy(data).cuda()
+    d_toff = torch.tensor([0, n], dtype=torch.int64, device="cuda")
+    d_ids = torch.empty(n, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    for _ in range(2):
+        t.encode_device(d_bytes.data_ptr(), n, d_toff.data_ptr(), 1, d_ids.data_ptr(), n)
+    whole = t.stage_ms()
+    assert whole["merge"] > 0
+    assert 0.7 * whole["merge"] < sliced["merge"] < 2.5 * whole["merge"], (sliced, whole)
+    assert sliced["pipeline"] >= sliced["merge"] and sliced["pack"] > 0
+
+
+def test_two_devices_two_threads_one_process(lib, merges_path, oracle):
+    """One handle per GPU, driven from two threads of one process: a 64 MiB batch of log-normal texts is cut
+    into two byte ranges, each range is tokenised on its own device, the offsets are stitched on the host and
+    the whole equals the oracle on the unsplit batch."""
+    import threading
+
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two CUDA devices")
+    n = 64 << 20
+    data = lib.TextGen(4).text(n, mix=lib.MIX_STRESS)
+    toff_in = lib.TextGen.lognormal_offsets(4, n)
+    bounds = lib.partition_by_bytes(toff_in, 2)
+    results, errors = [None, None], []
+
+    def work(dev):
+        try:
+            lo, hi = int(bounds[dev]), int(bounds[dev + 1])
+            tok = lib.Tokenizer(merges_path, 65536, 50, device=dev)
+            part = data[toff_in[lo]:toff_in[hi]]
+            for _ in range(3):                              # repeated calls while the other thread runs too
+                ids, toff, coff, _ = tok.encode(part, toff_in[lo:hi + 1] - toff_in[lo])
+            results[dev] = (ids, coff)
+        except Exception as exc:  # noqa: BLE001
+            errors.append(exc)
+
+    threads = [threading.Thread(target=work, args=(d,)) for d in (0, 1)]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join()
+    assert not errors, errors
+    ids = np.concatenate([results[0][0], results[1][0]])
+    coff = lib.stitch_offsets([results[0][1], results[1][1]])
+    want, woff = oracle.encode_chunks(data, toff_in, mode=MODE_SEGMENTED, threads=NCPU)
+    check_chunks(ids, coff, want, woff, "two devices")
