@@ -65,7 +65,7 @@ WORKLOADS = {
     "cfg4": (3, 64 << 20, 32768, 1, False),
     "cfg5": (4, 512 << 20, 65536, 1, True),
 }
-SLICE_BYTES = 16 << 20  # slice size of the library's host path (the copy-only leg mirrors it)
+SLICE_BYTES = 24 << 20  # slice size of the library's host path (the copy-only leg mirrors it)
 
 
 def measured_hbm_peak():
@@ -661,7 +661,7 @@ def main() -> None:
             "e2e": {"value": e2e_value, "unit": "MB/s", "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_ms, "steps": args.steps,
                     "copy_ceiling": copy_ceiling, "copy_ceiling_ms": ceil_ms, "frac_of_copy_ceiling": e2e_value / copy_ceiling,
-                    "copy_ceiling_note": "the call's transfers alone (text up in 16 MiB slices, int32 ids down per "
+                    "copy_ceiling_note": "the call's transfers alone (text up in 24 MiB slices, int32 ids down per "
                                          "slice, two copy streams, no kernels), all ranks at once"},
             "gpu_launches": dev["launches"],
             "roofline": {"bound": "hbm", "kernel": "k_merge_" + args.mode, "achieved": achieved, "peak": peak,
