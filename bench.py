@@ -369,7 +369,7 @@ def e2e_run(hx: Harness, tok, pin, text_off, mode, steps):
 
 
 def copy_ceiling_run(hx: Harness, n_bytes: int, n_ids: int, steps: int):
-    """Copy-only stand-in for the host path: the same bytes up (text, 16 MiB slices) and down (int32 ids of
+    """Copy-only stand-in for the host path: the same bytes up (text, 24 MiB slices) and down (int32 ids of
     each slice) on two copy streams with the same slice-to-slice dependencies, and no kernel at all.  What
     this takes is what the host link allows for the call's transfers."""
     torch = hx.torch
