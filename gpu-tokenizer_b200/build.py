@@ -4,6 +4,8 @@
     python build.py --force    # rebuild even if up to date
 
   libgputok_b200.so   CUDA kernels + C ABI (nvcc, sm_100a only)
+  libgputok_b200_checked.so   the same built with -DGTK_CHECKED: every data-dependent index into shared
+                      memory and the work buffers is range-checked, violations are recorded and skipped
   libgtk_textgen.so   seeded synthetic text generator (gcc, CPU only)
   gputok_gpu*.so      pybind11 module exposing the reference's GpuTokenizer surface (g++)
   gpu_tokenizer_blockbpe  command-line front end with the reference binary's arguments and output (g++)
@@ -20,6 +22,7 @@ CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
 LIB = os.path.join(HERE, "libgputok_b200.so")
+LIB_CHECKED = os.path.join(HERE, "libgputok_b200_checked.so")
 TEXTGEN = os.path.join(HERE, "libgtk_textgen.so")
 PYMOD = os.path.join(HERE, "gputok_gpu" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
 CLI = os.path.join(HERE, "gpu_tokenizer_blockbpe")
@@ -51,6 +54,17 @@ def build_cuda(force: bool = False, ptxas_verbose: bool = False) -> str:
     return LIB
 
 
+def build_cuda_checked(force: bool = False) -> str:
+    """The bounds-checked build (stands in for a memory sanitizer, which this pool does not offer)."""
+    srcs = [os.path.join(CSRC, f) for f in ("gtk_kernels.cu", "gtk_api.cu", "gtk_table.cpp")]
+    deps = srcs + [os.path.join(CSRC, f) for f in ("gtk_device.cuh", "gtk_table.hpp")] + \
+        [os.path.join(INCLUDE, "gputok_b200.h")]
+    if force or _stale(LIB_CHECKED, deps):
+        nvcc = os.environ.get("NVCC", "nvcc")
+        _run([nvcc] + NVCC_FLAGS + ["-DGTK_CHECKED"] + srcs + ["-o", LIB_CHECKED])
+    return LIB_CHECKED
+
+
 def build_textgen(force: bool = False) -> str:
     src = os.path.join(CSRC, "gtk_textgen.c")
     if force or _stale(TEXTGEN, [src]):
@@ -80,6 +94,7 @@ def build_cli(force: bool = False) -> str:
 
 def build_all(force: bool = False) -> None:
     build_cuda(force)
+    build_cuda_checked(force)
     build_textgen(force)
     build_pymod(force)
     build_cli(force)

@@ -33,6 +33,28 @@ namespace {
 __device__ unsigned long long g_phase_cycles[24];
 #endif
 
+// Checked build (-DGTK_CHECKED): every index into shared memory, the lane scratch, the staging buffer and the
+// per-chunk / per-unit arrays that is computed from data is compared with its limit before it is used.  A
+// violation is recorded (first failing check, offending value, limit, number of violations) and the access is
+// skipped, so a wrong index shows up as a report, never as a fault; read the record with
+// gtk_debug_check_words.  Without the flag the checks compile to nothing.
+#ifdef GTK_CHECKED
+__device__ int g_check_words[4];
+__device__ __noinline__ bool check_failed(int id, long long value, long long limit)
+{
+  if (atomicAdd(&g_check_words[3], 1) == 0) {
+    g_check_words[0] = id;
+    g_check_words[1] = int(value);
+    g_check_words[2] = int(limit);
+  }
+  return false;
+}
+#define GTK_IN(value, limit, id) \
+  ((static_cast<unsigned long long>(value) < static_cast<unsigned long long>(limit)) || check_failed((id), (long long)(value), (long long)(limit)))
+#else
+#define GTK_IN(value, limit, id) true
+#endif
+
 constexpr uint32_t NONE = 0xFFFFu;  // pair not mergeable
 constexpr uint32_t SEL  = 0xFFFEu;  // pair selected for the current pass
 constexpr uint32_t DEAD = 0xFFFFu;  // token slot holds nothing
@@ -186,6 +208,10 @@ __device__ __forceinline__ bool thread_merge_step(uint16_t* tok_all, uint16_t* r
   uint16_t* rk  = rk_all + s;
   const int j   = int(best & 0xFFFFu);
   const int q   = j + __ffs(int(alive >> (j + 1)));  // next live slot after j (j <= 30)
+  if (!(GTK_IN(j, L - 1, 12) && GTK_IN(q - j - 1, L - j - 1, 13))) {
+    best = 0xFFFFFFFFu;
+    return false;
+  }
   const uint32_t c = P.merged_of_rank ? __ldg(P.merged_of_rank + r) : 256u + r;
   alive &= ~(1u << q);
   const uint32_t right = (q >= 31) ? 0u : (alive >> (q + 1));
@@ -443,6 +469,7 @@ __device__ int group_merge(uint16_t* tok, uint16_t* rk, int L, const DeviceTable
     int at[kMem];
     for_each_rank<NW, VEC>(rk, n, tid, pick, [&](int i) {
       const int j = next_live(tok, i, n);  // exists: the pair has a cached rank
+      if (!GTK_IN(i, n, 30)) return;
       tok[i] = uint16_t(c);
       rk[i]  = uint16_t(NONE);
       if (j < n) {
@@ -609,6 +636,7 @@ __device__ int group_merge_dense(uint16_t* tok, uint16_t* rk, int L, const Devic
       out += tot;
       gsync<NW>();
     }
+    if (!GTK_IN(out, L + 1, 29)) break;
     if (out >= len) {  // a pass must remove at least one token
       if (tid == 0 && status) atomicMax(status, int(kStatusBadSegment));
       break;
@@ -911,6 +939,7 @@ __device__ __noinline__ uint32_t thread_merge_segments(int s, int L, PairTable P
   uint16_t* tok = g_tile.tok;  // named directly so that the accesses compile to shared-memory instructions
   uint16_t* rk  = g_tile.rk;
   uint32_t alive = 0, best = 0xFFFFFFFFu;
+  if (s >= 0 && !(GTK_IN(s + L, kWindow + 1, 10) && GTK_IN(L - 2, kThreadSegMax - 1, 11))) s = -1;
   if (s >= 0) {
     alive = (L >= 32) ? 0xFFFFFFFFu : ((1u << L) - 1u);
     best  = segment_argmin(rk, s, L);
@@ -955,6 +984,11 @@ __device__ __noinline__ uint32_t thread_merge_segments(int s, int L, PairTable P
 template <int WW>
 __device__ __noinline__ uint32_t thread_merge_segments_lanes(int s, int L, PairTable P, int area, uint32_t alive)
 {
+  if (!GTK_IN(area + 32 * WW, kLaneScratchWords + 1, 14)) return alive;
+  if (s >= 0 && !(GTK_IN(s + L, kWindow + 1, 15) && GTK_IN(L - 2, 2 * WW - 1, 16))) {
+    s     = -1;
+    alive = 0;
+  }
   uint32_t* scr = lane_scratch() + area + (threadIdx.x & 31);
   uint16_t* tok = g_tile.tok + max(s, 0);
 #pragma unroll
@@ -980,6 +1014,10 @@ __device__ __noinline__ uint32_t thread_merge_segments_lanes(int s, int L, PairT
       const uint32_t r = best >> 16;
       const int j      = int(best & 0xFFFFu);
       const int q      = j + __ffs(int(alive >> (j + 1)));
+      if (!(GTK_IN(j, L - 1, 17) && GTK_IN(q - j - 1, L - j - 1, 18))) {
+        best = 0xFFFFFFFFu;
+        continue;
+      }
       const uint32_t c = P.merged_of_rank ? __ldg(P.merged_of_rank + r) : 256u + r;
       alive &= ~(1u << q);
       const uint32_t right = (q >= 31) ? 0u : (alive >> (q + 1));
@@ -1020,8 +1058,12 @@ __device__ __noinline__ uint32_t thread_merge_segments_lanes(int s, int L, PairT
 __device__ __forceinline__ int next_cut(const uint32_t* cut, int s)
 {
   int w      = (s + 1) >> 5;
+  if (!GTK_IN(w, kCutWords + 2, 1)) return kWindow;
   uint32_t x = cut[w] & (0xFFFFFFFFu << ((s + 1) & 31));
-  while (!x) x = cut[++w];
+  while (!x) {
+    if (!GTK_IN(w + 1, kCutWords + 2, 2)) return kWindow;
+    x = cut[++w];
+  }
   return w * 32 + __ffs(int(x)) - 1;
 }
 
@@ -1055,11 +1097,11 @@ __device__ __noinline__ void walk_segments(const uint4* word_slots, uint32_t wor
         S.over_start = ss;  // runs past the window: finished in the HBM workspace
       } else if (LL > kThreadSegMax) {
         const int q = atomicAdd(&S.nlong, 1);
-        if (q < kLongCap) S.longq[q] = uint16_t(ss);
+        if (q < kLongCap && GTK_IN(ss, kWindow, 3)) S.longq[q] = uint16_t(ss);
         else atomicMax(status, int(kStatusLongQueueOverflow));
       } else {
         miss = true;
-        if (LL <= 12) {
+        if (LL <= 12 && GTK_IN(ss, kWindow, 4)) {
           uint32_t k0, k1, k2;
           segment_key(S.bytes, 16 + ss, LL, k0, k1, k2);
           const uint32_t id = word_lookup(word_slots, word_shift, k0, k1, k2, uint32_t(LL));
@@ -1075,7 +1117,7 @@ __device__ __noinline__ void walk_segments(const uint4* word_slots, uint32_t wor
       int wbase = 0;
       if (lane == 0) wbase = atomicAdd(&S.nmiss, __popc(bal));
       wbase = __shfl_sync(0xFFFFFFFFu, wbase, 0);
-      if (miss) S.seg[wbase + __popc(bal & lt)] = uint16_t(ss);
+      if (miss && GTK_IN(wbase + __popc(bal & lt), kSegCap, 5)) S.seg[wbase + __popc(bal & lt)] = uint16_t(ss);
     }
   }
 }
@@ -1089,6 +1131,7 @@ __device__ __forceinline__ void mark_alive(uint32_t* cut, int s, uint32_t a)
   a &= ~1u;
   if (!a) return;
   const int sh = s & 31;
+  if (!GTK_IN((s >> 5) + 1, kCutWords + 2, 6)) return;
   atomicOr(&cut[s >> 5], a << sh);
   if (sh && (a >> (32 - sh))) atomicOr(&cut[(s >> 5) + 1], a >> (32 - sh));
 }
@@ -1096,7 +1139,7 @@ __device__ __forceinline__ void mark_alive(uint32_t* cut, int s, uint32_t a)
 // one warp: positions [lo, hi) become live
 __device__ __forceinline__ void mark_alive_range(uint32_t* cut, int lo, int hi, int lane)
 {
-  if (hi <= lo) return;
+  if (hi <= lo || !GTK_IN(hi - 1, kWindow, 7) || !GTK_IN(lo, kWindow, 7)) return;
   for (int w = (lo >> 5) + lane; w <= ((hi - 1) >> 5); w += 32) {
     uint32_t x = 0xFFFFFFFFu;
     if (w == (lo >> 5)) x &= 0xFFFFFFFFu << (lo & 31);
@@ -1220,7 +1263,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
       for (int64_t c = c0 + tid; c <= C; c += kOptThreads) {
         const int64_t p = b.chunk_off[c] - lo;
         if (p >= wlen) break;
-        if (p >= 0) {
+        if (p >= 0 && GTK_IN(p, kWindow, 28)) {
           atomicOr(&S.cut[p >> 5], 1u << (p & 31));
           if (p > 0) S.rk[p - 1] = uint16_t(NONE);
         }
@@ -1263,6 +1306,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
       if (tid < nmiss) {
         ss   = S.seg[tid];
         LL   = next_cut(S.cut, ss) - ss;
+        if (!GTK_IN(LL, 33, 8)) LL = 2;
         slot = atomicAdd(&S.hist[LL], 1);
       }
       __syncthreads();
@@ -1278,7 +1322,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
         S.hist[len] = inc - v;
       }
       __syncthreads();
-      if (tid < nmiss) S.seg[S.hist[LL] + slot] = uint16_t(ss);
+      if (tid < nmiss && GTK_IN(S.hist[LL] + slot, kSegCap, 9)) S.seg[S.hist[LL] + slot] = uint16_t(ss);
       __syncthreads();
     }
 
@@ -1360,6 +1404,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
       for (int q = warp; q < nl; q += kOptThreads / 32) {
         const int s   = S.longq[q];
         const int L   = next_cut(S.cut, s) - s;
+        if (!(GTK_IN(s, kWindow, 19) && GTK_IN(s + L, kWindow + 1, 20))) continue;
         const int len = group_merge_dense<1>(S.tok + s, S.rk + s, L, T, nullptr, status);  // ids at the front
         mark_alive_range(S.cut, s + 1, s + len, lane);
         __syncwarp();
@@ -1397,12 +1442,13 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
         const uint32_t t[4] = {tk.x & 0xFFFFu, tk.x >> 16, tk.y & 0xFFFFu, tk.y >> 16};
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          if ((nib >> k) & 1u) S.rk[d++] = uint16_t(t[k]);
+          if (((nib >> k) & 1u) && GTK_IN(d, kWindow, 21)) S.rk[d++] = uint16_t(t[k]);
       }
     }
     __syncthreads();
     const int64_t region_start = lo + ((first < kWindow) ? first : 0);
-    for (int j = tid; j < total; j += kOptThreads) b.staging[region_start + j] = S.rk[j];
+    for (int j = tid; j < total; j += kOptThreads)
+      if (GTK_IN(j, kWindow, 22) && GTK_IN(region_start + j, n, 23)) b.staging[region_start + j] = S.rk[j];
 
     GTK_PHASE(6);
     // ---- I. per-chunk token counts from the alive bitmap ----
@@ -1412,7 +1458,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
       if (c0 < C && region_end <= b.chunk_off[c0 + 1]) {
         // the owned region lies inside the chunk that holds the tile's first byte (CTA-uniform test):
         // the count is the tile's total
-        if (tid == 0 && total > 0) atomicAdd(b.chunk_cnt + c0, total);
+        if (tid == 0 && total > 0 && GTK_IN(c0, b.chunk_cap, 24)) atomicAdd(b.chunk_cnt + c0, total);
       } else
       for (int64_t c = c0 + warp; c < C; c += kOptThreads / 32) {
         const int64_t cs_g = b.chunk_off[c];
@@ -1429,7 +1475,7 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
           cnt += __popc(x);
         }
         cnt = __reduce_add_sync(0xFFFFFFFFu, cnt);
-        if (lane == 0 && cnt) atomicAdd(b.chunk_cnt + c, cnt);
+        if (lane == 0 && cnt && GTK_IN(c, b.chunk_cap, 25)) atomicAdd(b.chunk_cnt + c, cnt);
       }
     }
 
@@ -1471,8 +1517,9 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
         }
         __syncthreads();
         const int len = group_merge<kOptThreads / 32, true>(wtok, wrk, L, T, &S.gs, status);
-        for (int j = tid; j < len; j += kOptThreads) b.staging[region_start + total + j] = wtok[j];
-        if (tid == 0) {
+        for (int j = tid; j < len; j += kOptThreads)
+          if (GTK_IN(region_start + total + j, n, 26)) b.staging[region_start + total + j] = wtok[j];
+        if (tid == 0 && GTK_IN(S.over_chunk, b.chunk_cap, 27)) {
           atomicAdd(b.chunk_cnt + S.over_chunk, len);
           S.over_len = len;
         }
@@ -1651,7 +1698,8 @@ __global__ void __launch_bounds__(NW * 32) k_merge_base(EncodeBuffers b, DeviceT
     }
     __syncthreads();
     const int len = group_merge<NW, true>(tok, rk, L, T, &gs, status);
-    for (int j = tid; j < len; j += G) b.staging[cs + j] = tok[j];
+    for (int j = tid; j < len; j += G)
+      if (GTK_IN(cs + j, b.n_bytes, 31)) b.staging[cs + j] = tok[j];
     if (tid == 0) b.chunk_cnt[c] = len;
   }
 }
@@ -1919,6 +1967,35 @@ int launch_encode_small(const EncodeBuffers& b, const DeviceTable& t, cudaStream
   k_encode_small<<<1, kOptThreads, 0, stream>>>(b, t);
   return 1;
 }
+
+#ifdef GTK_CHECKED
+// Checked build only: the record of index checks that failed since the last reset ([0] id of the first failing
+// check, [1] its value, [2] its limit, [3] number of failures), plus a self-test of the mechanism: a kernel
+// evaluates one check that must fail and skips the guarded store.
+__global__ void k_check_selftest(int* sink)
+{
+  const int bad = 5 + int(threadIdx.x);
+  if (GTK_IN(bad, 4, 99)) sink[bad] = 1;
+}
+
+extern "C" __attribute__((visibility("default"))) int gtk_debug_check_words(int out[4], int reset, int selftest)
+{
+  if (selftest) {
+    int* sink = nullptr;
+    if (cudaMalloc(&sink, 64) != cudaSuccess) return -1;
+    k_check_selftest<<<1, 1>>>(sink);
+    cudaDeviceSynchronize();
+    cudaFree(sink);
+  }
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  if (cudaMemcpyFromSymbol(out, g_check_words, sizeof(int) * 4) != cudaSuccess) return -1;
+  if (reset) {
+    const int z[4] = {0, 0, 0, 0};
+    cudaMemcpyToSymbol(g_check_words, z, sizeof(z));
+  }
+  return 0;
+}
+#endif
 
 #ifdef GTK_PHASE_TIMING
 extern "C" __attribute__((visibility("default"))) void gtk_debug_phase_cycles(unsigned long long out[24], int reset)

@@ -33,7 +33,13 @@ class _TableInfo(C.Structure):
 
 
 def library_path() -> str:
-    return os.path.join(_PKG_ROOT, "libgputok_b200.so")
+    """The CUDA library beside the package; ``GPUTOK_B200_LIBRARY`` names another build of it (the
+    bounds-checked one, ``libgputok_b200_checked.so``)."""
+    return os.environ.get("GPUTOK_B200_LIBRARY") or os.path.join(_PKG_ROOT, "libgputok_b200.so")
+
+
+def checked_library_path() -> str:
+    return os.path.join(_PKG_ROOT, "libgputok_b200_checked.so")
 
 
 def load_library() -> C.CDLL:

@@ -23,6 +23,24 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box with -m gpu)")
 
 
+def pytest_sessionfinish(session, exitstatus):
+    """When the session ran on the bounds-checked build of the library (GPUTOK_B200_LIBRARY points to it),
+    report the record of failed index checks; a non-empty record fails the session."""
+    import ctypes
+
+    path = os.environ.get("GPUTOK_B200_LIBRARY")
+    if not path or not os.path.exists(path):
+        return
+    lib = ctypes.CDLL(path)
+    if not hasattr(lib, "gtk_debug_check_words"):
+        return
+    words = (ctypes.c_int * 4)()
+    rc = lib.gtk_debug_check_words(words, 0, 0)
+    print(f"\nCHECKED_BUILD rc={rc} failures={words[3]} first_check={words[0]} value={words[1]} limit={words[2]}")
+    if rc != 0 or words[3] != 0:
+        session.exitstatus = 3
+
+
 @pytest.fixture(scope="session")
 def merges_path() -> str:
     return MERGES

@@ -570,3 +570,32 @@ def test_two_devices_two_threads_one_process(lib, merges_path, oracle):
     coff = lib.stitch_offsets([results[0][1], results[1][1]])
     want, woff = oracle.encode_chunks(data, toff_in, mode=MODE_SEGMENTED, threads=NCPU)
     check_chunks(ids, coff, want, woff, "two devices")
+
+
+def test_checked_build_runs_clean(native_built):
+    """The library built with -DGTK_CHECKED (every data-dependent index into shared memory, the lane scratch,
+    the staging buffer and the count arrays is compared with its limit; a violation is recorded and the
+    access skipped) runs the golden, config-1, adversarial-segment and irregular-table tests in a process of
+    its own and must end with an empty record.  The mechanism itself is exercised first: a check that is
+    made to fail is reported with its id, value and limit, and nothing faults."""
+    import ctypes
+    import subprocess
+    import sys
+
+    from gputok_b200.capi import checked_library_path
+
+    path = checked_library_path()
+    assert os.path.exists(path), "the checked build is part of build_all()"
+    probe = ("import ctypes,sys; lib=ctypes.CDLL(sys.argv[1]); w=(ctypes.c_int*4)(); "
+             "rc=lib.gtk_debug_check_words(w,1,1); print('SELFTEST',rc,w[0],w[1],w[2],w[3]); "
+             "rc=lib.gtk_debug_check_words(w,0,0); print('AFTER_RESET',rc,w[3])")
+    out = subprocess.run([sys.executable, "-c", probe, path], capture_output=True, text=True, timeout=300)
+    assert "SELFTEST 0 99 5 4 1" in out.stdout and "AFTER_RESET 0 0" in out.stdout, out.stdout + out.stderr
+    env = dict(os.environ, GPUTOK_B200_LIBRARY=path)
+    here = os.path.dirname(os.path.abspath(__file__))
+    sel = ("golden_novel or reference_function_cases or config1 or adversarial_long_segments or "
+           "long_and_huge_segments or irregular_table or crowded_pair_bucket or random_small_batches or chunk_sizes")
+    run = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "test_gpu_parity.py"), "-m", "gpu", "-x",
+                          "-q", "-s", "-k", sel], capture_output=True, text=True, timeout=1500, env=env)
+    assert run.returncode == 0, run.stdout[-3000:] + run.stderr[-2000:]
+    assert "CHECKED_BUILD rc=0 failures=0" in run.stdout, run.stdout[-2000:]
