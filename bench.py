@@ -632,6 +632,8 @@ def main() -> None:
     extras = not args.no_extras and args.workload == "cfg2" and not args.bytes and args.mode == "opt"
     del dev["coff"]
     pin.free()
+    if world == 1 and args.workload == "cfg3" and not extras:
+        latency = latency_run(hx, MERGES, args.latency_calls)
     if extras and world == 1:
         latency = latency_run(hx, MERGES, args.latency_calls)
         configs = {}
