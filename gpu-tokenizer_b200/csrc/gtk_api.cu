@@ -130,7 +130,8 @@ struct gtk_tokenizer {
   int max_iters = 50;
   int device = -1;
   int sm_count = 0;
-  int opt_grid = 0, base_grid = 0, localmin_grid = 0;
+  int opt_grid = 0, base_grid = 0, localmin_grid = 0, wide_grid = 0;
+  bool wide = false;  // ids or ranks beyond 16 bits: every GPU mode runs the 32-bit one-CTA-per-chunk kernel
   cudaStream_t stream = nullptr;      // stream in use
   cudaStream_t own_stream = nullptr;  // created by gtk_create
   cudaEvent_t ev[6] = {};
@@ -139,7 +140,8 @@ struct gtk_tokenizer {
 
   // table in HBM
   DevBuf d_bpi;
-  DevBuf d_slots, d_overflow, d_bpr, d_mor, d_sor, d_adj, d_b2i, d_words, d_low_map;
+  DevBuf d_slots, d_overflow, d_bpr, d_mor, d_sor, d_adj, d_b2i, d_words, d_low_map, d_wide_slots;
+  DevBuf d_staging32, d_seg_scratch32;  // 32-bit kernel
   int id_space = GTK_IDS_REFERENCE;
   gtk::DeviceTable dtab{};
 
@@ -197,6 +199,7 @@ void upload_table(gtk_tokenizer* h)
   upload(h->d_b2i, t.byte_to_id, sizeof(t.byte_to_id), h->stream);
   upload(h->d_low_map, t.gpt2_low_id, sizeof(t.gpt2_low_id), h->stream);
   upload(h->d_words, t.word_slots.data(), t.word_slots.size() * sizeof(gtk::WordSlot), h->stream);
+  if (h->wide) upload(h->d_wide_slots, t.slots.data(), t.slots.size() * sizeof(gtk::HashSlot), h->stream);
   GTK_CUDA(cudaStreamSynchronize(h->stream));
   h->dtab.pair_buckets = h->d_slots.as<uint4>();
   h->dtab.pair_overflow = t.pair_overflow.empty() ? nullptr : h->d_overflow.as<uint2>();
@@ -209,6 +212,9 @@ void upload_table(gtk_tokenizer* h)
   h->dtab.byte_to_id = h->d_b2i.as<uint16_t>();
   h->dtab.word_slots = h->d_words.as<uint4>();
   h->dtab.word_log2_capacity = t.word_log2_capacity;
+  h->dtab.wide_slots = h->wide ? h->d_wide_slots.as<uint4>() : nullptr;
+  h->dtab.wide_log2 = t.log2_capacity;
+  h->dtab.wide_max_probe = t.max_probe;
   h->dtab.monotone = t.monotone ? 1 : 0;
   h->dtab.merged_is_256_plus_rank = t.merged_is_256_plus_rank ? 1 : 0;
   h->dtab.byte_ids_identity = t.byte_ids_identity ? 1 : 0;
@@ -258,7 +264,11 @@ Plan plan_batch(gtk_tokenizer* h, const uint8_t* d_bytes, int64_t n_bytes, const
   int64_t scratch_tokens = 0;
   if (longest > gtk::kHalo) scratch_tokens = (longest + 63) & ~int64_t(63);
   const int ctas = std::max(h->opt_grid, std::max(h->base_grid, h->localmin_grid));
-  if (scratch_tokens) h->d_seg_scratch.reserve(size_t(ctas) * 2 * size_t(scratch_tokens) * 2);
+  if (scratch_tokens && !h->wide) h->d_seg_scratch.reserve(size_t(ctas) * 2 * size_t(scratch_tokens) * 2);
+  if (h->wide) {
+    h->d_staging32.reserve(size_t(n_bytes + 16) * 4);
+    if (scratch_tokens) h->d_seg_scratch32.reserve(size_t(h->wide_grid) * 2 * size_t(scratch_tokens) * 4);
+  }
 
   b.bytes = d_bytes;
   b.n_bytes = n_bytes;
@@ -279,7 +289,9 @@ Plan plan_batch(gtk_tokenizer* h, const uint8_t* d_bytes, int64_t n_bytes, const
   b.text_id_off = want_text_id_off ? h->d_text_id_off.as<int64_t>() : nullptr;
   b.out_ids = d_out_ids;
   b.out_capacity = out_capacity;
-  b.seg_scratch = scratch_tokens ? h->d_seg_scratch.as<uint16_t>() : nullptr;
+  b.seg_scratch = (scratch_tokens && !h->wide) ? h->d_seg_scratch.as<uint16_t>() : nullptr;
+  b.seg_scratch32 = (scratch_tokens && h->wide) ? h->d_seg_scratch32.as<uint32_t>() : nullptr;
+  b.staging32 = h->wide ? h->d_staging32.as<int32_t>() : nullptr;
   b.seg_scratch_tokens = scratch_tokens;
   b.scan_block_sums = h->d_scan_sums.as<int64_t>();
   b.counters = h->d_counters.as<int32_t>();
@@ -311,11 +323,12 @@ void run_front(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* lau
   GTK_CUDA(cudaEventRecord(ev[0], s));
   *launches += gtk::launch_chunker(b, s);
   GTK_CUDA(cudaEventRecord(ev[1], s));
-  if (mode == GTK_MODE_BASE) *launches += gtk::launch_merge_base(b, h->dtab, h->base_grid, s);
+  if (h->wide) *launches += gtk::launch_merge_wide(b, h->dtab, h->wide_grid, s);
+  else if (mode == GTK_MODE_BASE) *launches += gtk::launch_merge_base(b, h->dtab, h->base_grid, s);
   else if (mode == GTK_MODE_LOCALMIN) *launches += gtk::launch_merge_localmin(b, h->dtab, h->localmin_grid, h->max_iters, s);
   else *launches += gtk::launch_merge_opt(b, h->dtab, h->opt_grid, s);
   GTK_CUDA(cudaEventRecord(ev[2], s));
-  *launches += gtk::launch_output_scans(b, mode != GTK_MODE_OPT, s);
+  *launches += gtk::launch_output_scans(b, mode != GTK_MODE_OPT || h->wide, s);
   GTK_CUDA(cudaEventRecord(ev[3], s));
   GTK_CUDA(cudaGetLastError());
   if (mapped_totals) {  // one small kernel writes the four words into mapped host memory: no copy-engine round trips
@@ -333,7 +346,8 @@ void run_pack(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* laun
   cudaStream_t s = on ? on : h->stream;
   if (!ev) ev = h->ev;
   GTK_CUDA(cudaEventRecord(ev[5], s));
-  *launches += gtk::launch_pack(b, mode != GTK_MODE_OPT, h->sm_count * 8, s);
+  if (h->wide) *launches += gtk::launch_pack_wide(b, h->sm_count * 8, s);
+  else *launches += gtk::launch_pack(b, mode != GTK_MODE_OPT, h->sm_count * 8, s);
   GTK_CUDA(cudaEventRecord(ev[4], s));
   GTK_CUDA(cudaGetLastError());
 }
@@ -375,6 +389,8 @@ void collect_stage_times(gtk_tokenizer* h)
 // streams.  A slice is an independent sub-batch (its pieces are texts or chunk-aligned parts of a
 // text), so the per-chunk results are exactly those of the unsliced batch.
 // ------------------------------------------------------------------------------------------------
+const char* const kWideNoLocalmin =
+    "the local-minimum mode is not offered for merge tables with ids >= 65535 or ranks >= 65534";
 constexpr int64_t kSliceThresholdBytes = int64_t(24) << 20;  // smaller batches take the single-shot path
 constexpr int64_t kSliceTargetBytes    = int64_t(24) << 20;  // measured best of 16..40 MiB on config 2 (256 MiB)
 
@@ -490,7 +506,9 @@ gtk::EncodeBuffers slice_buffers(gtk_tokenizer* h, SliceArena& a, const SlicePla
   b.out_capacity = n_bytes;
   const int64_t longest = std::min<int64_t>(h->chunk_tokens, n_bytes);
   const int64_t scratch_tokens = longest > gtk::kHalo ? ((longest + 63) & ~int64_t(63)) : 0;
-  b.seg_scratch = scratch_tokens ? h->d_seg_scratch.as<uint16_t>() : nullptr;
+  b.seg_scratch = (scratch_tokens && !h->wide) ? h->d_seg_scratch.as<uint16_t>() : nullptr;
+  b.seg_scratch32 = (scratch_tokens && h->wide) ? h->d_seg_scratch32.as<uint32_t>() : nullptr;
+  b.staging32 = h->wide ? h->d_staging32.as<int32_t>() + dev_off : nullptr;
   b.seg_scratch_tokens = scratch_tokens;
   b.scan_block_sums = a.scan_sums.as<int64_t>();
   b.counters = a.counters.as<int32_t>();
@@ -527,7 +545,11 @@ int encode_host_sliced(gtk_tokenizer* h, int mode, const uint8_t* bytes, const i
   h->d_out_ids.reserve(span * 4);
   {
     const int64_t longest = std::min<int64_t>(h->chunk_tokens, max_bytes);
-    if (longest > gtk::kHalo)
+    if (h->wide) {
+      h->d_staging32.reserve(span * 4);
+      if (longest > gtk::kHalo)
+        h->d_seg_scratch32.reserve(size_t(h->wide_grid) * 2 * size_t((longest + 63) & ~int64_t(63)) * 4);
+    } else if (longest > gtk::kHalo)
       h->d_seg_scratch.reserve(size_t(std::max(h->opt_grid, std::max(h->base_grid, h->localmin_grid))) * 2 * size_t((longest + 63) & ~int64_t(63)) * 2);
   }
   h->d_piece_off.reserve(size_t(piece_at[nsz]) * 8);
@@ -720,7 +742,7 @@ void release_handle(gtk_tokenizer* h)
   if (h->device >= 0) {
     cudaSetDevice(h->device);
     if (h->stream) cudaStreamSynchronize(h->stream);
-    for (DevBuf* b : {&h->d_bpi, &h->d_slots, &h->d_overflow, &h->d_bpr, &h->d_mor, &h->d_sor, &h->d_adj, &h->d_b2i, &h->d_words, &h->d_low_map, &h->d_bytes, &h->d_text_off,
+    for (DevBuf* b : {&h->d_bpi, &h->d_slots, &h->d_overflow, &h->d_bpr, &h->d_mor, &h->d_sor, &h->d_adj, &h->d_b2i, &h->d_words, &h->d_low_map, &h->d_wide_slots, &h->d_staging32, &h->d_seg_scratch32, &h->d_bytes, &h->d_text_off,
                       &h->d_text_chunk_base, &h->d_chunk_off, &h->d_tile_chunk0, &h->d_staging, &h->d_unit_first,
                       &h->d_unit_cnt, &h->d_chunk_cnt, &h->d_unit_base, &h->d_chunk_id_off, &h->d_text_id_off,
                       &h->d_out_ids, &h->d_seg_scratch, &h->d_scan_sums, &h->d_counters, &h->d_totals})
@@ -758,6 +780,7 @@ bool handle_view(gtk_tokenizer* h, HandleView* out)
   out->device = h->device;
   out->stream = h->stream;
   out->table = h->dtab;
+  out->wide = h->wide;
   out->low_id_map = (h->device >= 0 && h->id_space == GTK_IDS_GPT2) ? h->d_low_map.as<uint16_t>() : nullptr;
   out->pinned_words = h->device >= 0 ? h->h_totals.as<int32_t>() + 8 : nullptr;
   out->mu = &h->mu;
@@ -806,11 +829,7 @@ GTK_API int gtk_create(const char* merges_path, int chunk_tokens, int max_iters,
       return GTK_ERR_IO;
     }
     if (device >= 0) {
-      if (!h->table->fits_u16) {
-        g_global_error = "merge table has ids >= 65535 or ranks >= 65534: outside the 16-bit kernels";
-        delete h;
-        return GTK_ERR_TABLE;
-      }
+      h->wide = !h->table->fits_u16;  // ids >= 65535 or ranks >= 65534: served by the 32-bit kernel
       int count = 0;
       cudaError_t e = cudaGetDeviceCount(&count);
       if (e != cudaSuccess || device >= count) {
@@ -828,6 +847,7 @@ GTK_API int gtk_create(const char* merges_path, int chunk_tokens, int max_iters,
       h->opt_grid = h->sm_count * std::max(1, gtk::opt_kernel_max_blocks_per_sm());
       h->base_grid = h->sm_count * std::max(1, gtk::base_kernel_max_blocks_per_sm(chunk_tokens));
       h->localmin_grid = h->sm_count * std::max(1, gtk::localmin_kernel_max_blocks_per_sm());
+      h->wide_grid = h->sm_count * std::max(1, gtk::wide_kernel_max_blocks_per_sm());
       h->h_totals.reserve(64);
       small_path_init(h);
     }
@@ -895,6 +915,7 @@ GTK_API int gtk_encode_device(gtk_tokenizer* h, int mode, const uint8_t* d_bytes
   std::fill(h->stage_ms, h->stage_ms + 5, 0.f);
   if (n_texts == 0 || n_bytes == 0) return GTK_OK;
   if (!d_bytes || !d_text_offsets || !d_out_ids) return h->fail(GTK_ERR_INVALID_ARG, "null device pointer");
+  if (h->wide && mode == GTK_MODE_LOCALMIN) return h->fail(GTK_ERR_TABLE, kWideNoLocalmin);
   try {
     GTK_CUDA(cudaSetDevice(h->device));
     const int64_t need_chunks = chunk_upper_bound(n_bytes, n_texts, h->chunk_tokens);
@@ -967,7 +988,8 @@ GTK_API int gtk_encode(gtk_tokenizer* h, int mode, const uint8_t* bytes, const i
       return GTK_OK;
     }
     if (!bytes) return h->fail(GTK_ERR_INVALID_ARG, "bytes is null");
-    if (mode == GTK_MODE_OPT && n_bytes <= gtk::kSmallMaxBytes && n_texts <= gtk::kSmallMaxTexts)
+    if (h->wide && mode == GTK_MODE_LOCALMIN) return h->fail(GTK_ERR_TABLE, kWideNoLocalmin);
+    if (!h->wide && mode == GTK_MODE_OPT && n_bytes <= gtk::kSmallMaxBytes && n_texts <= gtk::kSmallMaxTexts)
       return encode_host_small(h, bytes, text_offsets, n_texts, n_bytes, kernel_ms);
     if (n_bytes >= kSliceThresholdBytes) return encode_host_sliced(h, mode, bytes, text_offsets, n_texts, n_bytes, kernel_ms);
     cudaStream_t s = h->stream;

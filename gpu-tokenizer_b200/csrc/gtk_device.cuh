@@ -35,6 +35,9 @@ struct DeviceTable {
   const uint16_t* byte_to_id;      // [256]
   const uint4* word_slots;         // WordSlot[word capacity]: {k0, k1, k2, length << 16 | id}, two-choice cuckoo
   uint32_t word_log2_capacity;
+  const uint4* wide_slots;         // tables beyond 16 bits: HashSlot[1 << wide_log2] {right, left, rank, merged id}
+  uint32_t wide_log2;
+  uint32_t wide_max_probe;         // longest displacement of a stored key
   int monotone;
   int merged_is_256_plus_rank;
   int byte_ids_identity;
@@ -76,6 +79,8 @@ struct EncodeBuffers {
   int64_t out_capacity;
   // scratch
   uint16_t* seg_scratch;     // per-CTA workspace for segments that do not fit in shared memory
+  uint32_t* seg_scratch32;   // the same for the 32-bit kernel (tables beyond 16 bits)
+  int32_t* staging32;        // [n_bytes] 32-bit kernel: tokens of a chunk, compacted at the chunk's first byte
   int64_t seg_scratch_tokens;  // tokens per CTA (two arrays of this length per CTA)
   int64_t* scan_block_sums;  // workspace of the multi-block scan
   int32_t* counters;         // [0] tile ticket, [1] status word, [2] base-mode chunk ticket
@@ -86,6 +91,9 @@ struct EncodeBuffers {
 int launch_chunker(const EncodeBuffers& b, cudaStream_t stream);
 int launch_merge_opt(const EncodeBuffers& b, const DeviceTable& t, int grid, cudaStream_t stream);
 int launch_merge_base(const EncodeBuffers& b, const DeviceTable& t, int grid, cudaStream_t stream);
+int launch_merge_wide(const EncodeBuffers& b, const DeviceTable& t, int grid, cudaStream_t stream);
+int launch_pack_wide(const EncodeBuffers& b, int grid, cudaStream_t stream);
+int wide_kernel_max_blocks_per_sm();
 int launch_merge_localmin(const EncodeBuffers& b, const DeviceTable& t, int grid, int max_iters, cudaStream_t stream);
 int launch_output_scans(const EncodeBuffers& b, int mode_base, cudaStream_t stream);
 int launch_pack(const EncodeBuffers& b, int mode_base, int grid, cudaStream_t stream);
@@ -101,6 +109,7 @@ struct HandleView {
   cudaStream_t stream;
   DeviceTable table;
   const uint16_t* low_id_map;  // nullptr, or the 256-entry remap of ids < 256 (GPT-2 id space selected)
+  bool wide;                   // table beyond 16 bits (the allocation-free kernel is 16-bit only)
   int32_t* pinned_words;  // 8 ints of page-locked host memory owned by the handle
   std::mutex* mu;
   std::string* last_error;

@@ -121,6 +121,29 @@ __device__ __forceinline__ uint32_t probe_rank(const DeviceTable& T, uint32_t le
   return resolve_rank(v, key, T.pair_overflow, T.pair_overflow_mask);
 }
 
+// Tables whose ids or ranks do not fit 16 bits are served from the 16-byte-slot open-addressing table
+// ({right, left, rank, merged id}, linear probing, empty = all ones): rank of the pair, 0xFFFFFFFF if none.
+__device__ __forceinline__ uint32_t probe_rank_wide(const DeviceTable& T, uint32_t left, uint32_t right)
+{
+  const uint32_t mask = (1u << T.wide_log2) - 1u;
+  uint32_t h = (((left << 16) ^ right) * 0x9E3779B1u) >> (32u - T.wide_log2);
+  for (uint32_t d = 0; d <= T.wide_max_probe; ++d) {
+    const uint4 v = __ldg(T.wide_slots + h);
+    if (v.x == right && v.y == left) return v.z;
+    if ((v.x & v.y) == 0xFFFFFFFFu) return 0xFFFFFFFFu;
+    h = (h + 1u) & mask;
+  }
+  return 0xFFFFFFFFu;
+}
+
+// rank of a pair in the marker convention of the element type (16-bit: 0xFFFF = none, 32-bit: all ones = none)
+template <typename TT>
+__device__ __forceinline__ uint32_t probe_rank_t(const DeviceTable& T, uint32_t left, uint32_t right)
+{
+  if (sizeof(TT) == 2) return probe_rank(T, left, right);
+  return probe_rank_wide(T, left, right);
+}
+
 // Whole-segment table: id of the vocabulary string (k0,k1,k2 = bytes zero padded, L = length)
 // if the greedy rule turns exactly that string into one token, else 0xFFFFFFFF.  Two-choice cuckoo
 // table: both candidate slots are loaded at once.
@@ -537,12 +560,14 @@ __device__ int group_merge(uint16_t* tok, uint16_t* rk, int L, const DeviceTable
 // The same merge with a compaction in every pass: cheaper for the short sequences a single warp handles
 // inside a tile (a few dozen to a few hundred tokens), where a sweep costs little and the tombstone searches of
 // the lazy variant do not pay.
-template <int NW>
-__device__ int group_merge_dense(uint16_t* tok, uint16_t* rk, int L, const DeviceTable& T, GroupScratch* gs,
+template <int NW, typename TT>
+__device__ int group_merge_dense(TT* tok, TT* rk, int L, const DeviceTable& T, GroupScratch* gs,
                            int* status)
 {
   constexpr int G = NW * 32;
   constexpr int E = 4;
+  // markers in the element type: all ones = no rank / tombstone, all ones minus one = selected
+  constexpr uint32_t kNone = uint32_t(TT(~TT(0))), kSel = kNone - 1u, kDead = kNone;
   const int lane  = threadIdx.x & 31;
   const int warp  = (NW == 1) ? 0 : (threadIdx.x >> 5);
   const int tid   = (NW == 1) ? lane : int(threadIdx.x);
@@ -551,10 +576,10 @@ __device__ int group_merge_dense(uint16_t* tok, uint16_t* rk, int L, const Devic
   int len    = L;
   for (int pass = 0; pass < L && len >= 2; ++pass) {
     // (1) lowest cached rank
-    uint32_t m = NONE;
+    uint32_t m = kNone;
     for (int i = tid; i < len - 1; i += G) m = min(m, uint32_t(rk[i]));
     m = group_min<NW>(m, gs, parity, lane, warp);
-    if (m >= SEL) break;
+    if (m >= kSel) break;
     const uint32_t r = m;
     const uint32_t c = merged_id(T, r);
     const bool batch = T.monotone != 0;
@@ -566,7 +591,7 @@ __device__ int group_merge_dense(uint16_t* tok, uint16_t* rk, int L, const Devic
         if (rk[i] == r) { p = uint32_t(i); break; }
       p = group_min<NW>(p, gs, parity, lane, warp);
       gsync<NW>();
-      if (tid == 0) rk[p] = uint16_t(SEL);
+      if (tid == 0) rk[p] = TT(kSel);
       gsync<NW>();
     } else if (same) {
       // occurrences of (a,a) overlap inside a run a a a ...; left to right
@@ -575,39 +600,39 @@ __device__ int group_merge_dense(uint16_t* tok, uint16_t* rk, int L, const Devic
         if (rk[i] != r) continue;
         if (i > 0) {
           const uint32_t pv = rk[i - 1];
-          if (pv == r || pv == SEL) continue;  // not the first match of its run
+          if (pv == r || pv == kSel) continue;  // not the first match of its run
         }
         int j = i;
         for (;;) {
-          rk[j] = uint16_t(SEL);
+          rk[j] = TT(kSel);
           if (j + 2 < len - 1 && rk[j + 1] == r && rk[j + 2] == r) j += 2;
           else break;
         }
       }
       gsync<NW>();
     }
-    const uint32_t pick = (!batch || same) ? SEL : r;
+    const uint32_t pick = (!batch || same) ? kSel : r;
     // (3) apply
     for (int i = tid; i < len - 1; i += G) {
       if (rk[i] == pick) {
-        tok[i]     = uint16_t(c);
-        tok[i + 1] = uint16_t(DEAD);
+        tok[i]     = TT(c);
+        tok[i + 1] = TT(kDead);
       }
     }
     gsync<NW>();
     // (4) in-place compaction, batch by batch, registers as the second buffer
     int out = 0;
     for (int base = 0; base < len; base += G * E) {
-      uint16_t t[E], q[E];
+      TT t[E], q[E];
       uint32_t bal[E];
       int wt = 0;
 #pragma unroll
       for (int k = 0; k < E; ++k) {
         const int i = base + warp * 32 * E + k * 32 + lane;
         const bool v = i < len;
-        t[k]   = v ? tok[i] : uint16_t(DEAD);
-        q[k]   = v ? rk[i] : uint16_t(NONE);
-        bal[k] = __ballot_sync(0xFFFFFFFFu, t[k] != DEAD);
+        t[k]   = v ? tok[i] : TT(kDead);
+        q[k]   = v ? rk[i] : TT(kNone);
+        bal[k] = __ballot_sync(0xFFFFFFFFu, t[k] != kDead);
         wt += __popc(bal[k]);
       }
       int pre = 0, tot = wt;
@@ -626,7 +651,7 @@ __device__ int group_merge_dense(uint16_t* tok, uint16_t* rk, int L, const Devic
       int o = out + pre;
 #pragma unroll
       for (int k = 0; k < E; ++k) {
-        if (t[k] != DEAD) {
+        if (t[k] != kDead) {
           const int d = o + __popc(bal[k] & lt);
           tok[d] = t[k];
           rk[d]  = q[k];
@@ -645,8 +670,8 @@ __device__ int group_merge_dense(uint16_t* tok, uint16_t* rk, int L, const Devic
     // (5) refresh ranks next to new tokens
     for (int d = tid; d < len; d += G) {
       if (tok[d] == c) {
-        rk[d] = uint16_t((d + 1 < len) ? probe_rank(T, c, tok[d + 1]) : NONE);
-        if (d > 0) rk[d - 1] = uint16_t(probe_rank(T, tok[d - 1], c));
+        rk[d] = TT((d + 1 < len) ? probe_rank_t<TT>(T, c, tok[d + 1]) : kNone);
+        if (d > 0) rk[d - 1] = TT(probe_rank_t<TT>(T, tok[d - 1], c));
       }
     }
     gsync<NW>();
@@ -1705,6 +1730,79 @@ __global__ void __launch_bounds__(NW * 32) k_merge_base(EncodeBuffers b, DeviceT
 }
 
 // ------------------------------------------------------------------------------------------------
+// Merge tables whose ids or ranks do not fit 16 bits (beyond roughly 65 000 merges): one CTA per chunk, 32-bit
+// tokens and ranks (shared memory up to kWideSmemTokens tokens, else the HBM workspace), the pass-by-pass
+// merge with a compaction in every pass, probes into the 16-byte-slot table.  The reference carries int32
+// ids and a 64-bit pair key and so accepts any merges file (gputok_blockbpe.cu:139-157); this kernel keeps
+// that property for the GPU entry points at the speed of the literal design.
+// ------------------------------------------------------------------------------------------------
+constexpr int kWideThreads    = 256;
+constexpr int kWideSmemTokens = 4096;
+
+__global__ void __launch_bounds__(kWideThreads) k_merge_wide(EncodeBuffers b, DeviceTable T)
+{
+  __shared__ __align__(16) uint32_t s_tok[kWideSmemTokens];
+  __shared__ __align__(16) uint32_t s_rk[kWideSmemTokens];
+  __shared__ GroupScratch gs;
+  __shared__ int ticket;
+  const int tid   = threadIdx.x;
+  const int64_t C = b.totals[0];
+  int* status     = b.counters + 1;
+  for (;;) {
+    __syncthreads();
+    if (tid == 0) ticket = atomicAdd(b.counters + 2, 1);
+    __syncthreads();
+    const int64_t c = ticket;
+    if (c >= C) break;
+    const int64_t cs  = b.chunk_off[c];
+    const int64_t L64 = b.chunk_off[c + 1] - cs;
+    uint32_t *tok = s_tok, *rk = s_rk;
+    if (L64 > kWideSmemTokens) {
+      if (L64 > b.seg_scratch_tokens || b.seg_scratch32 == nullptr) {
+        if (tid == 0) {
+          atomicMax(status, int(kStatusScratchTooSmall));
+          b.chunk_cnt[c] = 0;
+        }
+        continue;
+      }
+      tok = b.seg_scratch32 + int64_t(blockIdx.x) * 2 * b.seg_scratch_tokens;
+      rk  = tok + b.seg_scratch_tokens;
+    }
+    const int L = int(L64);
+    for (int i = tid; i < L; i += kWideThreads) {
+      const uint32_t cur = __ldg(T.byte_to_id + b.bytes[cs + i]);
+      tok[i] = cur;
+      rk[i]  = (i + 1 < L) ? probe_rank_wide(T, cur, __ldg(T.byte_to_id + b.bytes[cs + i + 1])) : 0xFFFFFFFFu;
+    }
+    __syncthreads();
+    const int len = group_merge_dense<kWideThreads / 32>(tok, rk, L, T, &gs, status);
+    for (int j = tid; j < len; j += kWideThreads) b.staging32[cs + j] = int32_t(tok[j]);
+    if (tid == 0) b.chunk_cnt[c] = len;
+  }
+}
+
+// packs the staged 32-bit tokens of every chunk (one warp per chunk)
+__global__ void __launch_bounds__(256) k_pack_wide(const int32_t* __restrict__ staging, const int64_t* __restrict__ first,
+                                                   const int32_t* __restrict__ cnt, const int64_t* __restrict__ base,
+                                                   const int64_t* n_units_ptr, int32_t* __restrict__ out,
+                                                   int64_t capacity, const uint16_t* __restrict__ low_id_map)
+{
+  const int64_t U    = *n_units_ptr;
+  const int lane     = threadIdx.x & 31;
+  const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nw   = (int64_t(gridDim.x) * blockDim.x) >> 5;
+  for (int64_t u = warp; u < U; u += nw) {
+    const int64_t src = first[u], dst = base[u];
+    int64_t m = cnt[u];
+    if (dst + m > capacity) m = capacity > dst ? capacity - dst : 0;
+    for (int64_t j = lane; j < m; j += 32) {
+      const uint32_t t = uint32_t(staging[src + j]);
+      out[dst + j] = int32_t((low_id_map && t < 256u) ? uint32_t(__ldg(low_id_map + t)) : t);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // local-minimum rule, one CTA per chunk (GTK_MODE_LOCALMIN).  The reference's tokenize_batch runs
 // this rule, not Algorithm 1 (bpe_merge_kernel_optimized, gputok_binding.cu:290-414): per pass
 // every adjacent pair gets its rank; a mergeable pair is merged unless its left neighbour ranks
@@ -1920,6 +2018,30 @@ int launch_merge_base(const EncodeBuffers& b, const DeviceTable& t, int grid, cu
     default: k_merge_base<32><<<grid, 1024, bytes, stream>>>(b, t, st); break;
   }
   return 1;
+}
+
+int launch_merge_wide(const EncodeBuffers& b, const DeviceTable& t, int grid, cudaStream_t stream)
+{
+  if (b.n_bytes <= 0) return 0;
+  if (grid > b.chunk_cap) grid = int(b.chunk_cap);
+  if (grid < 1) grid = 1;
+  k_merge_wide<<<grid, kWideThreads, 0, stream>>>(b, t);
+  return 1;
+}
+
+int launch_pack_wide(const EncodeBuffers& b, int grid, cudaStream_t stream)
+{
+  if (b.n_bytes <= 0) return 0;
+  k_pack_wide<<<grid, 256, 0, stream>>>(b.staging32, b.chunk_off, b.chunk_cnt, b.chunk_id_off, b.totals + 0, b.out_ids,
+                                        b.out_capacity, b.low_id_map);
+  return 1;
+}
+
+int wide_kernel_max_blocks_per_sm()
+{
+  int nb = 0;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, k_merge_wide, kWideThreads, 0);
+  return nb;
 }
 
 int launch_merge_localmin(const EncodeBuffers& b, const DeviceTable& t, int grid, int max_iters, cudaStream_t stream)
@@ -2164,6 +2286,7 @@ extern "C" GTK_API int gtk_encode_chunks_noalloc(gtk_tokenizer* h, const uint8_t
     return code;
   };
   if (v.device < 0) return fail(GTK_ERR_NO_DEVICE, "host-only handle: no GPU entry points");
+  if (v.wide) return fail(GTK_ERR_TABLE, "the allocation-free entry point serves merge tables with ids < 65535 and ranks < 65534 only");
   if (v.device >= kMaxDevices) return fail(GTK_ERR_INVALID_ARG, "device ordinal beyond the supported range");
   if (n_chunks < 0 || n_bytes < 0 || max_chunk_bytes <= 0) return fail(GTK_ERR_INVALID_ARG, "negative or zero size");
   if (n_chunks > int64_t(0x7FFFFFF0)) return fail(GTK_ERR_INVALID_ARG, "more than 2^31 chunks in one call");

@@ -47,7 +47,7 @@ enum {
   GTK_ERR_IO           = 2, /* merges file unreadable or empty (std::runtime_error, :153-161) */
   GTK_ERR_CUDA         = 3, /* a CUDA runtime call failed (the reference prints and exit()s, :24-30) */
   GTK_ERR_CAPACITY     = 4, /* a caller-provided output buffer is too small */
-  GTK_ERR_TABLE        = 5, /* merge table outside what the 16-bit kernels support */
+  GTK_ERR_TABLE        = 5, /* the entry point does not serve this merge table (see gtk_create) */
   GTK_ERR_NO_DEVICE    = 6, /* GPU entry point called on a host-only handle */
   GTK_ERR_KERNEL       = 7  /* a kernel reported an internal inconsistency through its status word */
 };
@@ -100,7 +100,13 @@ GTK_API const char* gtk_global_error(void);
  * never-merge bigram bitmap and uploads them to `device`.
  * chunk_tokens <= 0 -> GTK_ERR_INVALID_ARG; max_iters <= 0 -> 50 (as :664-666).
  * device == -1 builds a host-only handle: the GPU entry points then return
- * GTK_ERR_NO_DEVICE (there is no CPU fallback); gtk_encode_cpu still works. */
+ * GTK_ERR_NO_DEVICE (there is no CPU fallback); gtk_encode_cpu still works.
+ * Any merges file the reference accepts is accepted (it carries int32 ids and a 64-bit pair key,
+ * gputok_blockbpe.cu:139-157).  The fast kernels hold ids and ranks in 16 bits; a table with ids
+ * >= 65535 or ranks >= 65534 (beyond roughly 65 000 merges; GPT-2 has 50 000) is served, for both
+ * GTK_MODE_OPT and GTK_MODE_BASE, by a 32-bit one-CTA-per-chunk kernel with the same results at
+ * the speed of the literal design.  For such a table GTK_MODE_LOCALMIN and
+ * gtk_encode_chunks_noalloc return GTK_ERR_TABLE. */
 GTK_API int gtk_create(const char* merges_path, int chunk_tokens, int max_iters, int device,
                        gtk_tokenizer** out);
 

@@ -147,3 +147,38 @@ def irregular_merges(merges_path: str, out_path: str, n_lines: int = 4000, seed:
         body.insert(at, body[int(rng.integers(0, at))])
     with open(out_path, "w", encoding="utf-8") as f:
         f.write("\n".join([head] + body) + "\n")
+
+
+def wide_merges(merges_path: str, out_path: str, oracle, text: bytes, extra: int = 16000):
+    """A merges file too large for 16-bit ids: GPT-2's 50 000 merges followed by ``extra`` new ones, the most
+    frequent adjacent token pairs of ``text`` under the GPT-2 table (so the new, high-ranked merges really
+    fire on that text and produce ids above 65 535).  Returns the number of merges written."""
+    from collections import Counter
+
+    from oracle.loader import MODE_SEGMENTED
+
+    ids, off = oracle.encode_fixed(text, 1 << 16, mode=MODE_SEGMENTED, threads=os.cpu_count() or 1)
+    pairs = Counter()
+    for c in range(len(off) - 1):
+        a = ids[off[c]:off[c + 1]]
+        pairs.update(zip(a[:-1].tolist(), a[1:].tolist()))
+    with open(merges_path, encoding="utf-8") as f:
+        lines = f.read().split("\n")
+    while lines and not lines[-1]:
+        lines.pop()
+    have = set(lines[1:])
+    new = []
+    for (l, r), _ in pairs.most_common():
+        sl = oracle.token_symbols(l).decode("utf-8")
+        sr = oracle.token_symbols(r).decode("utf-8")
+        line = f"{sl} {sr}"
+        if " " in sl or " " in sr or not sl or not sr or line in have:
+            continue
+        new.append(line)
+        have.add(line)
+        if len(new) >= extra:
+            break
+    lines += new[::-1]  # rarest first: the most frequent pairs get the highest ranks and ids
+    with open(out_path, "w", encoding="utf-8") as f:
+        f.write("\n".join(lines) + "\n")
+    return len(lines) - 1

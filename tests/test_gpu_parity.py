@@ -11,7 +11,7 @@ import os
 import numpy as np
 import pytest
 
-from conftest import first_mismatch, fixed_chunk_offsets
+from conftest import first_mismatch, fixed_chunk_offsets, wide_merges
 from oracle.loader import MODE_GREEDY, MODE_SEGMENTED
 
 pytestmark = pytest.mark.gpu
@@ -599,3 +599,53 @@ def test_checked_build_runs_clean(native_built):
                           "-q", "-s", "-k", sel], capture_output=True, text=True, timeout=1500, env=env)
     assert run.returncode == 0, run.stdout[-3000:] + run.stderr[-2000:]
     assert "CHECKED_BUILD rc=0 failures=0" in run.stdout, run.stdout[-2000:]
+
+
+def test_merge_table_beyond_16_bits(lib, merges_path, oracle, novel, tmp_path):
+    """A merges file with 66 000 merges (ids and ranks beyond 16 bits): the reference accepts any file, and so do
+    the GPU entry points -- both modes run the 32-bit kernel and must equal the literal rule under that table,
+    on the sample novel, on a batch large enough for the sliced host path, and in the device-resident call."""
+    import torch
+    from oracle.loader import Oracle
+
+    path = str(tmp_path / "wide_merges.txt")
+    n_merges = wide_merges(merges_path, path, oracle, novel)
+    assert n_merges >= 65600
+    wide = Oracle(path)
+    t = lib.Tokenizer(path, 2048, 50, device=0)
+    info = t.table_info()
+    assert info["num_merges"] == n_merges and info["max_rank"] >= 65534
+    want, woff = wide.encode_fixed(novel, 2048, mode=MODE_GREEDY, threads=NCPU)
+    assert want.max() > 65535                              # the new merges really fire
+    for m in (lib.GTK_MODE_OPT, lib.GTK_MODE_BASE):
+        ids, _, coff, _ = t.encode(novel, mode=m)
+        check_chunks(ids, coff, want, woff, f"wide table, novel, mode {m}")
+    assert t.decode(ids) == novel
+    for piece in (novel[:300], b"", b"a"):                 # tiny batches take the same kernel
+        ids, _, coff, _ = t.encode(piece)
+        w2, _ = wide.encode_fixed(piece, 2048, mode=MODE_GREEDY)
+        assert np.array_equal(ids, w2)
+    # 26 MiB: the sliced host path; ragged texts; 32 KiB chunks use the kernel's HBM workspace
+    data = np.concatenate([np.frombuffer(novel, np.uint8)] * 4 + [lib.TextGen(3).text(23 << 20, mix=lib.MIX_STRESS)])
+    toff = np.array([0, 1000, 1000, len(novel) * 4 + 77, len(data)], dtype=np.int64)
+    t32 = lib.Tokenizer(path, 32768, 50, device=0)
+    chunk_off = [0]
+    for s0, e0 in zip(toff[:-1], toff[1:]):
+        chunk_off.extend(list(range(int(s0) + 32768, int(e0), 32768)) + ([int(e0)] if e0 > s0 else []))
+    want, woff = wide.encode_chunks(data, np.array(chunk_off, np.int64), mode=MODE_SEGMENTED, threads=NCPU)
+    ids, toff_out, coff, _ = t32.encode(data, toff)
+    check_chunks(ids, coff, want, woff, "wide table, sliced batch")
+    assert toff_out[2] == toff_out[1] and toff_out[-1] == len(ids)
+    d_bytes = torch.from_numpy(data[:4 << 20].copy()).cuda()
+    d_toff = torch.tensor([0, 4 << 20], dtype=torch.int64, device="cuda")
+    d_ids = torch.empty(4 << 20, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    n_ids, n_chunks, _ = t32.encode_device(d_bytes.data_ptr(), 4 << 20, d_toff.data_ptr(), 1, d_ids.data_ptr(), 4 << 20)
+    w3, _ = wide.encode_fixed(data[:4 << 20], 32768, mode=MODE_SEGMENTED, threads=NCPU)
+    assert n_ids == len(w3) and np.array_equal(d_ids[:n_ids].cpu().numpy(), w3)
+    for call in (lambda: t.encode(novel, mode=lib.GTK_MODE_LOCALMIN),
+                 lambda: t.encode_chunks_noalloc(d_bytes.data_ptr(), 4096, d_toff.data_ptr(), 1, 4096, d_ids.data_ptr(),
+                                                 d_ids.data_ptr())):
+        with pytest.raises(lib.GtkError) as e:
+            call()
+        assert e.value.code == 5

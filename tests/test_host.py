@@ -309,3 +309,22 @@ def test_two_rank_sharding_over_gloo(native_built, merges_path, oracle, tmp_path
     outs = [p.communicate(timeout=240)[0] for p in procs]
     assert all(p.returncode == 0 for p in procs), outs
     assert "SHARDS_OK" in outs[0]
+
+
+def test_host_table_beyond_16_bits(native_built, merges_path, oracle, novel, tmp_path):
+    """A merges file with more than 65 534 merges builds (the reference accepts any file); the host tokenizer
+    equals the oracle under that table and the new, high ids really occur."""
+    import gputok_b200
+    from conftest import wide_merges
+    from oracle.loader import MODE_GREEDY, Oracle
+
+    path = str(tmp_path / "wide_merges.txt")
+    n = wide_merges(merges_path, path, oracle, novel[:200000], extra=16000)
+    assert n > 65534
+    tok = gputok_b200.Tokenizer(path, 1024, 50, device=-1)
+    assert tok.table_info()["num_merges"] == n
+    part = novel[:60000]
+    ids, _, coff = tok.encode_cpu(part)
+    want, woff = Oracle(path).encode_fixed(part, 1024, mode=MODE_GREEDY, threads=4)
+    assert np.array_equal(ids, want) and np.array_equal(coff, woff)
+    assert ids.max() > 65535
