@@ -593,9 +593,27 @@ __device__ int group_merge_dense(TT* tok, TT* rk, int L, const DeviceTable& T, G
       gsync<NW>();
       if (tid == 0) rk[p] = TT(kSel);
       gsync<NW>();
+    } else if (same && NW == 1) {
+      // occurrences of (a,a) overlap inside a run a a a ...; left to right selection keeps the even offsets of
+      // every maximal run of matches.  One warp, 32 slots per round: a ballot gives the matches, the distance of a
+      // match to the start of its run is the distance to the nearest non-match below it (the run may reach back
+      // into earlier rounds: `before` carries the parity of the matches that directly precede this round)
+      uint32_t before = 0;
+      for (int base = 0; base < len - 1; base += 32) {
+        const int i       = base + lane;
+        const bool match  = (i < len - 1) && (rk[i] == r);
+        const uint32_t mm = __ballot_sync(0xFFFFFFFFu, match);
+        if (match) {
+          const uint32_t gaps = ~mm & lt;  // non-matches below this lane
+          const uint32_t off  = gaps ? uint32_t(lane) - (32u - uint32_t(__clz(int(gaps)))) : uint32_t(lane) + before;
+          if ((off & 1u) == 0u) rk[i] = TT(kSel);
+        }
+        const uint32_t tail = uint32_t(__clz(int(~mm)));  // matches at the top of this round
+        before = (tail == 32u) ? ((before + 32u) & 1u) : (tail & 1u);
+      }
+      __syncwarp();
     } else if (same) {
-      // occurrences of (a,a) overlap inside a run a a a ...; left to right
-      // selection keeps the even offsets of every maximal run of matches
+      // the same selection for a CTA-wide group: the first match of every run walks its run
       for (int i = tid; i < len - 1; i += G) {
         if (rk[i] != r) continue;
         if (i > 0) {
