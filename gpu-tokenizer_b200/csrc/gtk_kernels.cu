@@ -13,14 +13,22 @@
 //                role as the fast entry point, gputok_binding.cu:704-846, with
 //                the greedy rule of gputok_blockbpe.cu:248-300)
 //   merge (base) one CTA per chunk runs Algorithm 1 pass by pass on the whole
-//                chunk (replaces bpe_merge_kernel_blockbpe,
-//                gputok_blockbpe.cu:328-538)
+//                chunk, held in dynamic shared memory sized by the chunk length
+//                (replaces bpe_merge_kernel_blockbpe, gputok_blockbpe.cu:328-538)
+//   merge (wide) the same for merge tables whose ids or ranks need more than
+//                16 bits: 32-bit tokens and ranks, 16-byte-slot pair table
+//   local-min    the reference's other rule (bpe_merge_kernel_optimized,
+//                gputok_binding.cu:290-414), one CTA per chunk
+//   small        chunker, tiles, scans and pack of a small batch in one
+//                single-CTA launch (latency mode)
 //   output       exclusive scans over per-unit and per-chunk token counts and
 //                a pack kernel that writes int32 ids back to back (replaces
 //                the padded D2H + host unflatten, gputok_binding.cu:807-836)
 //
 // Nothing here is a dense contraction: the kernels are integer/byte work bound
 // by shared-memory and issue throughput, so there is no tensor-core code.
+// Kernels report trouble through a status word and never trap; every loop is
+// bounded.  -DGTK_CHECKED adds range checks on every data-dependent index.
 #include "gtk_device.cuh"
 
 #include <algorithm>
@@ -294,10 +302,12 @@ __device__ __forceinline__ bool thread_merge_step(uint16_t* tok_all, uint16_t* r
 // over consecutive passes because no merge at the minimum rank can expose a
 // lower rank.  Otherwise only the left-most occurrence is merged.
 // ------------------------------------------------------------------------------------------------
+constexpr int kMergeList = 64;  // merges of one pass that are re-probed from a list; more fall back to a sweep
 struct GroupScratch {
   uint32_t red[2][32];
   uint32_t wsum[32];
   int dead;  // tombstones since the last compaction (CTA-wide groups)
+  int list[kMergeList];  // slots merged in the current pass (CTA-wide groups)
 };
 
 template <int NW>
@@ -487,7 +497,9 @@ __device__ int group_merge(uint16_t* tok, uint16_t* rk, int L, const DeviceTable
       gsync<NW>();
     }
     const uint32_t pick = (!batch || same) ? SEL : r;
-    // (3) apply: the selected occurrences never share a slot, so the writes are disjoint
+    // (3) apply: the selected occurrences never share a slot, so the writes are disjoint.  A CTA-wide group
+    // collects the merged slots in a shared list (the tombstone counter hands out the places), a single warp
+    // keeps them in registers
     int mine = 0;
     int at[kMem];
     for_each_rank<NW, VEC>(rk, n, tid, pick, [&](int i) {
@@ -499,31 +511,16 @@ __device__ int group_merge(uint16_t* tok, uint16_t* rk, int L, const DeviceTable
         tok[j] = uint16_t(DEAD);
         rk[j]  = uint16_t(NONE);
       }
+      if (NW > 1) {
+        const int place = atomicAdd(&gs->dead, 1) - dead;
+        if (place < kMergeList) gs->list[place] = i;
+      } else {
 #pragma unroll
-      for (int k = 0; k < kMem; ++k)
-        if (mine == k) at[k] = i;
-      ++mine;
+        for (int k = 0; k < kMem; ++k)
+          if (mine == k) at[k] = i;
+        ++mine;
+      }
     });
-    bool sweep;
-    if (NW > 1) {
-      const int wsum = __reduce_add_sync(0xFFFFFFFFu, mine);
-      if (lane == 0 && wsum) atomicAdd(&gs->dead, wsum);
-      sweep = __syncthreads_or(mine > kMem) != 0;
-      const int now = gs->dead;
-      if (now == dead) {  // a pass must remove at least one token
-        if (tid == 0 && status) atomicMax(status, int(kStatusBadSegment));
-        break;
-      }
-      dead = now;
-    } else {
-      const int wsum = __reduce_add_sync(0xFFFFFFFFu, mine);
-      sweep          = __any_sync(0xFFFFFFFFu, mine > kMem) != 0;
-      if (wsum == 0) {
-        if (tid == 0 && status) atomicMax(status, int(kStatusBadSegment));
-        break;
-      }
-      dead += wsum;
-    }
     // (4) ranks of the two pairs next to every new token
     auto refresh = [&](int i) {
       const int jn = next_live(tok, i, n);
@@ -531,13 +528,37 @@ __device__ int group_merge(uint16_t* tok, uint16_t* rk, int L, const DeviceTable
       const int pl = prev_live(tok, i);
       if (pl >= 0) rk[pl] = uint16_t(probe_rank(T, tok[pl], c));
     };
-    if (!sweep) {
-#pragma unroll
-      for (int k = 0; k < kMem; ++k)
-        if (k < mine) refresh(at[k]);
+    if (NW > 1) {
+      __syncthreads();
+      const int now = gs->dead;
+      if (now == dead) {  // a pass must remove at least one token
+        if (tid == 0 && status) atomicMax(status, int(kStatusBadSegment));
+        break;
+      }
+      const int merged = now - dead;
+      dead = now;
+      if (merged <= kMergeList) {  // the first threads take one merged slot each: one or two warps do the probes
+        if (tid < merged) refresh(gs->list[tid]);
+      } else {
+        for (int i = tid; i < n; i += G)
+          if (tok[i] == c) refresh(i);
+      }
     } else {
-      for (int i = tid; i < n; i += G)
-        if (tok[i] == c) refresh(i);
+      const int wsum   = __reduce_add_sync(0xFFFFFFFFu, mine);
+      const bool sweep = __any_sync(0xFFFFFFFFu, mine > kMem) != 0;
+      if (wsum == 0) {
+        if (tid == 0 && status) atomicMax(status, int(kStatusBadSegment));
+        break;
+      }
+      dead += wsum;
+      if (!sweep) {
+#pragma unroll
+        for (int k = 0; k < kMem; ++k)
+          if (k < mine) refresh(at[k]);
+      } else {
+        for (int i = tid; i < n; i += G)
+          if (tok[i] == c) refresh(i);
+      }
     }
     gsync<NW>();
     // (5) compaction when an eighth of the slots is dead
@@ -2013,7 +2034,10 @@ template <int NW>
 int base_blocks_per_sm(int smem_tokens)
 {
   const int bytes = smem_tokens * 4;
-  cudaFuncSetAttribute(k_merge_base<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  // opt in to the largest size any chunk length of this warp count can ask for, so that handles with different
+  // chunk sizes on one device never lower each other's limit
+  constexpr int kMaxTokens = (NW == 32) ? kBaseSmemMaxTokens : NW * 1024;
+  cudaFuncSetAttribute(k_merge_base<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxTokens * 4);
   int nb = 0;
   cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, k_merge_base<NW>, NW * 32, bytes);
   return nb;
