@@ -52,10 +52,10 @@ for _p in (ROOT, PKG):
 
 BLOCK = 65536  # generator block size
 
-# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per input byte of one k_merge_opt launch: 201.5 MB
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per input byte of one k_merge_opt launch: 201.1 MB
 # measured by ncu for a launch over 128 MiB of config-2 text.  Traffic grows in proportion to the tile count,
 # so a launch over n bytes moves this x n.
-MERGE_OPT_DRAM_BYTES_PER_INPUT_BYTE = 201.5e6 / (128 << 20)
+MERGE_OPT_DRAM_BYTES_PER_INPUT_BYTE = 201.1e6 / (128 << 20)
 
 WORKLOADS = {
     #        seed  bytes per GPU   chunk   mix  lognormal
@@ -671,7 +671,7 @@ def main() -> None:
                          "traffic": (MERGE_OPT_DRAM_BYTES_PER_INPUT_BYTE * n_bytes
                                      if args.mode == "opt" and args.workload == "cfg2" else None),
                          "traffic_note": "a constant: ncu dram__bytes_read.sum + dram__bytes_write.sum of one k_merge_opt "
-                                         "launch over 128 MiB of this text (201.5 MB), scaled by input bytes",
+                                         "launch over 128 MiB of this text (201.1 MB), scaled by input bytes",
                          "peak_source": peak_kind,
                          "algorithmic_bytes_per_input_byte": algo_bytes_per_byte,
                          "frac_note": "frac = whole-path algorithmic bytes (text + int32 ids + offsets) over the merge "
