@@ -718,6 +718,8 @@ int encode_host_small(gtk_tokenizer* h, const uint8_t* bytes, const int64_t* tex
   p.b.totals      = reinterpret_cast<int64_t*>(h->small_out_d + kSmallOutTotals);
   h->d_text_off.reserve((size_t(gtk::kSmallMaxTexts) + 1) * 8);
   p.b.text_off_copy = h->d_text_off.as<int64_t>();
+  h->d_chunk_id_off.reserve(size_t(kSmallChunkCap + 1) * 8);
+  p.b.chunk_id_mirror = h->d_chunk_id_off.as<int64_t>();
   cudaStream_t s = h->stream;
   GTK_CUDA(cudaEventRecord(h->ev[1], s));
   const int launches = gtk::launch_encode_small(p.b, h->dtab, s);

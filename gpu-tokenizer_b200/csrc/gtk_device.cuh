@@ -74,6 +74,7 @@ struct EncodeBuffers {
   int64_t* unit_base;        // [n_tiles+1]
   int64_t* chunk_id_off;     // [chunk_cap+1] packed id offset of each chunk (caller visible)
   int64_t* text_id_off;      // [n_texts+1] or nullptr
+  int64_t* chunk_id_mirror;  // small-batch kernel only: device copy of chunk_id_off when that lives in host memory
   int32_t* out_ids;
   const uint16_t* low_id_map;  // nullptr, or 256 entries: output id of every id < 256 (GPT-2 id space)
   int64_t out_capacity;

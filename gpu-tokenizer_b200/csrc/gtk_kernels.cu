@@ -977,6 +977,7 @@ struct OptSmem {
   int first_start, last_start, over_start;
   int over_len;
   long long over_end;
+  long long run_base;  // single-CTA kernel: ids written by the tiles so far
   int over_chunk;
   int end_owned;
 };
@@ -1235,6 +1236,10 @@ __device__ __forceinline__ void opt_tile_reset(OptSmem& S)
 
 // One tile of the byte stream: tokenises every segment that starts in bytes [k*kTile, (k+1)*kTile),
 // writes the tokens compacted to staging, the unit record and the per-chunk counts.
+// SEQ: the tiles of a batch are walked in order by one CTA (small batches); the tile then writes its ids and the
+// id offsets of its chunks straight to the output, at the running id count kept in S.run_base, instead of going
+// through staging, counts, scans and pack.
+template <bool SEQ>
 __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, const DeviceTable& T, int64_t k,
                                          int64_t C)
 {
@@ -1510,6 +1515,85 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
       }
     }
     __syncthreads();
+    if (SEQ) {
+      // ---- single-CTA kernel: ids and chunk offsets go straight to the output ----
+      // J'. a segment that runs past the window is merged first (its tokens follow the tile's own ones)
+      int over_len         = 0;
+      const uint16_t* wtok = nullptr;
+      if (S.over_start >= 0) {  // CTA-uniform
+        const int64_t gs0 = lo + S.over_start;
+        if (tid == 0) {
+          int64_t c = b.tile_chunk0[k];
+          while (c + 1 < C && b.chunk_off[c + 1] <= gs0) ++c;
+          S.over_end = b.chunk_off[c + 1];
+        }
+        __syncthreads();
+        const int64_t cend = S.over_end;
+        int64_t ge         = cend;
+        for (int64_t pos = lo + kWindow; pos < cend; pos += kOptThreads) {
+          const int64_t p = pos + tid;
+          const bool cutp = (p < cend) && !adj_bit(T.adj, b.bytes[p - 1], b.bytes[p]);
+          if (__syncthreads_or(cutp)) {
+            if (cutp) atomicMin(reinterpret_cast<unsigned long long*>(&S.over_end), (unsigned long long)p);
+            __syncthreads();
+            ge = S.over_end;
+            break;
+          }
+        }
+        const int64_t L64 = ge - gs0;
+        if (L64 > b.seg_scratch_tokens || b.seg_scratch == nullptr) {
+          if (tid == 0) atomicMax(status, int(kStatusScratchTooSmall));
+        } else {
+          const int L   = int(L64);
+          uint16_t* wt  = b.seg_scratch + int64_t(blockIdx.x) * 2 * b.seg_scratch_tokens;
+          uint16_t* wrk = wt + b.seg_scratch_tokens;
+          for (int i = tid; i < L; i += kOptThreads) {
+            const uint32_t cur = b.bytes[gs0 + i];
+            wt[i]  = __ldg(T.byte_to_id + cur);
+            wrk[i] = (i + 1 < L) ? __ldg(T.byte_pair_rank + ((cur << 8) | b.bytes[gs0 + i + 1])) : uint16_t(NONE);
+          }
+          __syncthreads();
+          over_len = group_merge<kOptThreads / 32, true>(wt, wrk, L, T, &S.gs, status);
+          wtok     = wt;
+        }
+        __syncthreads();
+      }
+      const int64_t out_base = S.run_base;  // written by thread 0 behind the barrier at the end of the last tile
+      const uint16_t* map    = b.low_id_map;
+      for (int j = tid; j < total; j += kOptThreads) {
+        const uint32_t t = S.rk[j];
+        if (out_base + j < b.out_capacity)
+          b.out_ids[out_base + j] = int32_t((map && t < 256u) ? uint32_t(__ldg(map + t)) : t);
+      }
+      for (int j = tid; j < over_len; j += kOptThreads) {
+        const uint32_t t = wtok[j];
+        if (out_base + total + j < b.out_capacity)
+          b.out_ids[out_base + total + j] = int32_t((map && t < 256u) ? uint32_t(__ldg(map + t)) : t);
+      }
+      // id offset of every chunk that starts in this tile: the ids in front of the tile plus the live tokens of the
+      // tile in front of the chunk's first byte (a chunk start is a segment start, so it lies inside the owned
+      // region, or is the start of the oversize segment right behind it)
+      const int64_t c0 = b.tile_chunk0[k];
+      for (int64_t c = c0 + tid; c < C; c += kOptThreads) {
+        const int64_t p64 = b.chunk_off[c] - lo;
+        if (p64 >= own) break;
+        if (p64 >= 0) {
+          const int p = int(p64);
+          const int64_t at = out_base + S.woff[p >> 5] + __popc(S.cut[p >> 5] & ((1u << (p & 31)) - 1u));
+          b.chunk_id_off[c]    = at;
+          b.chunk_id_mirror[c] = at;
+        }
+      }
+      __syncthreads();
+      if (tid == 0) {
+        S.run_base = out_base + total + over_len;
+        if (k == b.n_tiles - 1) {  // the tile with the last byte closes the offsets
+          b.chunk_id_off[C]    = S.run_base;
+          b.chunk_id_mirror[C] = S.run_base;
+        }
+      }
+      return;
+    }
     const int64_t region_start = lo + ((first < kWindow) ? first : 0);
     for (int j = tid; j < total; j += kOptThreads)
       if (GTK_IN(j, kWindow, 22) && GTK_IN(region_start + j, n, 23)) b.staging[region_start + j] = S.rk[j];
@@ -1617,7 +1701,7 @@ __global__ void __launch_bounds__(kOptThreads, 6) k_merge_opt(EncodeBuffers b, D
     __syncthreads();
     const int64_t k = S.ticket;
     if (k >= b.n_tiles) break;
-    opt_tile(S, b, T, k, C);
+    opt_tile<false>(S, b, T, k, C);
   }
 }
 
@@ -1666,7 +1750,6 @@ __global__ void __launch_bounds__(kOptThreads) k_encode_small(EncodeBuffers b, D
   const int64_t C = cta_exclusive_scan(ChunksPerText{b.text_off, b.chunk_bytes}, b.n_texts, b.text_chunk_base,
                                        S.scanbuf, &carry_s);
   for (int64_t c = tid; c <= C; c += kOptThreads) {
-    if (c < C) b.chunk_cnt[c] = 0;
     if (c == C) {
       b.chunk_off[c] = b.text_off[b.n_texts];
       continue;
@@ -1688,30 +1771,21 @@ __global__ void __launch_bounds__(kOptThreads) k_encode_small(EncodeBuffers b, D
     }
     b.tile_chunk0[k] = int32_t(lo);
   }
-  // tiles, one after the other
+  // tiles, one after the other; each writes its ids and the id offsets of the chunks that start in it
+  if (tid == 0) S.run_base = 0;
   for (int64_t k = 0; k < b.n_tiles; ++k) {
     __syncthreads();
     if (tid == 0) opt_tile_reset(S);
     __syncthreads();
-    opt_tile(S, b, T, k, C);
+    opt_tile<true>(S, b, T, k, C);
   }
   __syncthreads();
-  // output: offsets of units, chunks and texts, then the packed ids
-  cta_exclusive_scan(CountsI32{b.unit_cnt}, b.n_tiles, b.unit_base, S.scanbuf, &carry_s);
-  const int64_t N = cta_exclusive_scan(CountsI32{b.chunk_cnt}, C, b.chunk_id_off, S.scanbuf, &carry_s);
-  for (int64_t t = tid; t <= b.n_texts; t += kOptThreads) b.text_id_off[t] = b.chunk_id_off[b.text_chunk_base[t]];
-  for (int64_t u = 0; u < b.n_tiles; ++u) {
-    const int64_t src = b.unit_first[u], dst = b.unit_base[u];
-    const int m       = b.unit_cnt[u];
-    for (int j = tid; j < m; j += kOptThreads)
-      if (dst + j < b.out_capacity) {
-        const uint32_t t = b.staging[src + j];
-        b.out_ids[dst + j] = int32_t((b.low_id_map && t < 256u) ? uint32_t(__ldg(b.low_id_map + t)) : t);
-      }
-  }
+  // the offsets of the texts follow from those of their chunks; the caller-visible chunk offsets may live in
+  // mapped host memory, so they are read back from the copy in device memory
+  for (int64_t t = tid; t <= b.n_texts; t += kOptThreads) b.text_id_off[t] = b.chunk_id_mirror[b.text_chunk_base[t]];
   if (tid == 0) {
     b.totals[0] = C;
-    b.totals[1] = N;
+    b.totals[1] = S.run_base;
     b.totals[2] = int64_t(b.counters[1]);
   }
 }

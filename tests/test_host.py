@@ -328,3 +328,21 @@ def test_host_table_beyond_16_bits(native_built, merges_path, oracle, novel, tmp
     want, woff = Oracle(path).encode_fixed(part, 1024, mode=MODE_GREEDY, threads=4)
     assert np.array_equal(ids, want) and np.array_equal(coff, woff)
     assert ids.max() > 65535
+
+
+def test_bench_reference_arm_line(native_built, oracle):
+    """`bench.py --impl reference` needs no GPU: it prints one JSON line with the contract's keys, describes the
+    same workload as the GPU arm would, and reports zero copy bytes."""
+    import json
+
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1",
+                          "--warmup", "0", "--ref-budget-s", "1", "--bytes", str(8 << 20)],
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [ln for ln in out.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["metric"] == "input_MB_per_s" and d["unit"] == "MB/s" and d["value"] > 0
+    assert d["config"]["workload"] == "cfg2" and d["config"]["chunk_bytes"] == 4096 and d["config"]["bytes_per_gpu"] == 8 << 20
+    assert d["cpu_baseline"]["kind"] in ("reference", "port") and d["cpu_baseline"]["cores"] >= 1
+    assert d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["d2h_bytes_per_step"] == 0 and d["higher_is_better"] is True
