@@ -1132,6 +1132,35 @@ __device__ __forceinline__ int next_cut(const uint32_t* cut, int s)
   return w * 32 + __ffs(int(x)) - 1;
 }
 
+// One multi-byte segment that starts at window position ss: oversize and long ones are noted, a short one is
+// looked up as a whole; returns true when it has to be merged (it then joins the list of misses).
+__device__ __forceinline__ bool walk_one(int ss, const uint4* word_slots, uint32_t word_shift, int wlen, int* status)
+{
+  OptSmem& S   = g_tile;
+  const int e  = next_cut(S.cut, ss);
+  const int LL = e - ss;
+  if (e >= kWindow && wlen == kWindow) {
+    S.over_start = ss;  // runs past the window: finished in the HBM workspace
+    return false;
+  }
+  if (LL > kThreadSegMax) {
+    const int q = atomicAdd(&S.nlong, 1);
+    if (q < kLongCap && GTK_IN(ss, kWindow, 3)) S.longq[q] = uint16_t(ss);
+    else atomicMax(status, int(kStatusLongQueueOverflow));
+    return false;
+  }
+  if (LL <= 12 && GTK_IN(ss, kWindow, 4)) {
+    uint32_t k0, k1, k2;
+    segment_key(S.bytes, 16 + ss, LL, k0, k1, k2);
+    const uint32_t id = word_lookup(word_slots, word_shift, k0, k1, k2, uint32_t(LL));
+    if (id != 0xFFFFFFFFu) {
+      S.tok[ss] = uint16_t(id);
+      return false;
+    }
+  }
+  return true;
+}
+
 // Step D/E1 of a tile, out of line so that it gets registers of its own: every thread walks the multi-byte
 // segments that start in its 16 positions (window positions [16*tid, 16*tid+16), owned ones only).
 __device__ __noinline__ void walk_segments(const uint4* word_slots, uint32_t word_shift, int own, int wlen,
@@ -1156,26 +1185,7 @@ __device__ __noinline__ void walk_segments(const uint4* word_slots, uint32_t wor
     if (m16) {
       ss = base + __ffs(int(m16)) - 1;
       m16 &= m16 - 1;
-      const int e  = next_cut(S.cut, ss);
-      const int LL = e - ss;
-      if (e >= kWindow && wlen == kWindow) {
-        S.over_start = ss;  // runs past the window: finished in the HBM workspace
-      } else if (LL > kThreadSegMax) {
-        const int q = atomicAdd(&S.nlong, 1);
-        if (q < kLongCap && GTK_IN(ss, kWindow, 3)) S.longq[q] = uint16_t(ss);
-        else atomicMax(status, int(kStatusLongQueueOverflow));
-      } else {
-        miss = true;
-        if (LL <= 12 && GTK_IN(ss, kWindow, 4)) {
-          uint32_t k0, k1, k2;
-          segment_key(S.bytes, 16 + ss, LL, k0, k1, k2);
-          const uint32_t id = word_lookup(word_slots, word_shift, k0, k1, k2, uint32_t(LL));
-          if (id != 0xFFFFFFFFu) {
-            miss      = false;
-            S.tok[ss] = uint16_t(id);
-          }
-        }
-      }
+      miss = walk_one(ss, word_slots, word_shift, wlen, status);
     }
     const uint32_t bal = __ballot_sync(0xFFFFFFFFu, miss);
     if (bal) {
@@ -1183,6 +1193,50 @@ __device__ __noinline__ void walk_segments(const uint4* word_slots, uint32_t wor
       if (lane == 0) wbase = atomicAdd(&S.nmiss, __popc(bal));
       wbase = __shfl_sync(0xFFFFFFFFu, wbase, 0);
       if (miss && GTK_IN(wbase + __popc(bal & lt), kSegCap, 5)) S.seg[wbase + __popc(bal & lt)] = uint16_t(ss);
+    }
+  }
+}
+
+// The same step for a CTA that has its SM to itself (small batches, one tile at a time): the segments are listed
+// first (block-wide scan of the per-thread counts) and then dealt out one per thread and round.  A 512-byte text,
+// whose segments all start in the positions of the first 32 threads, is then looked up in one round of table loads
+// instead of one round per segment of the busiest thread.
+__device__ __noinline__ void walk_segments_cta(const uint4* word_slots, uint32_t word_shift, int own, int wlen,
+                                               int* status)
+{
+  OptSmem& S     = g_tile;
+  const int tid  = threadIdx.x, lane = tid & 31;
+  const uint32_t lt = lanemask_lt();
+  const int base = tid * 16;
+  uint32_t m16   = 0;
+  if (base < own) {
+    const uint32_t w32     = __funnelshift_r(S.cut[tid >> 1], S.cut[(tid >> 1) + 1], (tid & 1) * 16);
+    const uint32_t ownmask = (base + 16 <= own) ? 0xFFFFu : ((1u << (own - base)) - 1u);
+    m16 = w32 & ~(w32 >> 1) & ownmask;
+  }
+  constexpr int kListAt = kSegCap / 2, kListCap = kSegCap - kListAt;  // upper half of seg; misses fill the lower
+  int total;
+  int at = block_exclusive_scan(__popc(m16), S.scanbuf, &total);
+  if (total > kListCap) {  // CTA-uniform: too many for the list, walk per thread
+    walk_segments(word_slots, word_shift, own, wlen, status);
+    return;
+  }
+  for (uint32_t m = m16; m; m &= m - 1) S.seg[kListAt + at++] = uint16_t(base + __ffs(int(m)) - 1);
+  __syncthreads();
+  for (int g0 = 0; g0 < total; g0 += kOptThreads) {
+    const int g = g0 + tid;
+    bool miss   = false;
+    int ss      = 0;
+    if (g < total) {
+      ss   = S.seg[kListAt + g];
+      miss = walk_one(ss, word_slots, word_shift, wlen, status);
+    }
+    const uint32_t bal = __ballot_sync(0xFFFFFFFFu, miss);
+    if (bal) {
+      int wbase = 0;
+      if (lane == 0) wbase = atomicAdd(&S.nmiss, __popc(bal));
+      wbase = __shfl_sync(0xFFFFFFFFu, wbase, 0);
+      if (miss && GTK_IN(wbase + __popc(bal & lt), kListAt, 5)) S.seg[wbase + __popc(bal & lt)] = uint16_t(ss);
     }
   }
 }
@@ -1360,7 +1414,8 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
           atomicMax(&S.end_owned, next_cut(S.cut, last));
         }
       }
-      walk_segments(T.word_slots, 32u - T.word_log2_capacity, own, wlen, status);
+      if (SEQ) walk_segments_cta(T.word_slots, 32u - T.word_log2_capacity, own, wlen, status);
+      else walk_segments(T.word_slots, 32u - T.word_log2_capacity, own, wlen, status);
     }
     __syncthreads();
     GTK_PHASE(3);
@@ -1741,14 +1796,29 @@ __global__ void __launch_bounds__(kOptThreads) k_encode_small(EncodeBuffers b, D
   const int tid = threadIdx.x;
   opt_tile_setup(S, T);
   if (tid < 4) b.counters[tid] = 0;
+  // One text of a few chunks (the one-string-per-call case): its chunk table is arithmetic and lives in shared
+  // memory, so nothing is read over PCIe but the text itself and no search or scan runs.
+  constexpr int kFastChunks = 64;
+  __shared__ int64_t s_chunk_off[kFastChunks + 1];
+  __shared__ int32_t s_tile_chunk0[kSmallMaxBytes / kTile + 1];
+  const int64_t one_c = (b.n_bytes + b.chunk_bytes - 1) / b.chunk_bytes;
+  const bool one_text = b.n_texts == 1 && one_c <= kFastChunks;  // CTA-uniform
+  int64_t C;
+  if (one_text) {
+    C = one_c;
+    for (int64_t c = tid; c <= C; c += kOptThreads) s_chunk_off[c] = min(c * int64_t(b.chunk_bytes), b.n_bytes);
+    for (int64_t k = tid; k < b.n_tiles; k += kOptThreads) s_tile_chunk0[k] = int32_t((k * kTile) / b.chunk_bytes);
+    b.chunk_off   = s_chunk_off;
+    b.tile_chunk0 = s_tile_chunk0;
+  } else {
   if (b.text_off_copy) {  // one parallel read over PCIe instead of dependent reads in the searches below
     for (int64_t t = tid; t <= b.n_texts; t += kOptThreads) b.text_off_copy[t] = b.text_off[t];
     b.text_off = b.text_off_copy;
     __syncthreads();
   }
   // chunker: chunks per text -> offsets of every chunk -> first chunk of every tile
-  const int64_t C = cta_exclusive_scan(ChunksPerText{b.text_off, b.chunk_bytes}, b.n_texts, b.text_chunk_base,
-                                       S.scanbuf, &carry_s);
+  C = cta_exclusive_scan(ChunksPerText{b.text_off, b.chunk_bytes}, b.n_texts, b.text_chunk_base,
+                         S.scanbuf, &carry_s);
   for (int64_t c = tid; c <= C; c += kOptThreads) {
     if (c == C) {
       b.chunk_off[c] = b.text_off[b.n_texts];
@@ -1771,6 +1841,7 @@ __global__ void __launch_bounds__(kOptThreads) k_encode_small(EncodeBuffers b, D
     }
     b.tile_chunk0[k] = int32_t(lo);
   }
+  }
   // tiles, one after the other; each writes its ids and the id offsets of the chunks that start in it
   if (tid == 0) S.run_base = 0;
   for (int64_t k = 0; k < b.n_tiles; ++k) {
@@ -1782,7 +1853,11 @@ __global__ void __launch_bounds__(kOptThreads) k_encode_small(EncodeBuffers b, D
   __syncthreads();
   // the offsets of the texts follow from those of their chunks; the caller-visible chunk offsets may live in
   // mapped host memory, so they are read back from the copy in device memory
-  for (int64_t t = tid; t <= b.n_texts; t += kOptThreads) b.text_id_off[t] = b.chunk_id_mirror[b.text_chunk_base[t]];
+  if (one_text) {
+    if (tid < 2) b.text_id_off[tid] = tid ? S.run_base : 0;
+  } else {
+    for (int64_t t = tid; t <= b.n_texts; t += kOptThreads) b.text_id_off[t] = b.chunk_id_mirror[b.text_chunk_base[t]];
+  }
   if (tid == 0) {
     b.totals[0] = C;
     b.totals[1] = S.run_base;
