@@ -454,7 +454,7 @@ def latency_run(hx: Harness, merges, calls: int):
             "kernel_p50_us": float(np.percentile(kern, 50)), "calls": int(len(lat)), "bytes_per_call": 512,
             "parity_check": bool(ok), "strings_checked": int(calls),
             "note": "host bytes in, ids on the host out, batch size 1; p50/p99 through Python ctypes, "
-                    "c_abi = gtk_encode alone, kernel = CUDA-event time of the one launch"}
+                    "c_abi = gtk_encode alone, kernel = the kernel's own globaltimer span"}
 
 
 def sub_config_run(hx: Harness, name: str, merges, steps: int):

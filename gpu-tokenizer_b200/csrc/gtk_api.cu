@@ -10,6 +10,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdio>
 #include <cstring>
 #include <memory>
@@ -159,6 +160,7 @@ struct gtk_tokenizer {
   uint8_t* small_out_h = nullptr;  // [totals | text id offsets | chunk id offsets | ids]
   uint8_t* small_out_d = nullptr;
   bool result_is_small = false;
+  int64_t small_seq = 0;  // calls of the small-batch kernel so far (the kernel echoes it as its completion mark)
   // sliced host path: copy streams and two slice arenas
   cudaStream_t in_stream = nullptr, out_stream = nullptr, pack_stream = nullptr;
   SliceArena slice[kSliceArenas];
@@ -699,6 +701,7 @@ void small_path_init(gtk_tokenizer* h)
   GTK_CUDA(cudaHostAlloc(&oh, kSmallOutSize, cudaHostAllocMapped));
   GTK_CUDA(cudaHostGetDevicePointer(&id, ih, 0));
   GTK_CUDA(cudaHostGetDevicePointer(&od, oh, 0));
+  std::memset(oh, 0, 64);  // the completion mark of the result block starts at call number 0
   h->small_in_h = static_cast<uint8_t*>(ih);
   h->small_out_h = static_cast<uint8_t*>(oh);
   h->small_in_d = static_cast<uint8_t*>(id);
@@ -721,15 +724,29 @@ int encode_host_small(gtk_tokenizer* h, const uint8_t* bytes, const int64_t* tex
   h->d_chunk_id_off.reserve(size_t(kSmallChunkCap + 1) * 8);
   p.b.chunk_id_mirror = h->d_chunk_id_off.as<int64_t>();
   cudaStream_t s = h->stream;
-  GTK_CUDA(cudaEventRecord(h->ev[1], s));
+  p.b.small_seq = ++h->small_seq;
   const int launches = gtk::launch_encode_small(p.b, h->dtab, s);
-  GTK_CUDA(cudaEventRecord(h->ev[2], s));
   GTK_CUDA(cudaGetLastError());
-  GTK_CUDA(cudaStreamSynchronize(s));
-  const int64_t* tot = reinterpret_cast<const int64_t*>(h->small_out_h + kSmallOutTotals);
+  // The kernel's last store is the call number, behind a system-wide fence: polling it in the mapped result block
+  // returns as soon as the results are on the host, several microseconds before a stream synchronisation would.
+  // The stream is asked now and then so that a failed launch or a fault ends the wait with its error.
+  volatile const int64_t* tot = reinterpret_cast<volatile const int64_t*>(h->small_out_h + kSmallOutTotals);
+  for (unsigned spin = 1; tot[3] != p.b.small_seq; ++spin) {
+    if ((spin & 0xFFFFu) == 0u) {
+      const cudaError_t q = cudaStreamQuery(s);
+      if (q == cudaSuccess) {
+        if (tot[3] != p.b.small_seq) return h->fail(GTK_ERR_KERNEL, "small-batch kernel ended without publishing its results");
+        break;
+      }
+      if (q != cudaErrorNotReady) throw CudaFail{std::string("small-batch kernel: ") + cudaGetErrorString(q)};
+    }
+#if defined(__x86_64__) || defined(__i386__)
+    __builtin_ia32_pause();
+#endif
+  }
+  std::atomic_thread_fence(std::memory_order_acquire);
   if (tot[2] != gtk::kStatusOk) return h->fail(GTK_ERR_KERNEL, status_text(int(tot[2])));
-  float ms = 0.f;
-  if (cudaEventElapsedTime(&ms, h->ev[1], h->ev[2]) == cudaSuccess) h->stage_ms[1] = h->stage_ms[4] = ms;
+  h->stage_ms[1] = h->stage_ms[4] = float(double(tot[4]) * 1e-6);  // the kernel's own globaltimer span
   h->last_launches = launches;
   h->result_is_small = true;
   h->res_n_chunks = tot[0];

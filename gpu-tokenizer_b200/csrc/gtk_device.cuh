@@ -75,6 +75,7 @@ struct EncodeBuffers {
   int64_t* chunk_id_off;     // [chunk_cap+1] packed id offset of each chunk (caller visible)
   int64_t* text_id_off;      // [n_texts+1] or nullptr
   int64_t* chunk_id_mirror;  // small-batch kernel only: device copy of chunk_id_off when that lives in host memory
+  int64_t small_seq;         // small-batch kernel only: call number, written to totals[3] as the last store of the kernel
   int32_t* out_ids;
   const uint16_t* low_id_map;  // nullptr, or 256 entries: output id of every id < 256 (GPT-2 id space)
   int64_t out_capacity;
@@ -100,7 +101,8 @@ int launch_output_scans(const EncodeBuffers& b, int mode_base, cudaStream_t stre
 int launch_pack(const EncodeBuffers& b, int mode_base, int grid, cudaStream_t stream);
 // totals[0..1] and counters[0..3] to `mapped` (page-locked host memory as the device sees it), laid out as 4 x int64
 int launch_publish_totals(const EncodeBuffers& b, int64_t* mapped, cudaStream_t stream);
-// Whole pipeline in one single-CTA kernel for small batches; totals[0..2] receive n_chunks, n_ids, status.
+// Whole pipeline in one single-CTA kernel for small batches; totals[0..2] receive n_chunks, n_ids, status,
+// totals[4] the kernel's own duration in nanoseconds and, as the very last store, totals[3] the call number.
 int launch_encode_small(const EncodeBuffers& b, const DeviceTable& t, cudaStream_t stream);
 constexpr int64_t kSmallMaxBytes = 32768;
 constexpr int64_t kSmallMaxTexts = 1024;

@@ -1794,6 +1794,8 @@ __global__ void __launch_bounds__(kOptThreads) k_encode_small(EncodeBuffers b, D
   OptSmem& S = g_tile;
   __shared__ int64_t carry_s;
   const int tid = threadIdx.x;
+  unsigned long long t_start = 0;
+  if (tid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_start));
   opt_tile_setup(S, T);
   if (tid < 4) b.counters[tid] = 0;
   // One text of a few chunks (the one-string-per-call case): its chunk table is arithmetic and lives in shared
@@ -1858,10 +1860,18 @@ __global__ void __launch_bounds__(kOptThreads) k_encode_small(EncodeBuffers b, D
   } else {
     for (int64_t t = tid; t <= b.n_texts; t += kOptThreads) b.text_id_off[t] = b.chunk_id_mirror[b.text_chunk_base[t]];
   }
+  // The results may live in mapped host memory and the host may be polling totals[3] instead of waiting for the
+  // stream: every store of this CTA is made visible system-wide before the call number goes out as the last one.
+  __syncthreads();
   if (tid == 0) {
+    unsigned long long t_end;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_end));
     b.totals[0] = C;
     b.totals[1] = S.run_base;
     b.totals[2] = int64_t(b.counters[1]);
+    b.totals[4] = int64_t(t_end - t_start);
+    __threadfence_system();
+    *reinterpret_cast<volatile int64_t*>(b.totals + 3) = b.small_seq;
   }
 }
 

@@ -125,7 +125,12 @@ GTK_API int gtk_table_info_get(const gtk_tokenizer* h, gtk_table_info* out);
  * *kernel_ms (optional) receives the device time of the kernel pipeline
  * (cudaEvent pair, as :790-805).  Results stay valid until the next call on
  * the handle; read them with gtk_result_sizes/_view/_copy.
- * An empty batch or a batch of empty texts is not an error: 0 ids, 0 chunks. */
+ * An empty batch or a batch of empty texts is not an error: 0 ids, 0 chunks.
+ * Small batches (up to 32 KiB and 1024 texts, GTK_MODE_OPT) run as one kernel that reads the text from and
+ * writes the results to mapped page-locked memory; the call returns when the kernel's completion mark has
+ * arrived there (its last store, behind a system-wide fence), which is when the results are complete -- the
+ * stream may still be retiring the kernel for a few microseconds.  *kernel_ms is then the kernel's own
+ * measurement of its duration. */
 GTK_API int gtk_encode(gtk_tokenizer* h, int mode, const uint8_t* bytes, const int64_t* text_offsets,
                        int64_t n_texts, float* kernel_ms);
 
