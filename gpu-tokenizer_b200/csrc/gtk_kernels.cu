@@ -1789,6 +1789,90 @@ __device__ int64_t cta_exclusive_scan(F f, int64_t n, int64_t* out, int* scanbuf
   return total;
 }
 
+// the same with 16 consecutive items per thread and round (4096 items per round): the scans of a medium batch
+template <class F>
+__device__ int64_t cta_exclusive_scan16(F f, int64_t n, int64_t* out, int* scanbuf, int64_t* carry_s)
+{
+  constexpr int E = 16;
+  if (threadIdx.x == 0) *carry_s = 0;
+  __syncthreads();
+  for (int64_t base = 0; base < n; base += int64_t(kOptThreads) * E) {
+    const int64_t first = base + int64_t(threadIdx.x) * E;
+    int v[E];
+    int s = 0;
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      v[e] = (first + e < n) ? int(f(first + e)) : 0;
+      s += v[e];
+    }
+    int total;
+    const int off = block_exclusive_scan(s, scanbuf, &total);
+    int64_t run   = *carry_s + off;
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      if (first + e < n) out[first + e] = run;
+      run += v[e];
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *carry_s += total;
+    __syncthreads();
+  }
+  const int64_t total = *carry_s;
+  if (threadIdx.x == 0) out[n] = total;
+  __syncthreads();
+  return total;
+}
+
+// Medium batches (a few thousand texts, chunks and tiles at most): the whole chunker in one single-CTA launch
+// instead of five, and both output scans plus the text offsets in one instead of seven -- at these sizes the
+// launches, not the work, are what the multi-block kernels cost.
+constexpr int64_t kMediumMaxItems = 8192;
+
+__global__ void __launch_bounds__(kOptThreads) k_chunker_medium(EncodeBuffers b)
+{
+  __shared__ int scanbuf[33];
+  __shared__ int64_t carry_s;
+  const int tid   = threadIdx.x;
+  const int64_t C = cta_exclusive_scan16(ChunksPerText{b.text_off, b.chunk_bytes}, b.n_texts, b.text_chunk_base,
+                                         scanbuf, &carry_s);
+  if (tid == 0) b.totals[0] = C;
+  for (int64_t c = tid; c <= C; c += kOptThreads) {
+    if (c == C) {
+      b.chunk_off[c] = b.text_off[b.n_texts];
+      continue;
+    }
+    int64_t lo = 0, hi = b.n_texts;  // last t with text_chunk_base[t] <= c
+    while (hi - lo > 1) {
+      const int64_t mid = (lo + hi) >> 1;
+      if (b.text_chunk_base[mid] <= c) lo = mid; else hi = mid;
+    }
+    b.chunk_off[c] = b.text_off[lo] + (c - b.text_chunk_base[lo]) * int64_t(b.chunk_bytes);
+  }
+  __syncthreads();
+  for (int64_t k = tid; k < b.n_tiles; k += kOptThreads) {
+    const int64_t pos = k * kTile;
+    int64_t lo = 0, hi = C;  // last c with chunk_off[c] <= pos
+    while (hi - lo > 1) {
+      const int64_t mid = (lo + hi) >> 1;
+      if (b.chunk_off[mid] <= pos) lo = mid; else hi = mid;
+    }
+    b.tile_chunk0[k] = int32_t(lo);
+  }
+}
+
+__global__ void __launch_bounds__(kOptThreads) k_scans_medium(EncodeBuffers b, int with_units)
+{
+  __shared__ int scanbuf[33];
+  __shared__ int64_t carry_s;
+  const int tid   = threadIdx.x;
+  const int64_t C = b.totals[0];
+  const int64_t N = cta_exclusive_scan16(CountsI32{b.chunk_cnt}, C, b.chunk_id_off, scanbuf, &carry_s);
+  if (tid == 0) b.totals[1] = N;
+  if (with_units) cta_exclusive_scan16(CountsI32{b.unit_cnt}, b.n_tiles, b.unit_base, scanbuf, &carry_s);
+  if (b.text_id_off)
+    for (int64_t t = tid; t <= b.n_texts; t += kOptThreads) b.text_id_off[t] = b.chunk_id_off[b.text_chunk_base[t]];
+}
+
 __global__ void __launch_bounds__(kOptThreads) k_encode_small(EncodeBuffers b, DeviceTable T)
 {
   OptSmem& S = g_tile;
@@ -2158,8 +2242,23 @@ inline unsigned grid_for(int64_t items, int threads, int64_t cap = 65535)
 // launchers
 // ------------------------------------------------------------------------------------------------
 
+// The scans have no dependent searches, so one CTA serves them up to a few thousand items; the chunker's binary
+// searches (one per chunk and one per tile) are latency-bound in a single CTA and only pay while there are few.
+static bool medium_scans(const EncodeBuffers& b)
+{
+  return b.n_texts <= kMediumMaxItems && b.chunk_cap <= kMediumMaxItems && b.n_tiles <= kMediumMaxItems;
+}
+static bool medium_chunker(const EncodeBuffers& b)
+{
+  return b.n_texts <= 256 && b.chunk_cap <= 2048 && b.n_tiles <= 1024;
+}
+
 int launch_chunker(const EncodeBuffers& b, cudaStream_t stream)
 {
+  if (medium_chunker(b)) {
+    k_chunker_medium<<<1, kOptThreads, 0, stream>>>(b);
+    return 1;
+  }
   int launches = run_scan(ChunksPerText{b.text_off, b.chunk_bytes}, b.n_texts, b.n_texts, nullptr,
                           b.scan_block_sums, b.text_chunk_base, b.totals + 0, stream);
   k_chunk_fill<<<grid_for(b.chunk_cap + 1, 256, 2048), 256, 0, stream>>>(b.text_off, b.text_chunk_base, b.n_texts,
@@ -2258,6 +2357,10 @@ int launch_merge_localmin(const EncodeBuffers& b, const DeviceTable& t, int grid
 
 int launch_output_scans(const EncodeBuffers& b, int mode_base, cudaStream_t stream)
 {
+  if (medium_scans(b)) {
+    k_scans_medium<<<1, kOptThreads, 0, stream>>>(b, (!mode_base && b.n_tiles > 0) ? 1 : 0);
+    return 1;
+  }
   int launches = 0;
   // per-chunk counts -> packed id offset of every chunk (+ total id count)
   launches += run_scan(CountsI32{b.chunk_cnt}, b.chunk_cap, 0, b.totals + 0, b.scan_block_sums, b.chunk_id_off,
