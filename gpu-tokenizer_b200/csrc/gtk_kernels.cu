@@ -2211,10 +2211,25 @@ __global__ void __launch_bounds__(256) k_pack(const uint16_t* __restrict__ stagi
     const int64_t head = min(m, int64_t(((16u - uint32_t(reinterpret_cast<uintptr_t>(dp) & 15u)) >> 2) & 3u));
     if (lane < head) dp[lane] = conv(sp[lane]);
     const int64_t quads = (m - head) >> 2;
-    for (int64_t q = lane; q < quads; q += 32) {
-      const uint16_t* s4 = sp + head + 4 * q;
-      const int4 v = make_int4(conv(s4[0]), conv(s4[1]), conv(s4[2]), conv(s4[3]));
-      *reinterpret_cast<int4*>(dp + head + 4 * q) = v;
+    // four groups of four tokens per lane and trip: sixteen independent 16-bit loads in flight before the first
+    // store, because this kernel lives on memory latency (one warp per unit, nothing to overlap with)
+    for (int64_t q0 = lane; q0 < quads; q0 += 128) {
+      uint32_t t[4][4];
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const int64_t q = q0 + 32 * g;
+        if (q < quads) {
+          const uint16_t* s4 = sp + head + 4 * q;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) t[g][e] = s4[e];
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const int64_t q = q0 + 32 * g;
+        if (q < quads)
+          *reinterpret_cast<int4*>(dp + head + 4 * q) = make_int4(conv(t[g][0]), conv(t[g][1]), conv(t[g][2]), conv(t[g][3]));
+      }
     }
     const int64_t done = head + 4 * quads;
     if (done + lane < m) dp[done + lane] = conv(sp[done + lane]);
