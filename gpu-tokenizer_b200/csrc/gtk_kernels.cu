@@ -1074,7 +1074,26 @@ __device__ __noinline__ uint32_t thread_merge_segments_lanes(int s, int L, PairT
   };
   auto set_rank = [&](int i, uint32_t v) { reinterpret_cast<uint16_t*>(scr + (i >> 1) * 32)[i & 1] = uint16_t(v); };
   uint32_t best = scan();
+#ifdef GTK_PHASE_TIMING
+  if (threadIdx.x == 0) {  // in-situ latency of one table load and of one rank scan
+    const long long a0 = clock64();
+    const uint4 v      = __ldg(P.buckets + (uint32_t(a0) * 2654435761u >> 16));
+    const long long a1 = clock64() + (v.x == 0x12345u);
+    atomicAdd(&g_phase_cycles[16], (unsigned long long)(a1 - a0));
+    atomicAdd(&g_phase_cycles[17], 1ull);
+    const long long b0 = clock64();
+    const uint32_t bb  = scan();
+    const long long b1 = clock64() + (bb == 0x12345u);
+    atomicAdd(&g_phase_cycles[18], (unsigned long long)(b1 - b0));
+    atomicAdd(&g_phase_cycles[19], 1ull);
+  }
+  const long long t0 = clock64();
+  int steps          = 0;
+#endif
   while (__any_sync(0xFFFFFFFFu, best < (SEL << 16))) {
+#ifdef GTK_PHASE_TIMING
+    ++steps;
+#endif
     if (best < (SEL << 16)) {
       const uint32_t r = best >> 16;
       const int j      = int(best & 0xFFFFu);
@@ -1116,6 +1135,12 @@ __device__ __noinline__ uint32_t thread_merge_segments_lanes(int s, int L, PairT
       }
     }
   }
+#ifdef GTK_PHASE_TIMING
+  if (threadIdx.x == 0) {  // warp 0: loop trips and their wall cycles
+    atomicAdd(&g_phase_cycles[14], (unsigned long long)(clock64() - t0));
+    atomicAdd(&g_phase_cycles[15], (unsigned long long)steps);
+  }
+#endif
   return alive;
 }
 
