@@ -470,8 +470,10 @@ def sub_config_run(hx: Harness, name: str, merges, steps: int):
     pin.array[:] = data
     e2e_ms, h2d, d2h, _ = e2e_run(hx, tok, pin, text_off, gputok_b200.GTK_MODE_OPT, max(2, steps))
     seed = WORKLOADS[name][0]
-    ok, n = parity_on_sample(tok, data, text_off, chunk, gputok_b200.GTK_MODE_OPT, seed, 8.0,
-                             os.cpu_count() or 1)
+    # the literal rule is quadratic in the chunk length: a 32 KiB chunk of config 4 costs one core 3.5 s
+    threads = os.cpu_count() or 1
+    ok, n = parity_on_sample(tok, data, text_off, chunk, gputok_b200.GTK_MODE_OPT, seed,
+                             4.0 * threads if chunk > 8192 else 8.0, threads)
     n_bytes = len(data)
     out = dict(desc, value=n_bytes / (dev["ms_per_step"] * 1e-3) / 1e6, unit="MB/s", ms_per_step=dev["ms_per_step"],
                tokens_per_s=dev["n_ids"] / (dev["ms_per_step"] * 1e-3), tokens_per_byte=dev["n_ids"] / n_bytes,

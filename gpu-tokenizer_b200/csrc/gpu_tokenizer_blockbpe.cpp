@@ -8,7 +8,8 @@
 // them per chunk, prints the timing lines the reference's scripts parse
 // (benchmark_tokenizer_scaling.py:155-157, profile_blockbpe_block_sizes.sh:30-32) and writes
 // data/output/gpu_tokens_blockbpe.txt (GTK_OUTPUT overrides).  Exit code 0 iff CPU and GPU agree.
-// The third argument picks the kernel: "base" (default, one CTA per chunk) or "opt".
+// The third argument picks the kernel: "base" (default, one CTA per chunk) or "opt".  GTK_BLOCK_SIZE=128|256|512|1024
+// sets the threads per CTA of the base kernel, which the reference fixes at compile time (-DBLOCK_SIZE, :313-315).
 #include <algorithm>
 #include <chrono>
 #include <cstdint>
@@ -46,6 +47,12 @@ int main(int argc, char** argv)
   if (rc != GTK_OK) {
     std::cerr << "Exception: " << gtk_global_error() << std::endl;
     return 1;
+  }
+  if (const char* bs = std::getenv("GTK_BLOCK_SIZE")) {
+    if (gtk_set_base_block_size(tok, std::atoi(bs)) != GTK_OK) {
+      std::cerr << "Exception: " << gtk_last_error(tok) << std::endl;
+      return 1;
+    }
   }
   gtk_table_info info;
   gtk_table_info_get(tok, &info);

@@ -132,6 +132,7 @@ struct gtk_tokenizer {
   int device = -1;
   int sm_count = 0;
   int opt_grid = 0, base_grid = 0, localmin_grid = 0, wide_grid = 0;
+  int base_block = 0;  // threads per CTA of the one-CTA-per-chunk kernel, 0 = from the chunk size
   bool wide = false;  // ids or ranks beyond 16 bits: every GPU mode runs the 32-bit one-CTA-per-chunk kernel
   cudaStream_t stream = nullptr;      // stream in use
   cudaStream_t own_stream = nullptr;  // created by gtk_create
@@ -326,7 +327,7 @@ void run_front(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* lau
   *launches += gtk::launch_chunker(b, s);
   GTK_CUDA(cudaEventRecord(ev[1], s));
   if (h->wide) *launches += gtk::launch_merge_wide(b, h->dtab, h->wide_grid, s);
-  else if (mode == GTK_MODE_BASE) *launches += gtk::launch_merge_base(b, h->dtab, h->base_grid, s);
+  else if (mode == GTK_MODE_BASE) *launches += gtk::launch_merge_base(b, h->dtab, h->base_grid, h->base_block, s);
   else if (mode == GTK_MODE_LOCALMIN) *launches += gtk::launch_merge_localmin(b, h->dtab, h->localmin_grid, h->max_iters, s);
   else *launches += gtk::launch_merge_opt(b, h->dtab, h->opt_grid, s);
   GTK_CUDA(cudaEventRecord(ev[2], s));
@@ -864,7 +865,7 @@ GTK_API int gtk_create(const char* merges_path, int chunk_tokens, int max_iters,
       for (auto& ev : h->ev) GTK_CUDA(cudaEventCreate(&ev));
       upload_table(h);
       h->opt_grid = h->sm_count * std::max(1, gtk::opt_kernel_max_blocks_per_sm());
-      h->base_grid = h->sm_count * std::max(1, gtk::base_kernel_max_blocks_per_sm(chunk_tokens));
+      h->base_grid = h->sm_count * std::max(1, gtk::base_kernel_max_blocks_per_sm(chunk_tokens, 0));
       h->localmin_grid = h->sm_count * std::max(1, gtk::localmin_kernel_max_blocks_per_sm());
       h->wide_grid = h->sm_count * std::max(1, gtk::wide_kernel_max_blocks_per_sm());
       h->h_totals.reserve(64);
@@ -1174,6 +1175,24 @@ GTK_API int gtk_set_stream(gtk_tokenizer* h, void* cuda_stream)
   cudaSetDevice(h->device);
   cudaStreamSynchronize(h->stream);
   h->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : h->own_stream;
+  return GTK_OK;
+}
+
+GTK_API int gtk_set_base_block_size(gtk_tokenizer* h, int threads)
+{
+  if (!h) return GTK_ERR_INVALID_ARG;
+  std::lock_guard<std::mutex> lock(h->mu);
+  if (h->device < 0) return h->fail(GTK_ERR_NO_DEVICE, "host-only handle: no GPU entry points");
+  if (threads != 0 && threads != 64 && threads != 128 && threads != 256 && threads != 512 && threads != 1024)
+    return h->fail(GTK_ERR_INVALID_ARG, "block size must be 0 (automatic), 64, 128, 256, 512 or 1024");
+  try {
+    GTK_CUDA(cudaSetDevice(h->device));
+    h->base_block = threads;
+    h->base_grid  = h->sm_count * std::max(1, gtk::base_kernel_max_blocks_per_sm(h->chunk_tokens, threads));
+    GTK_CUDA(cudaGetLastError());
+  } catch (const CudaFail& f) {
+    return h->fail(GTK_ERR_CUDA, f.what);
+  }
   return GTK_OK;
 }
 

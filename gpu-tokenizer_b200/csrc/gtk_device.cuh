@@ -92,7 +92,7 @@ struct EncodeBuffers {
 // Launchers (all asynchronous on `stream`; return the number of kernels launched).
 int launch_chunker(const EncodeBuffers& b, cudaStream_t stream);
 int launch_merge_opt(const EncodeBuffers& b, const DeviceTable& t, int grid, cudaStream_t stream);
-int launch_merge_base(const EncodeBuffers& b, const DeviceTable& t, int grid, cudaStream_t stream);
+int launch_merge_base(const EncodeBuffers& b, const DeviceTable& t, int grid, int block_threads, cudaStream_t stream);
 int launch_merge_wide(const EncodeBuffers& b, const DeviceTable& t, int grid, cudaStream_t stream);
 int launch_pack_wide(const EncodeBuffers& b, int grid, cudaStream_t stream);
 int wide_kernel_max_blocks_per_sm();
@@ -120,8 +120,8 @@ struct HandleView {
 bool handle_view(gtk_tokenizer* h, HandleView* out);
 
 int opt_kernel_max_blocks_per_sm();
-int base_kernel_max_blocks_per_sm(int chunk_bytes);
+int base_kernel_max_blocks_per_sm(int chunk_bytes, int block_threads);
 int localmin_kernel_max_blocks_per_sm();
-void base_kernel_geometry(int chunk_bytes, int* warps, int* smem_tokens);
+void base_kernel_geometry(int chunk_bytes, int block_threads, int* warps, int* smem_tokens);
 
 }  // namespace gtk

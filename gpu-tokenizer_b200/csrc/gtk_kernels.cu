@@ -2321,10 +2321,12 @@ int launch_merge_opt(const EncodeBuffers& b, const DeviceTable& t, int grid, cud
 }
 
 // Geometry of the one-CTA-per-chunk kernel for a chunk size: warps per CTA and slots of shared memory per array.
-void base_kernel_geometry(int chunk_bytes, int* warps, int* smem_tokens)
+// block_threads = 0 picks the warp count from the chunk size; 64 .. 1024 (a power of two) forces it, which is what
+// the reference's BLOCK_SIZE compile-time constant does (gputok_blockbpe.cu:313-315).
+void base_kernel_geometry(int chunk_bytes, int block_threads, int* warps, int* smem_tokens)
 {
   const int c  = std::max(chunk_bytes, 1);
-  const int w  = (c + 1023) >> 10;  // one warp per KiB of chunk
+  const int w  = block_threads > 0 ? block_threads / 32 : (c + 1023) >> 10;  // one warp per KiB of chunk
   *warps       = w <= 2 ? 2 : w <= 4 ? 4 : w <= 8 ? 8 : w <= 16 ? 16 : 32;
   *smem_tokens = (std::min(c, kBaseSmemMaxTokens) + 63) & ~63;
 }
@@ -2334,23 +2336,22 @@ template <int NW>
 int base_blocks_per_sm(int smem_tokens)
 {
   const int bytes = smem_tokens * 4;
-  // opt in to the largest size any chunk length of this warp count can ask for, so that handles with different
-  // chunk sizes on one device never lower each other's limit
-  constexpr int kMaxTokens = (NW == 32) ? kBaseSmemMaxTokens : NW * 1024;
-  cudaFuncSetAttribute(k_merge_base<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxTokens * 4);
+  // opt in to the largest size any chunk length can ask for (a forced block size pairs any warp count with any
+  // chunk length), so that handles with different chunk sizes on one device never lower each other's limit
+  cudaFuncSetAttribute(k_merge_base<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBaseSmemMaxTokens * 4);
   int nb = 0;
   cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, k_merge_base<NW>, NW * 32, bytes);
   return nb;
 }
 }  // namespace
 
-int launch_merge_base(const EncodeBuffers& b, const DeviceTable& t, int grid, cudaStream_t stream)
+int launch_merge_base(const EncodeBuffers& b, const DeviceTable& t, int grid, int block_threads, cudaStream_t stream)
 {
   if (b.n_bytes <= 0) return 0;
   if (grid > b.chunk_cap) grid = int(b.chunk_cap);
   if (grid < 1) grid = 1;
   int nw = 0, st = 0;
-  base_kernel_geometry(b.chunk_bytes, &nw, &st);
+  base_kernel_geometry(b.chunk_bytes, block_threads, &nw, &st);
   const size_t bytes = size_t(st) * 4;
   switch (nw) {
     case 2: k_merge_base<2><<<grid, 64, bytes, stream>>>(b, t, st); break;
@@ -2506,10 +2507,10 @@ int opt_kernel_max_blocks_per_sm()
 
 // Call once per device and chunk size (that device current): opts the kernel in to its dynamic shared memory
 // and returns the resident CTAs per SM.
-int base_kernel_max_blocks_per_sm(int chunk_bytes)
+int base_kernel_max_blocks_per_sm(int chunk_bytes, int block_threads)
 {
   int nw = 0, st = 0;
-  base_kernel_geometry(chunk_bytes, &nw, &st);
+  base_kernel_geometry(chunk_bytes, block_threads, &nw, &st);
   switch (nw) {
     case 2: return base_blocks_per_sm<2>(st);
     case 4: return base_blocks_per_sm<4>(st);

@@ -74,6 +74,7 @@ def load_library() -> C.CDLL:
     lib.gtk_token_symbols.restype = i32
     lib.gtk_set_stream.argtypes = [vp, vp]
     lib.gtk_set_id_space.argtypes = [vp, C.c_int]
+    lib.gtk_set_base_block_size.argtypes = [vp, C.c_int]
     lib.gtk_write_token_strings.argtypes = [vp, C.c_char_p, vp, vp, i64]
     lib.gtk_encode_chunks_noalloc.argtypes = [vp, vp, i64, vp, i64, i32, vp, vp]
     lib.gtk_pinned_alloc.argtypes = [C.c_size_t]
@@ -175,6 +176,11 @@ class Tokenizer:
         """False (default): ids as the reference produces them (ids < 256 are byte values);
         True: ids < 256 remapped to GPT-2's own vocabulary order (feedable to a GPT-2 model)."""
         self._check(self._lib.gtk_set_id_space(self._h, 1 if gpt2 else 0))
+
+    def set_base_block_size(self, threads: int) -> None:
+        """Threads per CTA of the one-CTA-per-chunk kernel (GTK_MODE_BASE): 0 = one warp per KiB of chunk,
+        else 64, 128, 256, 512 or 1024 (the reference's BLOCK_SIZE).  Results never depend on it."""
+        self._check(self._lib.gtk_set_base_block_size(self._h, int(threads)))
 
     def write_token_strings(self, path: str, ids, chunk_id_offsets) -> None:
         """One chunk per line, tokens as GPT-2 symbol strings separated by spaces (the reference's

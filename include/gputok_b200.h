@@ -195,6 +195,12 @@ GTK_API int32_t gtk_token_symbols(const gtk_tokenizer* h, int32_t id, char* buf,
  * points stay synchronous on return. */
 GTK_API int gtk_set_stream(gtk_tokenizer* h, void* cuda_stream);
 
+/* Threads per CTA of the one-CTA-per-chunk kernel (GTK_MODE_BASE).  Replaces the reference's compile-time
+ * BLOCK_SIZE (gputok_blockbpe.cu:313-315, swept by profile_blockbpe_block_sizes.sh:9,22-25 over 128..1024):
+ * 0 (default) = one warp per KiB of chunk, 64 / 128 / 256 / 512 / 1024 = that many threads whatever the chunk
+ * size; anything else is GTK_ERR_INVALID_ARG.  Results never depend on it. */
+GTK_API int gtk_set_base_block_size(gtk_tokenizer* h, int threads);
+
 /* Id space of the ids returned by the GPU encode entry points (no counterpart in the reference,
  * whose ids 0..255 are the byte values -- a permutation of GPT-2's own ids for the byte tokens,
  * e.g. the space byte is 32 here and 220 in GPT-2's vocab.json; ids >= 256 coincide).

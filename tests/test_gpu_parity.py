@@ -490,6 +490,42 @@ def test_standalone_cli_reproduces_reference_run(native_built, merges_path, nove
         assert hashlib.sha256(out.read_bytes()).hexdigest() == want
 
 
+def test_base_kernel_block_sizes(lib, native_built, merges_path, novel, oracle, tmp_path):
+    """The reference's BLOCK_SIZE sweep (profile_blockbpe_block_sizes.sh:9-10,22-25) as a run-time setting: every
+    block size gives the ids of the literal rule at every chunk length, other sizes are refused, and the sweep
+    script prints the reference's CSV columns."""
+    import subprocess
+
+    text = np.frombuffer(novel[:200_000], dtype=np.uint8)
+    for chunk in (128, 1024, 4096):
+        want, woff = oracle.encode_fixed(novel[:200_000], chunk, mode=MODE_GREEDY, threads=os.cpu_count() or 1)
+        t = make_tok(lib, merges_path, chunk)
+        for threads in (0, 64, 128, 256, 512, 1024):
+            t.set_base_block_size(threads)
+            ids, _, coff, ms = t.encode(text, mode=lib.GTK_MODE_BASE)
+            assert np.array_equal(ids, want) and np.array_equal(coff, woff), (chunk, threads)
+            assert ms > 0
+        with pytest.raises(lib.GtkError):
+            t.set_base_block_size(96)
+    big = make_tok(lib, merges_path, 32768)                      # a small CTA on a chunk far beyond its warp count
+    stress = lib.TextGen(3).text(1 << 20, mix=lib.MIX_STRESS)
+    ref, _, roff, _ = big.encode(stress, mode=lib.GTK_MODE_OPT)
+    big.set_base_block_size(128)
+    ids, _, coff, _ = big.encode(stress, mode=lib.GTK_MODE_BASE)
+    assert np.array_equal(ids, ref) and np.array_equal(coff, roff)
+
+    src = tmp_path / "novel.txt"
+    src.write_bytes(novel[:100_000])
+    env = dict(os.environ, GTK_MERGES=merges_path, GTK_OUTPUT=str(tmp_path / "tokens.txt"))
+    script = os.path.join(os.path.dirname(native_built.CLI), "profile_blockbpe_block_sizes.sh")
+    r = subprocess.run(["bash", script, str(src)], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    rows = [ln.split(",") for ln in r.stdout.splitlines() if ln[:1].isdigit()]
+    assert "block_size,seq_len,cpu_ms,gpu_ms,gpu_tokens_per_s" in r.stdout
+    assert len(rows) == 24 and {row[0] for row in rows} == {"128", "256", "512", "1024"}
+    assert all(len(row) == 5 and float(row[3]) > 0 and float(row[4]) > 0 for row in rows)
+
+
 def test_pybind_methods_on_gpu(lib, merges_path, oracle):
     import gputok_gpu
 
