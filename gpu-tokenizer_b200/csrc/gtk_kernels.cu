@@ -1093,6 +1093,10 @@ __device__ __noinline__ uint32_t thread_merge_segments_lanes(int s, int L, PairT
   while (__any_sync(0xFFFFFFFFu, best < (SEL << 16))) {
 #ifdef GTK_PHASE_TIMING
     ++steps;
+    {  // merges done by this loop, all warps (each costs two bucket loads)
+      const uint32_t act = __ballot_sync(0xFFFFFFFFu, best < (SEL << 16));
+      if ((threadIdx.x & 31) == 0) atomicAdd(&g_phase_cycles[21], (unsigned long long)__popc(act));
+    }
 #endif
     if (best < (SEL << 16)) {
       const uint32_t r = best >> 16;
