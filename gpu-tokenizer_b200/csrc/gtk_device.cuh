@@ -13,10 +13,16 @@ namespace gtk {
 // Tile geometry of the segment-parallel kernel: a CTA owns the segments that
 // start inside TILE consecutive bytes and sees HALO more bytes so that the
 // last owned segment can finish inside shared memory.
-constexpr int kTile = 4096;
+#ifndef GTK_TILE
+#define GTK_TILE 4096
+#endif
+#ifndef GTK_OPT_THREADS
+#define GTK_OPT_THREADS 256
+#endif
+constexpr int kTile = GTK_TILE;
 constexpr int kHalo = 256;
 constexpr int kWindow = kTile + kHalo;
-constexpr int kOptThreads = 256;
+constexpr int kOptThreads = GTK_OPT_THREADS;
 constexpr int kBaseThreads = 512;
 constexpr int kBaseSmemTokens = 8192;  // chunks up to this length stay in shared memory in the local-minimum and allocation-free kernels
 constexpr int kBaseSmemMaxTokens = 49152;  // one-CTA-per-chunk kernel: longest chunk held in (dynamic) shared memory, 4 bytes per slot

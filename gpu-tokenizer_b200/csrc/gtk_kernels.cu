@@ -1770,7 +1770,10 @@ __device__ __forceinline__ void opt_tile(OptSmem& S, const EncodeBuffers& b, con
 
 // Six CTAs per SM (40 registers per thread) measured faster than eight (32 registers, 120 bytes of spills): the
 // shared memory the two missing CTAs leave free becomes L1 for the table probes.
-__global__ void __launch_bounds__(kOptThreads, 6) k_merge_opt(EncodeBuffers b, DeviceTable T)
+#ifndef GTK_OPT_CTAS
+#define GTK_OPT_CTAS 6
+#endif
+__global__ void __launch_bounds__(kOptThreads, GTK_OPT_CTAS) k_merge_opt(EncodeBuffers b, DeviceTable T)
 {
   OptSmem& S = g_tile;
   const int tid   = threadIdx.x;
