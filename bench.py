@@ -634,10 +634,10 @@ def main() -> None:
     extras = not args.no_extras and args.workload == "cfg2" and not args.bytes and args.mode == "opt"
     del dev["coff"]
     pin.free()
-    if world == 1 and args.workload == "cfg3" and not extras:
+    if world == 1 and args.workload == "cfg3" and not extras and args.latency_calls > 0:
         latency = latency_run(hx, MERGES, args.latency_calls)
     if extras and world == 1:
-        latency = latency_run(hx, MERGES, args.latency_calls)
+        latency = latency_run(hx, MERGES, args.latency_calls) if args.latency_calls > 0 else None
         configs = {}
         for name, k in (("cfg1", 10), ("cfg3", 10), ("cfg4", 5), ("cfg5", 3)):
             configs[name] = sub_config_run(hx, name, MERGES, k)

@@ -321,8 +321,10 @@ void run_front(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* lau
 {
   cudaStream_t s = h->stream;
   if (!ev) ev = h->ev;
-  GTK_CUDA(cudaMemsetAsync(b.counters, 0, 64, s));
-  GTK_CUDA(cudaMemsetAsync(b.chunk_cnt, 0, size_t(b.chunk_cap + 1) * 4, s));
+  if (!gtk::chunker_resets_counters(b)) {
+    GTK_CUDA(cudaMemsetAsync(b.counters, 0, 64, s));
+    GTK_CUDA(cudaMemsetAsync(b.chunk_cnt, 0, size_t(b.chunk_cap + 1) * 4, s));
+  }
   GTK_CUDA(cudaEventRecord(ev[0], s));
   *launches += gtk::launch_chunker(b, s);
   GTK_CUDA(cudaEventRecord(ev[1], s));

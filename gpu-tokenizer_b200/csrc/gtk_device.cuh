@@ -97,6 +97,7 @@ struct EncodeBuffers {
 
 // Launchers (all asynchronous on `stream`; return the number of kernels launched).
 int launch_chunker(const EncodeBuffers& b, cudaStream_t stream);
+bool chunker_resets_counters(const EncodeBuffers& b);
 int launch_merge_opt(const EncodeBuffers& b, const DeviceTable& t, int grid, cudaStream_t stream);
 int launch_merge_base(const EncodeBuffers& b, const DeviceTable& t, int grid, int block_threads, cudaStream_t stream);
 int launch_merge_wide(const EncodeBuffers& b, const DeviceTable& t, int grid, cudaStream_t stream);

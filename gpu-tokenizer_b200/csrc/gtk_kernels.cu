@@ -38,7 +38,7 @@ namespace gtk {
 namespace {
 
 #ifdef GTK_PHASE_TIMING
-__device__ unsigned long long g_phase_cycles[24];
+__device__ unsigned long long g_phase_cycles[32];
 #endif
 
 // Checked build (-DGTK_CHECKED): every index into shared memory, the lane scratch, the staging buffer and the
@@ -770,7 +770,9 @@ struct ChunksPerText {
   __device__ int64_t operator()(int64_t i) const
   {
     const int64_t len = off[i + 1] - off[i];
-    return len <= 0 ? 0 : (len + chunk - 1) / chunk;
+    if (len <= 0) return 0;
+    if (len < (int64_t(1) << 31)) return int64_t((uint32_t(len) + uint32_t(chunk) - 1u) / uint32_t(chunk));  // the usual case, a 32-bit division
+    return (len + chunk - 1) / chunk;
   }
 };
 
@@ -1821,36 +1823,39 @@ __device__ int64_t cta_exclusive_scan(F f, int64_t n, int64_t* out, int* scanbuf
   return total;
 }
 
-// the same with 16 consecutive items per thread and round (4096 items per round): the scans of a medium batch
+// The scans of a medium batch, one CTA of kMediumThreads: rounds of four items per thread.  The items are
+// evaluated in lane order (coalesced loads) into shared memory and scanned in blocks of four per thread (each
+// thread then writes 32 contiguous bytes of offsets).
+constexpr int kMediumThreads = 1024;  // more warps hide the latency of the dependent loads of a single CTA
 template <class F>
-__device__ int64_t cta_exclusive_scan16(F f, int64_t n, int64_t* out, int* scanbuf, int64_t* carry_s)
+__device__ int64_t cta_exclusive_scan_medium(F f, int64_t n, int64_t* out, int* scanbuf, int64_t* carry_s, int* stage)
 {
-  constexpr int E = 16;
-  if (threadIdx.x == 0) *carry_s = 0;
+  constexpr int E = 4;
+  const int tid = threadIdx.x;
+  if (tid == 0) *carry_s = 0;
   __syncthreads();
-  for (int64_t base = 0; base < n; base += int64_t(kOptThreads) * E) {
-    const int64_t first = base + int64_t(threadIdx.x) * E;
-    int v[E];
-    int s = 0;
+  for (int64_t base = 0; base < n; base += int64_t(kMediumThreads) * E) {
 #pragma unroll
     for (int e = 0; e < E; ++e) {
-      v[e] = (first + e < n) ? int(f(first + e)) : 0;
-      s += v[e];
-    }
-    int total;
-    const int off = block_exclusive_scan(s, scanbuf, &total);
-    int64_t run   = *carry_s + off;
-#pragma unroll
-    for (int e = 0; e < E; ++e) {
-      if (first + e < n) out[first + e] = run;
-      run += v[e];
+      const int64_t i = base + e * kMediumThreads + tid;
+      stage[e * kMediumThreads + tid] = (i < n) ? int(f(i)) : 0;
     }
     __syncthreads();
-    if (threadIdx.x == 0) *carry_s += total;
+    const int4 v = reinterpret_cast<const int4*>(stage)[tid];
+    int total;
+    const int off       = block_exclusive_scan(v.x + v.y + v.z + v.w, scanbuf, &total);
+    const int64_t first = base + int64_t(tid) * E;
+    const int64_t r0    = *carry_s + off;
+    const int64_t r[4]  = {r0, r0 + v.x, r0 + v.x + v.y, r0 + v.x + v.y + v.z};
+#pragma unroll
+    for (int e = 0; e < E; ++e)
+      if (first + e < n) out[first + e] = r[e];
+    __syncthreads();
+    if (tid == 0) *carry_s += total;
     __syncthreads();
   }
   const int64_t total = *carry_s;
-  if (threadIdx.x == 0) out[n] = total;
+  if (tid == 0) out[n] = total;
   __syncthreads();
   return total;
 }
@@ -1858,30 +1863,97 @@ __device__ int64_t cta_exclusive_scan16(F f, int64_t n, int64_t* out, int* scanb
 // Medium batches (a few thousand texts, chunks and tiles at most): the whole chunker in one single-CTA launch
 // instead of five, and both output scans plus the text offsets in one instead of seven -- at these sizes the
 // launches, not the work, are what the multi-block kernels cost.
-constexpr int64_t kMediumMaxItems = 8192;
+constexpr int64_t kMediumMaxItems = 16384;
 
-__global__ void __launch_bounds__(kOptThreads) k_chunker_medium(EncodeBuffers b)
+__global__ void __launch_bounds__(kMediumThreads) k_chunker_medium(EncodeBuffers b, int per_text)
 {
   __shared__ int scanbuf[33];
   __shared__ int64_t carry_s;
-  const int tid   = threadIdx.x;
-  const int64_t C = cta_exclusive_scan16(ChunksPerText{b.text_off, b.chunk_bytes}, b.n_texts, b.text_chunk_base,
-                                         scanbuf, &carry_s);
+  __shared__ __align__(16) int stage[4 * kMediumThreads];
+  const int tid = threadIdx.x;
+#ifdef GTK_PHASE_TIMING
+  const long long m_t0 = clock64();
+#endif
+  // this launch also resets the call's counters and per-chunk counts (two memsets less on the host)
+  if (tid < 16) b.counters[tid] = 0;
+  for (int64_t c = tid; c <= b.chunk_cap; c += kMediumThreads) b.chunk_cnt[c] = 0;
+  const int64_t C = cta_exclusive_scan_medium(ChunksPerText{b.text_off, b.chunk_bytes}, b.n_texts, b.text_chunk_base,
+                                              scanbuf, &carry_s, stage);
+#ifdef GTK_PHASE_TIMING
+  if (tid == 0) g_phase_cycles[24] = (unsigned long long)(clock64() - m_t0);
+#endif
   if (tid == 0) b.totals[0] = C;
-  for (int64_t c = tid; c <= C; c += kOptThreads) {
-    if (c == C) {
-      b.chunk_off[c] = b.text_off[b.n_texts];
-      continue;
+  if (per_text) {
+    // many short texts: every text writes the offsets of its own chunks and the first chunk of every tile that
+    // starts inside one of them (no search); a thread takes the texts of up to 32 chunks, a warp the longer ones.
+    // A medium batch has at most 2048 tiles, so byte offsets and chunk numbers fit 32 bits.
+    constexpr int kLongTexts = 128;
+    __shared__ int n_long;
+    __shared__ int long_text[kLongTexts];
+    const uint32_t cb = uint32_t(b.chunk_bytes);
+    auto lay_chunk = [&](uint32_t c, uint32_t start, uint32_t end) {  // chunk c covers bytes [start, end)
+      b.chunk_off[c] = start;
+      for (uint32_t k = (start + kTile - 1) / kTile; k * kTile < end; ++k) b.tile_chunk0[k] = int32_t(c);
+    };
+    if (tid == 0) {
+      b.chunk_off[C] = b.text_off[b.n_texts];
+      n_long         = 0;
     }
-    int64_t lo = 0, hi = b.n_texts;  // last t with text_chunk_base[t] <= c
-    while (hi - lo > 1) {
-      const int64_t mid = (lo + hi) >> 1;
-      if (b.text_chunk_base[mid] <= c) lo = mid; else hi = mid;
+    __syncthreads();
+    for (int64_t t = tid; t < b.n_texts; t += kMediumThreads) {
+      const uint32_t c0 = uint32_t(b.text_chunk_base[t]), nc = uint32_t(b.text_chunk_base[t + 1]) - c0;
+      const uint32_t at = uint32_t(b.text_off[t]), to = uint32_t(b.text_off[t + 1]);
+      if (nc == 1) {
+        lay_chunk(c0, at, to);
+      } else if (nc <= 32) {
+        for (uint32_t c = 0; c < nc; ++c) lay_chunk(c0 + c, at + c * cb, min(at + (c + 1) * cb, to));
+      } else {
+        const int q = atomicAdd(&n_long, 1);
+        if (q < kLongTexts) long_text[q] = int(t);
+      }
     }
-    b.chunk_off[c] = b.text_off[lo] + (c - b.text_chunk_base[lo]) * int64_t(b.chunk_bytes);
+    __syncthreads();
+#ifdef GTK_PHASE_TIMING
+    if (tid == 0) g_phase_cycles[25] = (unsigned long long)(clock64() - m_t0);
+#endif
+    const int lane = tid & 31, warp = tid >> 5;
+    if (n_long <= kLongTexts) {  // the usual case: the few long texts come from the list
+      for (int q = warp; q < n_long; q += kMediumThreads / 32) {
+        const int64_t t   = long_text[q];
+        const uint32_t cc = uint32_t(b.text_chunk_base[t]), nn = uint32_t(b.text_chunk_base[t + 1]) - cc;
+        const uint32_t at = uint32_t(b.text_off[t]), to = uint32_t(b.text_off[t + 1]);
+        for (uint32_t c = lane; c < nn; c += 32) lay_chunk(cc + c, at + c * cb, min(at + (c + 1) * cb, to));
+      }
+      return;
+    }
+    for (int64_t t0 = int64_t(warp) * 32; t0 < b.n_texts; t0 += kMediumThreads) {
+      const int64_t t   = t0 + lane;
+      const uint32_t c0 = (t < b.n_texts) ? uint32_t(b.text_chunk_base[t]) : 0u;
+      const uint32_t nc = (t < b.n_texts) ? uint32_t(b.text_chunk_base[t + 1]) - c0 : 0u;
+      for (uint32_t m = __ballot_sync(0xFFFFFFFFu, nc > 32); m; m &= m - 1) {
+        const int src     = __ffs(int(m)) - 1;
+        const uint32_t cc = __shfl_sync(0xFFFFFFFFu, c0, src), nn = __shfl_sync(0xFFFFFFFFu, nc, src);
+        const uint32_t at = uint32_t(b.text_off[t0 + src]), to = uint32_t(b.text_off[t0 + src + 1]);
+        for (uint32_t c = lane; c < nn; c += 32) lay_chunk(cc + c, at + c * cb, min(at + (c + 1) * cb, to));
+      }
+    }
+    return;
+  } else {
+    for (int64_t c = tid; c <= C; c += kMediumThreads) {
+      if (c == C) {
+        b.chunk_off[c] = b.text_off[b.n_texts];
+        continue;
+      }
+      int64_t lo = 0, hi = b.n_texts;  // last t with text_chunk_base[t] <= c
+      while (hi - lo > 1) {
+        const int64_t mid = (lo + hi) >> 1;
+        if (b.text_chunk_base[mid] <= c) lo = mid; else hi = mid;
+      }
+      b.chunk_off[c] = b.text_off[lo] + (c - b.text_chunk_base[lo]) * int64_t(b.chunk_bytes);
+    }
   }
   __syncthreads();
-  for (int64_t k = tid; k < b.n_tiles; k += kOptThreads) {
+  for (int64_t k = tid; k < b.n_tiles; k += kMediumThreads) {
     const int64_t pos = k * kTile;
     int64_t lo = 0, hi = C;  // last c with chunk_off[c] <= pos
     while (hi - lo > 1) {
@@ -1892,17 +1964,18 @@ __global__ void __launch_bounds__(kOptThreads) k_chunker_medium(EncodeBuffers b)
   }
 }
 
-__global__ void __launch_bounds__(kOptThreads) k_scans_medium(EncodeBuffers b, int with_units)
+__global__ void __launch_bounds__(kMediumThreads) k_scans_medium(EncodeBuffers b, int with_units)
 {
   __shared__ int scanbuf[33];
   __shared__ int64_t carry_s;
+  __shared__ __align__(16) int stage[4 * kMediumThreads];
   const int tid   = threadIdx.x;
   const int64_t C = b.totals[0];
-  const int64_t N = cta_exclusive_scan16(CountsI32{b.chunk_cnt}, C, b.chunk_id_off, scanbuf, &carry_s);
+  const int64_t N = cta_exclusive_scan_medium(CountsI32{b.chunk_cnt}, C, b.chunk_id_off, scanbuf, &carry_s, stage);
   if (tid == 0) b.totals[1] = N;
-  if (with_units) cta_exclusive_scan16(CountsI32{b.unit_cnt}, b.n_tiles, b.unit_base, scanbuf, &carry_s);
+  if (with_units) cta_exclusive_scan_medium(CountsI32{b.unit_cnt}, b.n_tiles, b.unit_base, scanbuf, &carry_s, stage);
   if (b.text_id_off)
-    for (int64_t t = tid; t <= b.n_texts; t += kOptThreads) b.text_id_off[t] = b.chunk_id_off[b.text_chunk_base[t]];
+    for (int64_t t = tid; t <= b.n_texts; t += kMediumThreads) b.text_id_off[t] = b.chunk_id_off[b.text_chunk_base[t]];
 }
 
 __global__ void __launch_bounds__(kOptThreads) k_encode_small(EncodeBuffers b, DeviceTable T)
@@ -2295,15 +2368,28 @@ static bool medium_scans(const EncodeBuffers& b)
 {
   return b.n_texts <= kMediumMaxItems && b.chunk_cap <= kMediumMaxItems && b.n_tiles <= kMediumMaxItems;
 }
-static bool medium_chunker(const EncodeBuffers& b)
+// The single-CTA chunker finds the text of every chunk by binary search, which is cheap for a few texts and a few
+// thousand chunks; a batch of many short texts (no more chunk-sized pieces than texts) is laid out per text instead.
+static bool medium_chunker_by_search(const EncodeBuffers& b)
 {
   return b.n_texts <= 256 && b.chunk_cap <= 2048 && b.n_tiles <= 1024;
+}
+static bool medium_chunker_per_text(const EncodeBuffers& b)
+{
+  return b.n_texts <= kMediumMaxItems && b.chunk_cap <= kMediumMaxItems && b.n_tiles <= 2048 &&
+         b.chunk_cap <= 2 * b.n_texts + 1;
+}
+
+// true when the chunker is the single-CTA kernel, which also resets counters[0..16) and chunk_cnt[0..chunk_cap]
+bool chunker_resets_counters(const EncodeBuffers& b)
+{
+  return medium_chunker_by_search(b) || medium_chunker_per_text(b);
 }
 
 int launch_chunker(const EncodeBuffers& b, cudaStream_t stream)
 {
-  if (medium_chunker(b)) {
-    k_chunker_medium<<<1, kOptThreads, 0, stream>>>(b);
+  if (medium_chunker_by_search(b) || medium_chunker_per_text(b)) {
+    k_chunker_medium<<<1, kMediumThreads, 0, stream>>>(b, medium_chunker_by_search(b) ? 0 : 1);
     return 1;
   }
   int launches = run_scan(ChunksPerText{b.text_off, b.chunk_bytes}, b.n_texts, b.n_texts, nullptr,
@@ -2406,7 +2492,7 @@ int launch_merge_localmin(const EncodeBuffers& b, const DeviceTable& t, int grid
 int launch_output_scans(const EncodeBuffers& b, int mode_base, cudaStream_t stream)
 {
   if (medium_scans(b)) {
-    k_scans_medium<<<1, kOptThreads, 0, stream>>>(b, (!mode_base && b.n_tiles > 0) ? 1 : 0);
+    k_scans_medium<<<1, kMediumThreads, 0, stream>>>(b, (!mode_base && b.n_tiles > 0) ? 1 : 0);
     return 1;
   }
   int launches = 0;
@@ -2474,12 +2560,12 @@ extern "C" __attribute__((visibility("default"))) int gtk_debug_check_words(int 
 #endif
 
 #ifdef GTK_PHASE_TIMING
-extern "C" __attribute__((visibility("default"))) void gtk_debug_phase_cycles(unsigned long long out[24], int reset)
+extern "C" __attribute__((visibility("default"))) void gtk_debug_phase_cycles(unsigned long long out[32], int reset)
 {
   cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out, g_phase_cycles, sizeof(unsigned long long) * 24);
+  cudaMemcpyFromSymbol(out, g_phase_cycles, sizeof(unsigned long long) * 32);
   if (reset) {
-    unsigned long long z[24] = {};
+    unsigned long long z[32] = {};
     cudaMemcpyToSymbol(g_phase_cycles, z, sizeof(z));
   }
 }
