@@ -173,7 +173,7 @@ def test_config5_lognormal_chunks(lib, merges_path, oracle):
 
 
 def test_sliced_host_path_boundaries(lib, merges_path, oracle):
-    """Host batches above 24 MiB are cut into overlapped slices: texts that span slices, empty texts
+    """Host batches of 8 MiB and more are cut into overlapped slices: texts that span slices, empty texts
     at slice edges and a chunk size that divides nothing must give the unsliced result."""
     lens = [30 * (1 << 20) + 11, 0, 5 << 20, 100, 17 * (1 << 20) + 3, 0, 1, 0]
     toff_in = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
@@ -210,8 +210,8 @@ def test_adversarial_long_segments(lib, merges_path, oracle):
 
 
 def test_long_and_huge_segments_in_a_large_batch(lib, merges_path, oracle):
-    """Large batches run the split pipeline (queues + separate kernels for short, long and huge
-    segments): segments of every class, including ones far longer than a tile, inside 12 MiB."""
+    """Segments of every class -- one thread's, a warp's, and ones far longer than a tile that the whole CTA
+    finishes in the workspace -- inside a 12 MiB host batch (which the host path cuts into slices)."""
     rng = np.random.default_rng(3)
     filler = lib.TextGen(8).text(12 << 20, mix=lib.MIX_STRESS).copy()
     inserts = [b"a" * 65536, b"ab" * 1500, ("\u65e5" * 900).encode(), b"e" * 2048, b"e" * 2049, b"l" * 33, b"s" * 32,
