@@ -300,6 +300,50 @@ def test_random_small_batches(lib, merges_path, oracle):
     assert np.array_equal(toff, woff[starts])
 
 
+def test_medium_batches_of_many_short_texts(lib, merges_path, oracle):
+    """Batches of thousands of short texts, which the single-CTA chunker lays out per text: only one-chunk and
+    empty texts; a few texts of more than 32 chunks among them (one warp each, from the list in shared
+    memory); more such texts than that list holds (the scan over all texts).  Host and device-resident entry."""
+    import torch
+
+    rng = np.random.default_rng(31)
+    src = lib.TextGen(6).text(2 << 20, mix=lib.MIX_STRESS)
+    cases = []
+    lens = rng.integers(0, 100, size=9000)
+    lens[::53] = 0
+    cases.append(("short only", 2048, lens))
+    lens = rng.integers(0, 60, size=5000)
+    lens[[7, 2500, 4999]] = [64 * 40 + 3, 64 * 33, 64 * 200 + 1]
+    cases.append(("a few long texts", 64, lens))
+    lens = np.full(7000, 4)
+    lens[rng.choice(7000, size=140, replace=False)] = 16 * 34 - 5
+    cases.append(("more long texts than the list holds", 16, lens))
+    for what, chunk, lens in cases:
+        toff_in = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+        n = int(toff_in[-1])
+        assert n // chunk <= len(lens) and n > 32768           # the shape the per-text layout is chosen for
+        data = src[:n]
+        chunk_off = [0]
+        for s, e in zip(toff_in[:-1], toff_in[1:]):
+            chunk_off.extend(list(range(int(s) + chunk, int(e), chunk)) + ([int(e)] if e > s else []))
+        chunk_off = np.array(chunk_off, np.int64)
+        want, woff = oracle.encode_chunks(data, chunk_off, mode=MODE_SEGMENTED, threads=NCPU)
+        starts = np.searchsorted(chunk_off, toff_in, side="left")
+        t = make_tok(lib, merges_path, chunk)
+        ids, toff, coff, _ = t.encode(data, toff_in)
+        check_chunks(ids, coff, want, woff, what)
+        assert np.array_equal(toff, woff[starts]), what
+        d_bytes, d_toff = torch.from_numpy(data.copy()).cuda(), torch.from_numpy(toff_in).cuda()
+        d_ids = torch.empty(n, dtype=torch.int32, device="cuda")
+        d_coff = torch.empty(len(chunk_off) + 8, dtype=torch.int64, device="cuda")
+        n_ids, n_chunks, _ = t.encode_device(d_bytes.data_ptr(), n, d_toff.data_ptr(), len(lens), d_ids.data_ptr(), n,
+                                             d_coff.data_ptr(), d_coff.numel())
+        assert n_chunks == len(woff) - 1 and n_ids == len(want), what
+        assert np.array_equal(d_ids[:n_ids].cpu().numpy(), want), what
+        assert np.array_equal(d_coff[:n_chunks + 1].cpu().numpy(), woff), what
+        assert t.stage_ms()["kernel_launches"] == 4, what        # chunker, merge, scans, pack: one launch each
+
+
 def test_generated_adversarial_strings(lib, merges_path, oracle):
     """Seeded adversarial strings (runs, tiny alphabets, arbitrary bytes, multi-byte characters, empty) in
     batches that take the single-kernel small path and the multi-kernel path, at several chunk sizes."""
