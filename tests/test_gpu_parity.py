@@ -344,6 +344,62 @@ def test_medium_batches_of_many_short_texts(lib, merges_path, oracle):
         assert t.stage_ms()["kernel_launches"] == 4, what        # chunker, merge, scans, pack: one launch each
 
 
+def test_path_selector_boundaries(lib, merges_path, oracle):
+    """Batches on both sides of every size limit that picks a code path: the single-CTA chunker by search (256
+    texts, 2048 chunks, 1024 tiles) and per text (16 384 items, 2048 tiles), the single-CTA scans (16 384 items), the
+    small-batch kernel (32 KiB, 1024 texts) and the sliced host path (8 MiB).  Host and device-resident entry."""
+    import torch
+
+    src = lib.TextGen(8).text(9 << 20, mix=lib.MIX_STRESS)
+
+    def check(what, chunk, lens, host=True):
+        lens = np.asarray(lens, dtype=np.int64)
+        toff_in = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+        n = int(toff_in[-1])
+        data = src[:n]
+        ends = toff_in[1:]
+        inner = [np.arange(s + chunk, e, chunk) for s, e in zip(toff_in[:-1], ends) if e - s > chunk]
+        chunk_off = np.unique(np.concatenate([[0], ends[lens > 0]] + inner)).astype(np.int64)
+        want, woff = oracle.encode_chunks(data, chunk_off, mode=MODE_SEGMENTED, threads=NCPU)
+        starts = np.searchsorted(chunk_off, toff_in, side="left")
+        t = make_tok(lib, merges_path, chunk)
+        if host:
+            ids, toff, coff, _ = t.encode(data, toff_in)
+            check_chunks(ids, coff, want, woff, what + " (host)")
+            assert np.array_equal(toff, woff[starts]), what
+        d_bytes, d_toff = torch.from_numpy(data.copy()).cuda(), torch.from_numpy(toff_in).cuda()
+        d_ids = torch.empty(n, dtype=torch.int32, device="cuda")
+        d_coff = torch.empty(len(chunk_off) + 8, dtype=torch.int64, device="cuda")
+        n_ids, n_chunks, _ = t.encode_device(d_bytes.data_ptr(), n, d_toff.data_ptr(), len(lens), d_ids.data_ptr(), n,
+                                             d_coff.data_ptr(), d_coff.numel())
+        assert n_chunks == len(woff) - 1 and n_ids == len(want), what
+        assert np.array_equal(d_ids[:n_ids].cpu().numpy(), want), what
+        assert np.array_equal(d_coff[:n_chunks + 1].cpu().numpy(), woff), what
+        return t.stage_ms()["kernel_launches"]
+
+    # chunker by search: 256 / 257 texts of ~3 chunks; 2048 / 2049 as the bound on chunks; 1024 / 1025 tiles
+    assert check("256 texts", 512, [1300] * 256) == 4
+    assert check("257 texts", 512, [1300] * 257) > 4
+    assert check("chunk bound 2048", 512, [2046 * 512]) == 4
+    assert check("chunk bound 2049", 512, [2047 * 512]) > 4
+    assert check("1024 tiles", 4096, [1024 * 4096]) == 4
+    assert check("1025 tiles", 4096, [1024 * 4096 + 1]) >= 4
+    # chunker per text and the scans: the bound on chunks (bytes / chunk + texts + 1) at 16 384 / 16 386
+    assert check("16 376 as the chunk bound", 128, [3] * 16000) == 4
+    assert check("16 386 as the chunk bound", 128, [3] * 16010) > 4
+    # per text: 2048 / 2049 tiles (8 MiB: device-resident entry only, the host entry slices such a batch)
+    assert check("2048 tiles, many texts", 4096, [1024] * 8192, host=False) == 4
+    assert check("2049 tiles, many texts", 4096, [1024] * 8192 + [1], host=False) > 4
+    # small-batch kernel: 32 KiB / one byte more; 1024 / 1025 texts
+    check("32 KiB", 2048, [32768])
+    check("32 KiB + 1", 2048, [32769])
+    check("1024 texts", 2048, [20] * 1024)
+    check("1025 texts", 2048, [20] * 1025)
+    # sliced host path: one byte below and at 8 MiB
+    check("8 MiB - 1", 4096, [(8 << 20) - 1])
+    check("8 MiB", 4096, [8 << 20])
+
+
 def test_generated_adversarial_strings(lib, merges_path, oracle):
     """Seeded adversarial strings (runs, tiny alphabets, arbitrary bytes, multi-byte characters, empty) in
     batches that take the single-kernel small path and the multi-kernel path, at several chunk sizes."""
