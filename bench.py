@@ -311,9 +311,12 @@ class Harness:
         return [float(t.item()) for t in every]
 
 
-def device_resident_run(hx: Harness, tok, data, text_off, chunk, mode, steps, warmup):
-    """Text in HBM before the timed region; K steps bracketed by barriers, CUDA events on the launching stream."""
+def device_resident_run(hx: Harness, tok, data, text_off, chunk, mode, steps, warmup, per_stage=True):
+    """Text in HBM before the timed region; K steps bracketed by barriers, CUDA events on the launching stream.
+    per_stage: the library records events between its stages too (the merge kernel's own time, for the roofline);
+    without it only the pipeline as a whole is timed, which is the library's default."""
     torch = hx.torch
+    tok.set_stage_timing(per_stage)
     n_bytes, n_texts = len(data), len(text_off) - 1
     with torch.cuda.stream(hx.stream):
         d_bytes = torch.from_numpy(data).cuda()
@@ -345,6 +348,7 @@ def device_resident_run(hx: Harness, tok, data, text_off, chunk, mode, steps, wa
     hx.barrier()
     wall_ms = (time.perf_counter() - t0) * 1e3
     dev_ms = ev0.elapsed_time(ev1)  # CUDA events on the stream the kernels run on
+    tok.set_stage_timing(False)
     with torch.cuda.stream(hx.stream):
         coff = d_coff[:n_chunks + 1].cpu().numpy()
     return {"ms_per_step": dev_ms / steps, "wall_ms_per_step": wall_ms / steps, "n_ids": int(n_ids),
@@ -465,7 +469,9 @@ def sub_config_run(hx: Harness, name: str, merges, steps: int):
     data, text_off, chunk, desc = make_workload(name, 0, 1, None)
     tok = gputok_b200.Tokenizer(merges, chunk_tokens=chunk, device=hx.torch.cuda.current_device())
     tok.set_stream(hx.stream.cuda_stream)
-    dev = device_resident_run(hx, tok, data, text_off, chunk, gputok_b200.GTK_MODE_OPT, steps, 3)
+    # timed as a caller gets it (the pipeline as a whole); the stage breakdown comes from a second, shorter pass
+    dev = device_resident_run(hx, tok, data, text_off, chunk, gputok_b200.GTK_MODE_OPT, steps, 3, per_stage=False)
+    dev["stage_ms"] = device_resident_run(hx, tok, data, text_off, chunk, gputok_b200.GTK_MODE_OPT, 3, 1)["stage_ms"]
     pin = PinnedArray(len(data))
     pin.array[:] = data
     e2e_ms, h2d, d2h, _ = e2e_run(hx, tok, pin, text_off, gputok_b200.GTK_MODE_OPT, max(2, steps))

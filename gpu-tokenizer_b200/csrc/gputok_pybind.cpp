@@ -187,6 +187,8 @@ class GpuTokenizer {
     return d;
   }
 
+  void set_stage_timing(bool per_stage) { check(gtk_set_stage_timing(h_, per_stage ? 1 : 0)); }
+
   py::dict stage_ms() const
   {
     float ms[5];
@@ -236,5 +238,9 @@ PYBIND11_MODULE(gputok_gpu, m)
          "Returns (ids int32[N], text_offsets int64[T+1], chunk_offsets int64[C+1], kernel_time_ms).")
     .def("decode", &GpuTokenizer::decode, py::arg("ids"))
     .def("table_info", &GpuTokenizer::table_info)
-    .def("stage_ms", &GpuTokenizer::stage_ms);
+    .def("stage_ms", &GpuTokenizer::stage_ms)
+    .def("set_stage_timing", [](GpuTokenizer& self, bool per_stage) { self.set_stage_timing(per_stage); },
+         py::arg("per_stage"),
+         "Time every stage of a batch (stage_ms()['chunker'/'merge'/'scan'/'pack']) instead of the pipeline as a\n"
+         "whole; off by default.");
 }

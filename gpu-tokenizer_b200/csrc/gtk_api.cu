@@ -133,6 +133,8 @@ struct gtk_tokenizer {
   int sm_count = 0;
   int opt_grid = 0, base_grid = 0, localmin_grid = 0, wide_grid = 0;
   int base_block = 0;  // threads per CTA of the one-CTA-per-chunk kernel, 0 = from the chunk size
+  bool stage_timing = false;  // events between the stages of a batch that runs in one piece (gtk_set_stage_timing)
+  float front_ms = -1.f;      // chunker + merge + scans of the last such batch when timed as one interval
   bool wide = false;  // ids or ranks beyond 16 bits: every GPU mode runs the 32-bit one-CTA-per-chunk kernel
   cudaStream_t stream = nullptr;      // stream in use
   cudaStream_t own_stream = nullptr;  // created by gtk_create
@@ -320,6 +322,7 @@ void run_front(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* lau
                int64_t* pinned_totals = nullptr, int64_t* mapped_totals = nullptr)
 {
   cudaStream_t s = h->stream;
+  const bool stages = ev != nullptr || h->stage_timing;  // sliced batches always time their stages
   if (!ev) ev = h->ev;
   if (!gtk::chunker_resets_counters(b)) {
     GTK_CUDA(cudaMemsetAsync(b.counters, 0, 64, s));
@@ -327,12 +330,12 @@ void run_front(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* lau
   }
   GTK_CUDA(cudaEventRecord(ev[0], s));
   *launches += gtk::launch_chunker(b, s);
-  GTK_CUDA(cudaEventRecord(ev[1], s));
+  if (stages) GTK_CUDA(cudaEventRecord(ev[1], s));
   if (h->wide) *launches += gtk::launch_merge_wide(b, h->dtab, h->wide_grid, s);
   else if (mode == GTK_MODE_BASE) *launches += gtk::launch_merge_base(b, h->dtab, h->base_grid, h->base_block, s);
   else if (mode == GTK_MODE_LOCALMIN) *launches += gtk::launch_merge_localmin(b, h->dtab, h->localmin_grid, h->max_iters, s);
   else *launches += gtk::launch_merge_opt(b, h->dtab, h->opt_grid, s);
-  GTK_CUDA(cudaEventRecord(ev[2], s));
+  if (stages) GTK_CUDA(cudaEventRecord(ev[2], s));
   *launches += gtk::launch_output_scans(b, mode != GTK_MODE_OPT || h->wide, s);
   GTK_CUDA(cudaEventRecord(ev[3], s));
   GTK_CUDA(cudaGetLastError());
@@ -363,8 +366,15 @@ void run_pack(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* laun
 // soon after) and the pack events when its ids have arrived.
 void collect_front_times(gtk_tokenizer* h, cudaEvent_t* ev = nullptr)
 {
+  const bool stages = ev != nullptr || h->stage_timing;
   if (!ev) ev = h->ev;
   float ms = 0;
+  if (!stages) {  // chunker, merge and scans as one interval
+    GTK_CUDA(cudaEventElapsedTime(&ms, ev[0], ev[3]));
+    h->front_ms = ms;
+    return;
+  }
+  h->front_ms = -1.f;
   for (int i = 0; i < 3; ++i) {
     GTK_CUDA(cudaEventElapsedTime(&ms, ev[i], ev[i + 1]));
     h->stage_ms[i] += ms;
@@ -376,8 +386,12 @@ void collect_pack_time(gtk_tokenizer* h, cudaEvent_t* ev = nullptr)
   if (!ev) ev = h->ev;
   float ms = 0;
   GTK_CUDA(cudaEventElapsedTime(&ms, ev[5], ev[4]));
-  h->stage_ms[3] += ms;
   // the pipeline time excludes the host round trip between scans and pack
+  if (h->front_ms >= 0.f) {
+    h->stage_ms[4] = h->front_ms + ms;
+    return;
+  }
+  h->stage_ms[3] += ms;
   h->stage_ms[4] = h->stage_ms[0] + h->stage_ms[1] + h->stage_ms[2] + h->stage_ms[3];
 }
 
@@ -937,6 +951,7 @@ GTK_API int gtk_encode_device(gtk_tokenizer* h, int mode, const uint8_t* d_bytes
   if (kernel_ms) *kernel_ms = 0.f;
   h->last_launches = 0;
   std::fill(h->stage_ms, h->stage_ms + 5, 0.f);
+  h->front_ms = -1.f;
   if (n_texts == 0 || n_bytes == 0) return GTK_OK;
   if (!d_bytes || !d_text_offsets || !d_out_ids) return h->fail(GTK_ERR_INVALID_ARG, "null device pointer");
   if (h->wide && mode == GTK_MODE_LOCALMIN) return h->fail(GTK_ERR_TABLE, kWideNoLocalmin);
@@ -1001,6 +1016,7 @@ GTK_API int gtk_encode(gtk_tokenizer* h, int mode, const uint8_t* bytes, const i
   h->res_n_texts = n_texts;
   h->last_launches = 0;
   std::fill(h->stage_ms, h->stage_ms + 5, 0.f);
+  h->front_ms = -1.f;
   try {
     GTK_CUDA(cudaSetDevice(h->device));
     const int64_t n_bytes = n_texts ? text_offsets[n_texts] : 0;
@@ -1179,6 +1195,14 @@ GTK_API int gtk_set_stream(gtk_tokenizer* h, void* cuda_stream)
   cudaSetDevice(h->device);
   cudaStreamSynchronize(h->stream);
   h->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : h->own_stream;
+  return GTK_OK;
+}
+
+GTK_API int gtk_set_stage_timing(gtk_tokenizer* h, int per_stage)
+{
+  if (!h) return GTK_ERR_INVALID_ARG;
+  std::lock_guard<std::mutex> lock(h->mu);
+  h->stage_timing = per_stage != 0;
   return GTK_OK;
 }
 

@@ -75,6 +75,7 @@ def load_library() -> C.CDLL:
     lib.gtk_set_stream.argtypes = [vp, vp]
     lib.gtk_set_id_space.argtypes = [vp, C.c_int]
     lib.gtk_set_base_block_size.argtypes = [vp, C.c_int]
+    lib.gtk_set_stage_timing.argtypes = [vp, C.c_int]
     lib.gtk_write_token_strings.argtypes = [vp, C.c_char_p, vp, vp, i64]
     lib.gtk_encode_chunks_noalloc.argtypes = [vp, vp, i64, vp, i64, i32, vp, vp]
     lib.gtk_pinned_alloc.argtypes = [C.c_size_t]
@@ -176,6 +177,11 @@ class Tokenizer:
         """False (default): ids as the reference produces them (ids < 256 are byte values);
         True: ids < 256 remapped to GPT-2's own vocabulary order (feedable to a GPT-2 model)."""
         self._check(self._lib.gtk_set_id_space(self._h, 1 if gpt2 else 0))
+
+    def set_stage_timing(self, per_stage: bool) -> None:
+        """Time every stage of a batch that runs in one piece (chunker, merge, scans, pack in ``stage_ms()``) instead
+        of the pipeline as a whole; off by default because the extra events cost small calls about a tenth."""
+        self._check(self._lib.gtk_set_stage_timing(self._h, 1 if per_stage else 0))
 
     def set_base_block_size(self, threads: int) -> None:
         """Threads per CTA of the one-CTA-per-chunk kernel (GTK_MODE_BASE): 0 = one warp per KiB of chunk,

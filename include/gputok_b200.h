@@ -171,8 +171,14 @@ GTK_API int gtk_encode_device(gtk_tokenizer* h, int mode, const uint8_t* d_bytes
 
 /* Device time of the stages of the last GPU encode, in milliseconds:
  * [0] chunker, [1] merge kernel, [2] output scans, [3] pack, [4] whole pipeline.
- * Also the number of kernels launched by that call (for launch accounting). */
+ * Also the number of kernels launched by that call (for launch accounting).
+ * [4] is always measured (it is the kernel_ms the encode entry points return, the reference's one event pair,
+ * gputok_binding.cu:790-805).  [0]..[3] are measured for batches that the host path cuts into slices, and for
+ * batches that run in one piece only after gtk_set_stage_timing(h, 1); otherwise they are 0.  The events between
+ * the stages cost a call of a few hundred KiB to a few MiB about a tenth of its time, which is why they are off
+ * by default. */
 GTK_API int gtk_last_stage_ms(const gtk_tokenizer* h, float stage_ms[5], int32_t* kernel_launches);
+GTK_API int gtk_set_stage_timing(gtk_tokenizer* h, int per_stage);
 
 /* ids -> bytes (inverse of the byte encoder + merges); the token-string writer
  * of gputok_blockbpe.cu:841-865 builds on this.  *n_out receives the byte count. */

@@ -453,8 +453,14 @@ def test_device_resident_entry_point(lib, merges_path, oracle):
     assert n_chunks == 2048 and n_ids == len(want) and ms > 0
     assert np.array_equal(d_ids[:n_ids].cpu().numpy(), want)
     assert np.array_equal(d_coff[:n_chunks + 1].cpu().numpy(), woff)
+    st = t.stage_ms()                                     # by default only the pipeline as a whole is timed
+    assert st["kernel_launches"] >= 4 and st["merge"] == 0 and st["pipeline"] == pytest.approx(ms)
+    t.set_stage_timing(True)
+    _, _, ms2 = t.encode_device(d_bytes.data_ptr(), n, d_toff.data_ptr(), 1, d_ids.data_ptr(), n,
+                                d_coff.data_ptr(), d_coff.numel())
     st = t.stage_ms()
-    assert st["kernel_launches"] >= 5 and st["merge"] > 0
+    assert 0 < st["merge"] < st["pipeline"] == pytest.approx(ms2) and st["pack"] > 0 and st["chunker"] > 0
+    assert np.array_equal(d_ids[:n_ids].cpu().numpy(), want)
     with pytest.raises(lib.GtkError) as e:                # too small an id buffer is reported, not overrun
         t.encode_device(d_bytes.data_ptr(), n, d_toff.data_ptr(), 1, d_ids.data_ptr(), 1000)
     assert e.value.code == 4
@@ -661,6 +667,7 @@ def test_stage_times_of_a_sliced_batch(lib, merges_path):
     d_toff = torch.tensor([0, n], dtype=torch.int64, device="cuda")
     d_ids = torch.empty(n, dtype=torch.int32, device="cuda")
     torch.cuda.synchronize()
+    t.set_stage_timing(True)
     for _ in range(2):
         t.encode_device(d_bytes.data_ptr(), n, d_toff.data_ptr(), 1, d_ids.data_ptr(), n)
     whole = t.stage_ms()
