@@ -262,8 +262,7 @@ Plan plan_batch(gtk_tokenizer* h, const uint8_t* d_bytes, int64_t n_bytes, const
   if (want_text_id_off) h->d_text_id_off.reserve(size_t(n_texts + 1) * 8);
   const int64_t scan_items = std::max<int64_t>(std::max(chunk_cap, n_tiles), n_texts);
   h->d_scan_sums.reserve(size_t(scan_items / 4096 + 2) * 8);
-  h->d_counters.reserve(64);
-  h->d_totals.reserve(64);
+  h->d_totals.reserve(128);  // [0] n_chunks, [1] n_ids as int64, then the 16 int32 counters: one copy brings both
   // workspace for segments / chunks that do not fit in shared memory
   const int64_t longest = std::min<int64_t>(h->chunk_tokens, n_bytes);
   int64_t scratch_tokens = 0;
@@ -299,8 +298,8 @@ Plan plan_batch(gtk_tokenizer* h, const uint8_t* d_bytes, int64_t n_bytes, const
   b.staging32 = h->wide ? h->d_staging32.as<int32_t>() : nullptr;
   b.seg_scratch_tokens = scratch_tokens;
   b.scan_block_sums = h->d_scan_sums.as<int64_t>();
-  b.counters = h->d_counters.as<int32_t>();
   b.totals = h->d_totals.as<int64_t>();
+  b.counters = reinterpret_cast<int32_t*>(b.totals + 2);
   b.low_id_map = (h->id_space == GTK_IDS_GPT2) ? h->d_low_map.as<uint16_t>() : nullptr;
   return p;
 }
@@ -318,8 +317,10 @@ const char* status_text(int s)
 
 // Chunker -> merge -> scans.  Leaves totals (n_chunks, n_ids) and the status
 // word in the pinned totals buffer; the caller synchronises and then packs.
+// chained: the pack follows on the same stream without a host round trip, so that one event pair around both
+// times the pipeline when the stages are not timed one by one.
 void run_front(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* launches, cudaEvent_t* ev = nullptr,
-               int64_t* pinned_totals = nullptr, int64_t* mapped_totals = nullptr)
+               int64_t* pinned_totals = nullptr, int64_t* mapped_totals = nullptr, bool chained = false)
 {
   cudaStream_t s = h->stream;
   const bool stages = ev != nullptr || h->stage_timing;  // sliced batches always time their stages
@@ -337,23 +338,28 @@ void run_front(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* lau
   else *launches += gtk::launch_merge_opt(b, h->dtab, h->opt_grid, s);
   if (stages) GTK_CUDA(cudaEventRecord(ev[2], s));
   *launches += gtk::launch_output_scans(b, mode != GTK_MODE_OPT || h->wide, s);
-  GTK_CUDA(cudaEventRecord(ev[3], s));
+  if (stages || !chained) GTK_CUDA(cudaEventRecord(ev[3], s));
   GTK_CUDA(cudaGetLastError());
   if (mapped_totals) {  // one small kernel writes the four words into mapped host memory: no copy-engine round trips
     *launches += gtk::launch_publish_totals(b, mapped_totals, s);
     return;
   }
   int64_t* ht = pinned_totals ? pinned_totals : h->h_totals.as<int64_t>();
-  GTK_CUDA(cudaMemcpyAsync(ht, b.totals, 16, cudaMemcpyDeviceToHost, s));
-  GTK_CUDA(cudaMemcpyAsync(ht + 2, b.counters, 16, cudaMemcpyDeviceToHost, s));
+  if (reinterpret_cast<const int64_t*>(b.counters) == b.totals + 2) {  // adjacent: one copy
+    GTK_CUDA(cudaMemcpyAsync(ht, b.totals, 32, cudaMemcpyDeviceToHost, s));
+  } else {
+    GTK_CUDA(cudaMemcpyAsync(ht, b.totals, 16, cudaMemcpyDeviceToHost, s));
+    GTK_CUDA(cudaMemcpyAsync(ht + 2, b.counters, 16, cudaMemcpyDeviceToHost, s));
+  }
 }
 
 void run_pack(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* launches, cudaEvent_t* ev = nullptr,
-              cudaStream_t on = nullptr)
+              cudaStream_t on = nullptr, bool chained = false)
 {
   cudaStream_t s = on ? on : h->stream;
+  const bool stages = ev != nullptr || h->stage_timing;
   if (!ev) ev = h->ev;
-  GTK_CUDA(cudaEventRecord(ev[5], s));
+  if (stages || !chained) GTK_CUDA(cudaEventRecord(ev[5], s));
   if (h->wide) *launches += gtk::launch_pack_wide(b, h->sm_count * 8, s);
   else *launches += gtk::launch_pack(b, mode != GTK_MODE_OPT, h->sm_count * 8, s);
   GTK_CUDA(cudaEventRecord(ev[4], s));
@@ -395,8 +401,12 @@ void collect_pack_time(gtk_tokenizer* h, cudaEvent_t* ev = nullptr)
   h->stage_ms[4] = h->stage_ms[0] + h->stage_ms[1] + h->stage_ms[2] + h->stage_ms[3];
 }
 
-void collect_stage_times(gtk_tokenizer* h)
+void collect_stage_times(gtk_tokenizer* h, bool chained = false)
 {
+  if (chained && !h->stage_timing) {  // one event pair around the whole pipeline
+    GTK_CUDA(cudaEventElapsedTime(&h->stage_ms[4], h->ev[0], h->ev[4]));
+    return;
+  }
   collect_front_times(h);
   collect_pack_time(h);
 }
@@ -962,12 +972,12 @@ GTK_API int gtk_encode_device(gtk_tokenizer* h, int mode, const uint8_t* d_bytes
     if (chunk_dst && chunk_capacity < need_chunks + 1) chunk_dst = nullptr;  // scan into the arena, copy what fits
     Plan p = plan_batch(h, d_bytes, n_bytes, d_text_offsets, n_texts, d_out_ids, out_capacity, chunk_dst, false);
     int launches = 0;
-    run_front(h, p.b, mode, &launches);
     // When the chunk offsets are scanned straight into the caller's buffer (or not wanted), the pack follows
     // the front without a host round trip: the pack kernel itself never writes past out_capacity, and the
     // totals are checked once at the end.
     const bool one_sync = !d_out_chunk_offsets || chunk_dst;
-    if (one_sync) run_pack(h, p.b, mode, &launches);
+    run_front(h, p.b, mode, &launches, nullptr, nullptr, nullptr, one_sync);
+    if (one_sync) run_pack(h, p.b, mode, &launches, nullptr, nullptr, true);
     GTK_CUDA(cudaStreamSynchronize(h->stream));
     const int64_t* ht = h->h_totals.as<int64_t>();
     const int64_t C = ht[0], N = ht[1];
@@ -975,7 +985,7 @@ GTK_API int gtk_encode_device(gtk_tokenizer* h, int mode, const uint8_t* d_bytes
     if (status != gtk::kStatusOk) return h->fail(GTK_ERR_KERNEL, status_text(status));
     if (N > out_capacity) return h->fail(GTK_ERR_CAPACITY, "d_out_ids too small: need " + std::to_string(N) + " ids");
     if (one_sync) {
-      collect_stage_times(h);
+      collect_stage_times(h, true);
       h->last_launches = launches;
       if (n_ids) *n_ids = N;
       if (n_chunks) *n_chunks = C;
