@@ -163,6 +163,11 @@ struct gtk_tokenizer {
   uint8_t* small_out_h = nullptr;  // [totals | text id offsets | chunk id offsets | ids]
   uint8_t* small_out_d = nullptr;
   bool result_is_small = false;
+  // batches below the slicing threshold: one arena [text id offsets | chunk id offsets | ids] on both sides
+  DevBuf d_out_pack;
+  PinBuf h_out_pack;
+  bool result_is_packed = false;
+  size_t pack_text_bytes = 0, pack_chunk_bytes = 0;
   int64_t small_seq = 0;  // calls of the small-batch kernel so far (the kernel echoes it as its completion mark)
   // sliced host path: copy streams and two slice arenas
   cudaStream_t in_stream = nullptr, out_stream = nullptr, pack_stream = nullptr;
@@ -793,9 +798,9 @@ void release_handle(gtk_tokenizer* h)
     for (DevBuf* b : {&h->d_bpi, &h->d_slots, &h->d_overflow, &h->d_bpr, &h->d_mor, &h->d_sor, &h->d_adj, &h->d_b2i, &h->d_words, &h->d_low_map, &h->d_wide_slots, &h->d_staging32, &h->d_seg_scratch32, &h->d_bytes, &h->d_text_off,
                       &h->d_text_chunk_base, &h->d_chunk_off, &h->d_tile_chunk0, &h->d_staging, &h->d_unit_first,
                       &h->d_unit_cnt, &h->d_chunk_cnt, &h->d_unit_base, &h->d_chunk_id_off, &h->d_text_id_off,
-                      &h->d_out_ids, &h->d_seg_scratch, &h->d_scan_sums, &h->d_counters, &h->d_totals})
+                      &h->d_out_ids, &h->d_seg_scratch, &h->d_scan_sums, &h->d_counters, &h->d_totals, &h->d_out_pack})
       b->release();
-    for (PinBuf* b : {&h->h_ids, &h->h_text_id_off, &h->h_chunk_id_off, &h->h_totals, &h->h_piece_off, &h->h_piece_id_off, &h->h_chunk_id_all}) b->release();
+    for (PinBuf* b : {&h->h_ids, &h->h_text_id_off, &h->h_chunk_id_off, &h->h_totals, &h->h_piece_off, &h->h_piece_id_off, &h->h_chunk_id_all, &h->h_out_pack}) b->release();
     for (DevBuf* b : {&h->d_piece_off, &h->d_piece_id_off, &h->d_chunk_id_all}) b->release();
     if (h->small_in_h) cudaFreeHost(h->small_in_h);
     if (h->small_out_h) cudaFreeHost(h->small_out_h);
@@ -1022,6 +1027,7 @@ GTK_API int gtk_encode(gtk_tokenizer* h, int mode, const uint8_t* bytes, const i
   if (kernel_ms) *kernel_ms = 0.f;
   h->result_is_cpu = false;
   h->result_is_small = false;
+  h->result_is_packed = false;
   h->res_n_ids = h->res_n_chunks = 0;
   h->res_n_texts = n_texts;
   h->last_launches = 0;
@@ -1047,26 +1053,33 @@ GTK_API int gtk_encode(gtk_tokenizer* h, int mode, const uint8_t* bytes, const i
     h->d_text_off.reserve(size_t(n_texts + 1) * 8);
     GTK_CUDA(cudaMemcpyAsync(h->d_bytes.p, bytes, size_t(n_bytes), cudaMemcpyHostToDevice, s));
     GTK_CUDA(cudaMemcpyAsync(h->d_text_off.p, text_offsets, size_t(n_texts + 1) * 8, cudaMemcpyHostToDevice, s));
-    Plan p = plan_batch(h, h->d_bytes.as<uint8_t>(), n_bytes, h->d_text_off.as<int64_t>(), n_texts, nullptr, 0,
-                        nullptr, true);
+    // Everything that goes back lives in one arena, [text id offsets | chunk id offsets | ids], each sized by its
+    // bound (a batch of this path is below 8 MiB, so 4 bytes per input byte for the ids is little): the pack
+    // follows the front without a host round trip and one copy brings the results.
+    const size_t text_b  = ((size_t(n_texts) + 1) * 8 + 63) & ~size_t(63);
+    const size_t chunk_b = ((size_t(chunk_upper_bound(n_bytes, n_texts, h->chunk_tokens)) + 1) * 8 + 63) & ~size_t(63);
+    h->d_out_pack.reserve(text_b + chunk_b + size_t(n_bytes) * 4 + 64);
+    uint8_t* dp = h->d_out_pack.as<uint8_t>();
+    Plan p = plan_batch(h, h->d_bytes.as<uint8_t>(), n_bytes, h->d_text_off.as<int64_t>(), n_texts,
+                        reinterpret_cast<int32_t*>(dp + text_b + chunk_b), n_bytes,
+                        reinterpret_cast<int64_t*>(dp + text_b), true);
+    p.b.text_id_off = reinterpret_cast<int64_t*>(dp);
     int launches = 0;
-    run_front(h, p.b, mode, &launches);
+    run_front(h, p.b, mode, &launches, nullptr, nullptr, nullptr, true);
+    run_pack(h, p.b, mode, &launches, nullptr, nullptr, true);
     GTK_CUDA(cudaStreamSynchronize(s));
     const int64_t* ht = h->h_totals.as<int64_t>();
     const int64_t C = ht[0], N = ht[1];
     const int status = reinterpret_cast<const int32_t*>(ht + 2)[1];
     if (status != gtk::kStatusOk) return h->fail(GTK_ERR_KERNEL, status_text(status));
-    h->d_out_ids.reserve(size_t(N + 1) * 4);
-    p.b.out_ids = h->d_out_ids.as<int32_t>();
-    p.b.out_capacity = N;
-    run_pack(h, p.b, mode, &launches);
-    h->h_ids.reserve(size_t(N + 1) * 4);
-    h->h_chunk_id_off.reserve(size_t(C + 1) * 8);
-    GTK_CUDA(cudaMemcpyAsync(h->h_ids.p, p.b.out_ids, size_t(N) * 4, cudaMemcpyDeviceToHost, s));
-    GTK_CUDA(cudaMemcpyAsync(h->h_chunk_id_off.p, p.b.chunk_id_off, size_t(C + 1) * 8, cudaMemcpyDeviceToHost, s));
-    GTK_CUDA(cudaMemcpyAsync(h->h_text_id_off.p, p.b.text_id_off, size_t(n_texts + 1) * 8, cudaMemcpyDeviceToHost, s));
+    if (N > n_bytes) return h->fail(GTK_ERR_KERNEL, "more ids than input bytes");
+    h->h_out_pack.reserve(text_b + chunk_b + size_t(N) * 4 + 64);
+    GTK_CUDA(cudaMemcpyAsync(h->h_out_pack.p, dp, text_b + chunk_b + size_t(N) * 4, cudaMemcpyDeviceToHost, s));
     GTK_CUDA(cudaStreamSynchronize(s));
-    collect_stage_times(h);
+    collect_stage_times(h, true);
+    h->result_is_packed = true;
+    h->pack_text_bytes  = text_b;
+    h->pack_chunk_bytes = chunk_b;
     h->last_launches = launches;
     h->res_n_ids = N;
     h->res_n_chunks = C;
@@ -1106,6 +1119,7 @@ GTK_API int gtk_encode_cpu(gtk_tokenizer* h, int rule, const uint8_t* bytes, con
   }
   h->result_is_cpu = true;
   h->result_is_small = false;
+  h->result_is_packed = false;
   h->res_n_ids = int64_t(h->cpu_ids.size());
   h->res_n_chunks = int64_t(h->cpu_chunk_off.size()) - 1;
   h->res_n_texts = n_texts;
@@ -1133,6 +1147,11 @@ GTK_API int gtk_result_view(const gtk_tokenizer* h, const int32_t** ids, const i
     if (ids) *ids = reinterpret_cast<const int32_t*>(h->small_out_h + kSmallOutIds);
     if (text_id_offsets) *text_id_offsets = reinterpret_cast<const int64_t*>(h->small_out_h + kSmallOutText);
     if (chunk_id_offsets) *chunk_id_offsets = reinterpret_cast<const int64_t*>(h->small_out_h + kSmallOutChunk);
+  } else if (h->result_is_packed) {
+    const uint8_t* base = h->h_out_pack.as<uint8_t>();
+    if (ids) *ids = reinterpret_cast<const int32_t*>(base + h->pack_text_bytes + h->pack_chunk_bytes);
+    if (text_id_offsets) *text_id_offsets = reinterpret_cast<const int64_t*>(base);
+    if (chunk_id_offsets) *chunk_id_offsets = reinterpret_cast<const int64_t*>(base + h->pack_text_bytes);
   } else {
     if (ids) *ids = h->h_ids.as<int32_t>();
     if (text_id_offsets) *text_id_offsets = h->h_text_id_off.as<int64_t>();

@@ -111,7 +111,7 @@ int launch_publish_totals(const EncodeBuffers& b, int64_t* mapped, cudaStream_t 
 // Whole pipeline in one single-CTA kernel for small batches; totals[0..2] receive n_chunks, n_ids, status,
 // totals[4] the kernel's own duration in nanoseconds and, as the very last store, totals[3] the call number.
 int launch_encode_small(const EncodeBuffers& b, const DeviceTable& t, cudaStream_t stream);
-constexpr int64_t kSmallMaxBytes = 32768;
+constexpr int64_t kSmallMaxBytes = 16384;  // four tiles one after the other in one CTA (95 us) still beat the general path's ~105 us
 constexpr int64_t kSmallMaxTexts = 1024;
 // What the allocation-free entry point needs from a handle (defined in gtk_api.cu).
 struct HandleView {

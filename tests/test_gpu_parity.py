@@ -347,7 +347,7 @@ def test_medium_batches_of_many_short_texts(lib, merges_path, oracle):
 def test_path_selector_boundaries(lib, merges_path, oracle):
     """Batches on both sides of every size limit that picks a code path: the single-CTA chunker by search (256
     texts, 2048 chunks, 1024 tiles) and per text (16 384 items, 2048 tiles), the single-CTA scans (16 384 items), the
-    small-batch kernel (32 KiB, 1024 texts) and the sliced host path (8 MiB).  Host and device-resident entry."""
+    small-batch kernel (16 KiB, 1024 texts) and the sliced host path (8 MiB).  Host and device-resident entry."""
     import torch
 
     src = lib.TextGen(8).text(9 << 20, mix=lib.MIX_STRESS)
@@ -390,9 +390,10 @@ def test_path_selector_boundaries(lib, merges_path, oracle):
     # per text: 2048 / 2049 tiles (8 MiB: device-resident entry only, the host entry slices such a batch)
     assert check("2048 tiles, many texts", 4096, [1024] * 8192, host=False) == 4
     assert check("2049 tiles, many texts", 4096, [1024] * 8192 + [1], host=False) > 4
-    # small-batch kernel: 32 KiB / one byte more; 1024 / 1025 texts
+    # small-batch kernel: 16 KiB / one byte more; 1024 / 1025 texts
+    check("16 KiB", 2048, [16384])
+    check("16 KiB + 1", 2048, [16385])
     check("32 KiB", 2048, [32768])
-    check("32 KiB + 1", 2048, [32769])
     check("1024 texts", 2048, [20] * 1024)
     check("1025 texts", 2048, [20] * 1025)
     # sliced host path: one byte below and at 8 MiB
