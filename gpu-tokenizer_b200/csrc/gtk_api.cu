@@ -151,8 +151,8 @@ struct gtk_tokenizer {
 
   // arenas
   DevBuf d_bytes, d_text_off, d_text_chunk_base, d_chunk_off, d_tile_chunk0, d_staging, d_unit_first, d_unit_cnt,
-      d_chunk_cnt, d_unit_base, d_chunk_id_off, d_text_id_off, d_out_ids, d_seg_scratch, d_scan_sums, d_counters,
-      d_totals;
+      d_chunk_cnt, d_unit_base, d_chunk_id_off, d_text_id_off, d_out_ids, d_seg_scratch, d_scan_sums,
+      d_totals;  // d_totals also holds the counters (plan_batch)
   PinBuf h_ids, h_text_id_off, h_chunk_id_off, h_totals;
   // sliced host batches: offsets of all slices, moved once per batch
   DevBuf d_piece_off, d_piece_id_off, d_chunk_id_all;
@@ -798,7 +798,7 @@ void release_handle(gtk_tokenizer* h)
     for (DevBuf* b : {&h->d_bpi, &h->d_slots, &h->d_overflow, &h->d_bpr, &h->d_mor, &h->d_sor, &h->d_adj, &h->d_b2i, &h->d_words, &h->d_low_map, &h->d_wide_slots, &h->d_staging32, &h->d_seg_scratch32, &h->d_bytes, &h->d_text_off,
                       &h->d_text_chunk_base, &h->d_chunk_off, &h->d_tile_chunk0, &h->d_staging, &h->d_unit_first,
                       &h->d_unit_cnt, &h->d_chunk_cnt, &h->d_unit_base, &h->d_chunk_id_off, &h->d_text_id_off,
-                      &h->d_out_ids, &h->d_seg_scratch, &h->d_scan_sums, &h->d_counters, &h->d_totals, &h->d_out_pack})
+                      &h->d_out_ids, &h->d_seg_scratch, &h->d_scan_sums, &h->d_totals, &h->d_out_pack})
       b->release();
     for (PinBuf* b : {&h->h_ids, &h->h_text_id_off, &h->h_chunk_id_off, &h->h_totals, &h->h_piece_off, &h->h_piece_id_off, &h->h_chunk_id_all, &h->h_out_pack}) b->release();
     for (DevBuf* b : {&h->d_piece_off, &h->d_piece_id_off, &h->d_chunk_id_all}) b->release();
