@@ -322,6 +322,18 @@ const char* status_text(int s)
 
 // Chunker -> merge -> scans.  Leaves totals (n_chunks, n_ids) and the status
 // word in the pinned totals buffer; the caller synchronises and then packs.
+// n_chunks, n_ids and the status word to the host: totals and counters are adjacent in the handle's own arena
+void copy_totals(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int64_t* pinned_totals, cudaStream_t s)
+{
+  int64_t* ht = pinned_totals ? pinned_totals : h->h_totals.as<int64_t>();
+  if (reinterpret_cast<const int64_t*>(b.counters) == b.totals + 2) {
+    GTK_CUDA(cudaMemcpyAsync(ht, b.totals, 32, cudaMemcpyDeviceToHost, s));
+  } else {
+    GTK_CUDA(cudaMemcpyAsync(ht, b.totals, 16, cudaMemcpyDeviceToHost, s));
+    GTK_CUDA(cudaMemcpyAsync(ht + 2, b.counters, 16, cudaMemcpyDeviceToHost, s));
+  }
+}
+
 // chained: the pack follows on the same stream without a host round trip, so that one event pair around both
 // times the pipeline when the stages are not timed one by one.
 void run_front(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* launches, cudaEvent_t* ev = nullptr,
@@ -349,13 +361,8 @@ void run_front(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* lau
     *launches += gtk::launch_publish_totals(b, mapped_totals, s);
     return;
   }
-  int64_t* ht = pinned_totals ? pinned_totals : h->h_totals.as<int64_t>();
-  if (reinterpret_cast<const int64_t*>(b.counters) == b.totals + 2) {  // adjacent: one copy
-    GTK_CUDA(cudaMemcpyAsync(ht, b.totals, 32, cudaMemcpyDeviceToHost, s));
-  } else {
-    GTK_CUDA(cudaMemcpyAsync(ht, b.totals, 16, cudaMemcpyDeviceToHost, s));
-    GTK_CUDA(cudaMemcpyAsync(ht + 2, b.counters, 16, cudaMemcpyDeviceToHost, s));
-  }
+  if (chained) return;  // the totals travel behind the pack (run_pack), which does not have to wait for them
+  copy_totals(h, b, pinned_totals, s);
 }
 
 void run_pack(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* launches, cudaEvent_t* ev = nullptr,
@@ -369,6 +376,7 @@ void run_pack(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* laun
   else *launches += gtk::launch_pack(b, mode != GTK_MODE_OPT, h->sm_count * 8, s);
   GTK_CUDA(cudaEventRecord(ev[4], s));
   GTK_CUDA(cudaGetLastError());
+  if (chained) copy_totals(h, b, nullptr, s);
 }
 
 // Adds the stage times of one pipeline run (one batch, or one slice) to h->stage_ms.  The events must have
