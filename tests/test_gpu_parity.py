@@ -401,6 +401,55 @@ def test_path_selector_boundaries(lib, merges_path, oracle):
     check("8 MiB", 4096, [8 << 20])
 
 
+def test_interleaved_paths_on_one_handle(lib, merges_path, oracle):
+    """One handle, calls of every kind in turn -- single-kernel, single-piece, sliced, device-resident, host reference,
+    empty -- twice over: each result must be that call's own (the result views, arenas and flags of one path must
+    not leak into the next)."""
+    import torch
+
+    src = lib.TextGen(12).text(10 << 20, mix=lib.MIX_STRESS)
+    rng = np.random.default_rng(5)
+    t = make_tok(lib, merges_path, 1024)
+
+    def offsets(lens):
+        return np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+
+    def expected(data, toff_in):
+        ends = toff_in[1:]
+        lens = np.diff(toff_in)
+        inner = [np.arange(s + 1024, e, 1024) for s, e in zip(toff_in[:-1], ends) if e - s > 1024]
+        chunk_off = np.unique(np.concatenate([[0], ends[lens > 0]] + inner)).astype(np.int64)
+        want, woff = oracle.encode_chunks(data, chunk_off, mode=MODE_SEGMENTED, threads=NCPU)
+        return want, woff, woff[np.searchsorted(chunk_off, toff_in, side="left")]
+
+    batches = {
+        "single kernel": offsets([300, 0, 212]),
+        "single piece, one text": offsets([200_000]),
+        "single piece, many texts": offsets(rng.integers(0, 90, size=6000)),
+        "sliced": offsets([5 << 20, 0, (4 << 20) + 77]),
+    }
+    want = {k: expected(src[:v[-1]], v) for k, v in batches.items()}
+    order = ["sliced", "single kernel", "single piece, many texts", "single piece, one text", "single kernel"]
+    for rnd in range(2):
+        for k in order:
+            toff_in = batches[k]
+            data = src[:toff_in[-1]]
+            ids, toff, coff, _ = t.encode(data, toff_in)
+            w, woff, wtext = want[k]
+            check_chunks(ids, coff, w, woff, f"{k}, round {rnd}")
+            assert np.array_equal(toff, wtext), k
+            if k == "single piece, one text":               # the device-resident entry and the host reference in between
+                d_bytes, d_toff = torch.from_numpy(data.copy()).cuda(), torch.from_numpy(toff_in).cuda()
+                d_ids = torch.empty(len(data), dtype=torch.int32, device="cuda")
+                n_ids, n_chunks, _ = t.encode_device(d_bytes.data_ptr(), len(data), d_toff.data_ptr(), 1,
+                                                     d_ids.data_ptr(), len(data))
+                assert n_ids == len(w) and np.array_equal(d_ids[:n_ids].cpu().numpy(), w)
+                cids, _, ccoff = t.encode_cpu(data[:5000], None)[:3]         # its first four chunks are the batch's
+                assert np.array_equal(cids[:ccoff[4]], w[:woff[4]]) and len(ccoff) == 6
+                eids, etoff, ecoff, _ = t.encode(np.zeros(0, np.uint8), np.array([0, 0, 0], dtype=np.int64))
+                assert len(eids) == 0 and np.array_equal(etoff, [0, 0, 0])
+
+
 def test_generated_adversarial_strings(lib, merges_path, oracle):
     """Seeded adversarial strings (runs, tiny alphabets, arbitrary bytes, multi-byte characters, empty) in
     batches that take the single-kernel small path and the multi-kernel path, at several chunk sizes."""
