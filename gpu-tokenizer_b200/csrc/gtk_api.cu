@@ -445,10 +445,19 @@ struct SlicePlan {
 };
 
 // Size of the slice that starts at byte `lo` of a batch of `total` bytes: full-size slices in the middle,
-// smaller ones at both ends (a quarter, then half), because the first slice's upload and kernels and the last
-// slice's download are the part of the call that nothing overlaps.
+// smaller ones at both ends (a quarter, then half; for batches of two full slices and more an eighth first), because
+// the first slice's upload and kernels and the last slice's download are the part of the call that nothing overlaps.
 int64_t slice_target(int64_t lo, int64_t total, int64_t full)
 {
+  if (total >= 2 * full) {  // large batches: three steps at both ends, an eighth, a quarter, a half (256 MiB: 8.03 against 8.11 ms)
+    const int64_t e = full / 8, rem = total - lo;
+    int64_t t = (lo < e) ? e : (lo < 3 * e) ? 2 * e : (lo < 7 * e) ? 4 * e : full;
+    if (rem <= e) t = rem;
+    else if (rem <= 3 * e) t = std::min(t, rem - e);
+    else if (rem <= 7 * e) t = std::min(t, rem - 3 * e);
+    else if (rem <= 7 * e + full) t = std::min(t, std::max(rem - 7 * e, e));
+    return std::max<int64_t>(t, 1);
+  }
   const int64_t q = full / 4, rem = total - lo;
   int64_t t = (lo < q) ? q : (lo < 3 * q) ? 2 * q : full;
   if (rem <= q) t = rem;
