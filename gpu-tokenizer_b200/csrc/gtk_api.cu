@@ -168,6 +168,11 @@ struct gtk_tokenizer {
   PinBuf h_out_pack;
   bool result_is_packed = false;
   size_t pack_text_bytes = 0, pack_chunk_bytes = 0;
+  const uint8_t* pack_base = nullptr;  // h_out_pack, or the mapped block below behind its 64-byte header
+  // batches of up to 256 KiB: a kernel writes the results into this mapped block and the host polls its header
+  uint8_t* mid_out_h = nullptr;
+  uint8_t* mid_out_d = nullptr;
+  int64_t mid_seq = 0;
   int64_t small_seq = 0;  // calls of the small-batch kernel so far (the kernel echoes it as its completion mark)
   // sliced host path: copy streams and two slice arenas
   cudaStream_t in_stream = nullptr, out_stream = nullptr, pack_stream = nullptr;
@@ -366,7 +371,7 @@ void run_front(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* lau
 }
 
 void run_pack(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* launches, cudaEvent_t* ev = nullptr,
-              cudaStream_t on = nullptr, bool chained = false)
+              cudaStream_t on = nullptr, bool chained = false, bool totals_by_copy = true)
 {
   cudaStream_t s = on ? on : h->stream;
   const bool stages = ev != nullptr || h->stage_timing;
@@ -376,7 +381,7 @@ void run_pack(gtk_tokenizer* h, const gtk::EncodeBuffers& b, int mode, int* laun
   else *launches += gtk::launch_pack(b, mode != GTK_MODE_OPT, h->sm_count * 8, s);
   GTK_CUDA(cudaEventRecord(ev[4], s));
   GTK_CUDA(cudaGetLastError());
-  if (chained) copy_totals(h, b, nullptr, s);
+  if (chained && totals_by_copy) copy_totals(h, b, nullptr, s);
 }
 
 // Adds the stage times of one pipeline run (one batch, or one slice) to h->stage_ms.  The events must have
@@ -744,6 +749,8 @@ constexpr size_t kSmallOutText   = 64;
 constexpr size_t kSmallOutChunk  = kSmallOutText + (((size_t(gtk::kSmallMaxTexts) + 1) * 8 + 63) & ~size_t(63));
 constexpr size_t kSmallOutIds    = kSmallOutChunk + (((size_t(kSmallChunkCap) + 1) * 8 + 63) & ~size_t(63));
 constexpr size_t kSmallOutSize   = kSmallOutIds + size_t(gtk::kSmallMaxBytes) * 4 + 64;
+constexpr size_t kMappedResultBytes        = size_t(2) << 20;    // mapped result block of the next size class
+constexpr int64_t kResultsByKernelMaxBytes = int64_t(256) << 10;  // batches up to this size use it
 
 void small_path_init(gtk_tokenizer* h)
 {
@@ -757,6 +764,32 @@ void small_path_init(gtk_tokenizer* h)
   h->small_out_h = static_cast<uint8_t*>(oh);
   h->small_in_d = static_cast<uint8_t*>(id);
   h->small_out_d = static_cast<uint8_t*>(od);
+  void *mh = nullptr, *md = nullptr;
+  GTK_CUDA(cudaHostAlloc(&mh, kMappedResultBytes, cudaHostAllocMapped));
+  GTK_CUDA(cudaHostGetDevicePointer(&md, mh, 0));
+  std::memset(mh, 0, 64);
+  h->mid_out_h = static_cast<uint8_t*>(mh);
+  h->mid_out_d = static_cast<uint8_t*>(md);
+}
+
+// Waits for a kernel's completion mark (the call number, its last store behind a system-wide fence) in a mapped
+// result block: returns as soon as the results are on the host, several microseconds before a stream
+// synchronisation would.  The stream is asked now and then so that a failed launch or a fault ends the wait
+// with its error.  false: the stream went idle without the mark.
+bool wait_for_mark(volatile const int64_t* mark, int64_t seq, cudaStream_t s, const char* what)
+{
+  for (unsigned spin = 1; *mark != seq; ++spin) {
+    if ((spin & 0xFFFFu) == 0u) {
+      const cudaError_t q = cudaStreamQuery(s);
+      if (q == cudaSuccess) return *mark == seq;
+      if (q != cudaErrorNotReady) throw CudaFail{std::string(what) + ": " + cudaGetErrorString(q)};
+    }
+#if defined(__x86_64__) || defined(__i386__)
+    __builtin_ia32_pause();
+#endif
+  }
+  std::atomic_thread_fence(std::memory_order_acquire);
+  return true;
 }
 
 int encode_host_small(gtk_tokenizer* h, const uint8_t* bytes, const int64_t* text_offsets, int64_t n_texts,
@@ -782,20 +815,8 @@ int encode_host_small(gtk_tokenizer* h, const uint8_t* bytes, const int64_t* tex
   // returns as soon as the results are on the host, several microseconds before a stream synchronisation would.
   // The stream is asked now and then so that a failed launch or a fault ends the wait with its error.
   volatile const int64_t* tot = reinterpret_cast<volatile const int64_t*>(h->small_out_h + kSmallOutTotals);
-  for (unsigned spin = 1; tot[3] != p.b.small_seq; ++spin) {
-    if ((spin & 0xFFFFu) == 0u) {
-      const cudaError_t q = cudaStreamQuery(s);
-      if (q == cudaSuccess) {
-        if (tot[3] != p.b.small_seq) return h->fail(GTK_ERR_KERNEL, "small-batch kernel ended without publishing its results");
-        break;
-      }
-      if (q != cudaErrorNotReady) throw CudaFail{std::string("small-batch kernel: ") + cudaGetErrorString(q)};
-    }
-#if defined(__x86_64__) || defined(__i386__)
-    __builtin_ia32_pause();
-#endif
-  }
-  std::atomic_thread_fence(std::memory_order_acquire);
+  if (!wait_for_mark(tot + 3, p.b.small_seq, s, "small-batch kernel"))
+    return h->fail(GTK_ERR_KERNEL, "small-batch kernel ended without publishing its results");
   if (tot[2] != gtk::kStatusOk) return h->fail(GTK_ERR_KERNEL, status_text(int(tot[2])));
   h->stage_ms[1] = h->stage_ms[4] = float(double(tot[4]) * 1e-6);  // the kernel's own globaltimer span
   h->last_launches = launches;
@@ -821,6 +842,7 @@ void release_handle(gtk_tokenizer* h)
     for (DevBuf* b : {&h->d_piece_off, &h->d_piece_id_off, &h->d_chunk_id_all}) b->release();
     if (h->small_in_h) cudaFreeHost(h->small_in_h);
     if (h->small_out_h) cudaFreeHost(h->small_out_h);
+    if (h->mid_out_h) cudaFreeHost(h->mid_out_h);
     for (auto& sl : h->slice) sl.release();
     if (h->in_stream) cudaStreamDestroy(h->in_stream);
     if (h->out_stream) cudaStreamDestroy(h->out_stream);
@@ -1082,17 +1104,38 @@ GTK_API int gtk_encode(gtk_tokenizer* h, int mode, const uint8_t* bytes, const i
                         reinterpret_cast<int64_t*>(dp + text_b), true);
     p.b.text_id_off = reinterpret_cast<int64_t*>(dp);
     int launches = 0;
+    // Up to 256 KiB of text a kernel behind the pack writes the results into mapped host memory and the host polls
+    // its completion mark: no copy of the totals, no second copy sized by them, no stream synchronisation.
+    const bool by_kernel = h->mid_out_h != nullptr && n_bytes <= kResultsByKernelMaxBytes &&
+                           64 + text_b + chunk_b + size_t(n_bytes) * 4 + 64 <= kMappedResultBytes;
     run_front(h, p.b, mode, &launches, nullptr, nullptr, nullptr, true);
-    run_pack(h, p.b, mode, &launches, nullptr, nullptr, true);
-    GTK_CUDA(cudaStreamSynchronize(s));
-    const int64_t* ht = h->h_totals.as<int64_t>();
-    const int64_t C = ht[0], N = ht[1];
-    const int status = reinterpret_cast<const int32_t*>(ht + 2)[1];
+    run_pack(h, p.b, mode, &launches, nullptr, nullptr, true, !by_kernel);
+    int64_t C = 0, N = 0;
+    int status = gtk::kStatusOk;
+    if (by_kernel) {
+      const int64_t seq = ++h->mid_seq;
+      launches += gtk::launch_results_to_host(p.b, dp, h->mid_out_d + 64, int64_t(text_b + chunk_b),
+                                              reinterpret_cast<int64_t*>(h->mid_out_d), seq, s);
+      GTK_CUDA(cudaGetLastError());
+      volatile const int64_t* tot = reinterpret_cast<volatile const int64_t*>(h->mid_out_h);
+      if (!wait_for_mark(tot + 3, seq, s, "result kernel"))
+        return h->fail(GTK_ERR_KERNEL, "result kernel ended without publishing its results");
+      C = tot[0], N = tot[1], status = int(tot[2]);
+      h->pack_base = h->mid_out_h + 64;
+    } else {
+      GTK_CUDA(cudaStreamSynchronize(s));
+      const int64_t* ht = h->h_totals.as<int64_t>();
+      C = ht[0], N = ht[1];
+      status = reinterpret_cast<const int32_t*>(ht + 2)[1];
+    }
     if (status != gtk::kStatusOk) return h->fail(GTK_ERR_KERNEL, status_text(status));
     if (N > n_bytes) return h->fail(GTK_ERR_KERNEL, "more ids than input bytes");
-    h->h_out_pack.reserve(text_b + chunk_b + size_t(N) * 4 + 64);
-    GTK_CUDA(cudaMemcpyAsync(h->h_out_pack.p, dp, text_b + chunk_b + size_t(N) * 4, cudaMemcpyDeviceToHost, s));
-    GTK_CUDA(cudaStreamSynchronize(s));
+    if (!by_kernel) {
+      h->h_out_pack.reserve(text_b + chunk_b + size_t(N) * 4 + 64);
+      GTK_CUDA(cudaMemcpyAsync(h->h_out_pack.p, dp, text_b + chunk_b + size_t(N) * 4, cudaMemcpyDeviceToHost, s));
+      GTK_CUDA(cudaStreamSynchronize(s));
+      h->pack_base = h->h_out_pack.as<uint8_t>();
+    }
     collect_stage_times(h, true);
     h->result_is_packed = true;
     h->pack_text_bytes  = text_b;
@@ -1165,7 +1208,7 @@ GTK_API int gtk_result_view(const gtk_tokenizer* h, const int32_t** ids, const i
     if (text_id_offsets) *text_id_offsets = reinterpret_cast<const int64_t*>(h->small_out_h + kSmallOutText);
     if (chunk_id_offsets) *chunk_id_offsets = reinterpret_cast<const int64_t*>(h->small_out_h + kSmallOutChunk);
   } else if (h->result_is_packed) {
-    const uint8_t* base = h->h_out_pack.as<uint8_t>();
+    const uint8_t* base = h->pack_base;
     if (ids) *ids = reinterpret_cast<const int32_t*>(base + h->pack_text_bytes + h->pack_chunk_bytes);
     if (text_id_offsets) *text_id_offsets = reinterpret_cast<const int64_t*>(base);
     if (chunk_id_offsets) *chunk_id_offsets = reinterpret_cast<const int64_t*>(base + h->pack_text_bytes);

@@ -108,6 +108,10 @@ int launch_output_scans(const EncodeBuffers& b, int mode_base, cudaStream_t stre
 int launch_pack(const EncodeBuffers& b, int mode_base, int grid, cudaStream_t stream);
 // totals[0..1] and counters[0..3] to `mapped` (page-locked host memory as the device sees it), laid out as 4 x int64
 int launch_publish_totals(const EncodeBuffers& b, int64_t* mapped, cudaStream_t stream);
+// the device result arena of a single-piece batch into mapped host memory, then totals {n_chunks, n_ids, status} and,
+// last, the call number into mapped[0..3]; uses counters[8] (zero at the start of the call)
+int launch_results_to_host(const EncodeBuffers& b, const void* src, void* dst, int64_t prefix_bytes, int64_t* mapped,
+                           int64_t seq, cudaStream_t stream);
 // Whole pipeline in one single-CTA kernel for small batches; totals[0..2] receive n_chunks, n_ids, status,
 // totals[4] the kernel's own duration in nanoseconds and, as the very last store, totals[3] the call number.
 int launch_encode_small(const EncodeBuffers& b, const DeviceTable& t, cudaStream_t stream);

@@ -2585,6 +2585,39 @@ __global__ void k_publish_totals(const int64_t* totals, const int32_t* counters,
   }
 }
 
+// Results of a batch that ran in one piece, from their device arena [text id offsets | chunk id offsets | ids] into
+// mapped host memory: the first prefix_bytes (a multiple of 16) and the n_ids ids behind them, n_ids read from the
+// totals on the device.  The CTA that finishes last (a counter, no waiting) publishes the totals and, as the very
+// last store behind a system-wide fence, the call number that the host polls for.
+__global__ void __launch_bounds__(256) k_results_to_host(const uint4* __restrict__ src, uint4* dst, int64_t prefix_bytes,
+                                                         const int64_t* totals, int32_t* counters, int64_t* mapped,
+                                                         int64_t seq)
+{
+  __shared__ int last;
+  const int64_t n16 = (prefix_bytes + totals[1] * 4 + 15) / 16;
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n16; i += int64_t(gridDim.x) * blockDim.x)
+    dst[i] = src[i];
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) last = (atomicAdd(counters + 8, 1) == int(gridDim.x) - 1);
+  __syncthreads();
+  if (last && threadIdx.x == 0) {
+    mapped[0] = totals[0];
+    mapped[1] = totals[1];
+    mapped[2] = int64_t(counters[1]);  // status word
+    __threadfence_system();
+    *reinterpret_cast<volatile int64_t*>(mapped + 3) = seq;
+  }
+}
+
+int launch_results_to_host(const EncodeBuffers& b, const void* src, void* dst, int64_t prefix_bytes, int64_t* mapped,
+                           int64_t seq, cudaStream_t stream)
+{
+  k_results_to_host<<<32, 256, 0, stream>>>(static_cast<const uint4*>(src), static_cast<uint4*>(dst), prefix_bytes,
+                                           b.totals, b.counters, mapped, seq);
+  return 1;
+}
+
 int launch_publish_totals(const EncodeBuffers& b, int64_t* mapped, cudaStream_t stream)
 {
   k_publish_totals<<<1, 32, 0, stream>>>(b.totals, b.counters, mapped);
