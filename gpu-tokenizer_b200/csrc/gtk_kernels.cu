@@ -2613,7 +2613,7 @@ __global__ void __launch_bounds__(256) k_results_to_host(const uint4* __restrict
 int launch_results_to_host(const EncodeBuffers& b, const void* src, void* dst, int64_t prefix_bytes, int64_t* mapped,
                            int64_t seq, cudaStream_t stream)
 {
-  k_results_to_host<<<32, 256, 0, stream>>>(static_cast<const uint4*>(src), static_cast<uint4*>(dst), prefix_bytes,
+  k_results_to_host<<<148, 256, 0, stream>>>(static_cast<const uint4*>(src), static_cast<uint4*>(dst), prefix_bytes,
                                            b.totals, b.counters, mapped, seq);
   return 1;
 }
