@@ -173,6 +173,9 @@ struct gtk_tokenizer {
   uint8_t* mid_out_h = nullptr;
   uint8_t* mid_out_d = nullptr;
   int64_t mid_seq = 0;
+  // one text of up to 64 KiB: chunk table, zeroed counters and the text travel in one copy (encode_host_one_text)
+  PinBuf h_fast_in;
+  DevBuf d_fast_in;
   int64_t small_seq = 0;  // calls of the small-batch kernel so far (the kernel echoes it as its completion mark)
   // sliced host path: copy streams and two slice arenas
   cudaStream_t in_stream = nullptr, out_stream = nullptr, pack_stream = nullptr;
@@ -827,6 +830,70 @@ int encode_host_small(gtk_tokenizer* h, const uint8_t* bytes, const int64_t* tex
   return GTK_OK;
 }
 
+// One text of 16..64 KiB (GTK_MODE_OPT, 16-bit table): two launches.  The host lays out the chunk table (every
+// chunk but the last is chunk_tokens long) and sends it with zeroed counters and the text in ONE copy; the tile
+// kernel runs as for any batch; one more kernel (a CTA per tile) does the scans and the pack and writes the results
+// into mapped host memory, where the host polls the call number.  No chunker launch, no copy back, no synchronisation.
+constexpr int64_t kOneTextMaxBytes  = int64_t(gtk::kFinishMaxTiles / 2) * gtk::kTile;  // 64 KiB
+constexpr int64_t kOneTextMaxChunks = 4096;
+
+int encode_host_one_text(gtk_tokenizer* h, const uint8_t* bytes, int64_t n_bytes, float* kernel_ms)
+{
+  auto up = [](size_t x) { return (x + 63) & ~size_t(63); };
+  const int64_t chunk = h->chunk_tokens;
+  const int64_t C     = (n_bytes + chunk - 1) / chunk;
+  const int64_t K     = (n_bytes + gtk::kTile - 1) / gtk::kTile;
+  const size_t o_cnt = 128, o_coff = up(o_cnt + size_t(C + 1) * 4), o_tile = up(o_coff + size_t(C + 1) * 8);
+  const size_t o_bytes = up(o_tile + size_t(K) * 4), total = o_bytes + size_t(n_bytes) + 32;
+  h->h_fast_in.reserve(total);
+  h->d_fast_in.reserve(total);
+  uint8_t* hp = static_cast<uint8_t*>(h->h_fast_in.p);
+  std::memset(hp, 0, o_coff);  // totals, counters, per-chunk counts
+  reinterpret_cast<int64_t*>(hp)[0] = C;
+  int64_t* coff = reinterpret_cast<int64_t*>(hp + o_coff);
+  for (int64_t c = 0; c <= C; ++c) coff[c] = std::min(c * chunk, n_bytes);
+  int32_t* tile0 = reinterpret_cast<int32_t*>(hp + o_tile);
+  for (int64_t k = 0; k < K; ++k) tile0[k] = int32_t(k * gtk::kTile / chunk);
+  std::memcpy(hp + o_bytes, bytes, size_t(n_bytes));
+  std::memset(hp + o_bytes + n_bytes, 0, 32);
+  cudaStream_t s = h->stream;
+  uint8_t* dp = h->d_fast_in.as<uint8_t>();
+  GTK_CUDA(cudaMemcpyAsync(dp, hp, total, cudaMemcpyHostToDevice, s));
+
+  const size_t chunk_b = up(size_t(C + 1) * 8);
+  uint8_t* md = h->mid_out_d;
+  Plan p = plan_batch(h, dp + o_bytes, n_bytes, nullptr, 1, reinterpret_cast<int32_t*>(md + 128 + chunk_b), n_bytes,
+                      reinterpret_cast<int64_t*>(md + 128), false);
+  p.b.text_id_off = reinterpret_cast<int64_t*>(md + 64);
+  p.b.totals      = reinterpret_cast<int64_t*>(dp);
+  p.b.counters    = reinterpret_cast<int32_t*>(dp + 16);
+  p.b.chunk_cnt   = reinterpret_cast<int32_t*>(dp + o_cnt);
+  p.b.chunk_off   = reinterpret_cast<int64_t*>(dp + o_coff);
+  p.b.tile_chunk0 = reinterpret_cast<int32_t*>(dp + o_tile);
+  const int64_t seq = ++h->mid_seq;
+  GTK_CUDA(cudaEventRecord(h->ev[0], s));
+  int launches = gtk::launch_merge_opt(p.b, h->dtab, h->opt_grid, s);
+  launches += gtk::launch_finish_one_text(p.b, reinterpret_cast<int64_t*>(md), seq, s);
+  GTK_CUDA(cudaEventRecord(h->ev[4], s));
+  GTK_CUDA(cudaGetLastError());
+  volatile const int64_t* tot = reinterpret_cast<volatile const int64_t*>(h->mid_out_h);
+  if (!wait_for_mark(tot + 3, seq, s, "one-text finish kernel"))
+    return h->fail(GTK_ERR_KERNEL, "finish kernel ended without publishing its results");
+  if (tot[2] != gtk::kStatusOk) return h->fail(GTK_ERR_KERNEL, status_text(int(tot[2])));
+  if (tot[0] != C || tot[1] > n_bytes) return h->fail(GTK_ERR_KERNEL, "inconsistent totals");
+  GTK_CUDA(cudaEventSynchronize(h->ev[4]));  // completes a moment after the mark
+  GTK_CUDA(cudaEventElapsedTime(&h->stage_ms[4], h->ev[0], h->ev[4]));
+  h->result_is_packed = true;
+  h->pack_base        = h->mid_out_h + 64;
+  h->pack_text_bytes  = 64;
+  h->pack_chunk_bytes = chunk_b;
+  h->last_launches    = launches;
+  h->res_n_chunks     = C;
+  h->res_n_ids        = tot[1];
+  if (kernel_ms) *kernel_ms = h->stage_ms[4];
+  return GTK_OK;
+}
+
 // frees every device / pinned buffer, stream and event of a handle (also used when gtk_create fails half way)
 void release_handle(gtk_tokenizer* h)
 {
@@ -836,9 +903,9 @@ void release_handle(gtk_tokenizer* h)
     for (DevBuf* b : {&h->d_bpi, &h->d_slots, &h->d_overflow, &h->d_bpr, &h->d_mor, &h->d_sor, &h->d_adj, &h->d_b2i, &h->d_words, &h->d_low_map, &h->d_wide_slots, &h->d_staging32, &h->d_seg_scratch32, &h->d_bytes, &h->d_text_off,
                       &h->d_text_chunk_base, &h->d_chunk_off, &h->d_tile_chunk0, &h->d_staging, &h->d_unit_first,
                       &h->d_unit_cnt, &h->d_chunk_cnt, &h->d_unit_base, &h->d_chunk_id_off, &h->d_text_id_off,
-                      &h->d_out_ids, &h->d_seg_scratch, &h->d_scan_sums, &h->d_totals, &h->d_out_pack})
+                      &h->d_out_ids, &h->d_seg_scratch, &h->d_scan_sums, &h->d_totals, &h->d_out_pack, &h->d_fast_in})
       b->release();
-    for (PinBuf* b : {&h->h_ids, &h->h_text_id_off, &h->h_chunk_id_off, &h->h_totals, &h->h_piece_off, &h->h_piece_id_off, &h->h_chunk_id_all, &h->h_out_pack}) b->release();
+    for (PinBuf* b : {&h->h_ids, &h->h_text_id_off, &h->h_chunk_id_off, &h->h_totals, &h->h_piece_off, &h->h_piece_id_off, &h->h_chunk_id_all, &h->h_out_pack, &h->h_fast_in}) b->release();
     for (DevBuf* b : {&h->d_piece_off, &h->d_piece_id_off, &h->d_chunk_id_all}) b->release();
     if (h->small_in_h) cudaFreeHost(h->small_in_h);
     if (h->small_out_h) cudaFreeHost(h->small_out_h);
@@ -1086,6 +1153,9 @@ GTK_API int gtk_encode(gtk_tokenizer* h, int mode, const uint8_t* bytes, const i
     if (h->wide && mode == GTK_MODE_LOCALMIN) return h->fail(GTK_ERR_TABLE, kWideNoLocalmin);
     if (!h->wide && mode == GTK_MODE_OPT && n_bytes <= gtk::kSmallMaxBytes && n_texts <= gtk::kSmallMaxTexts)
       return encode_host_small(h, bytes, text_offsets, n_texts, n_bytes, kernel_ms);
+    if (!h->wide && mode == GTK_MODE_OPT && n_texts == 1 && n_bytes <= kOneTextMaxBytes && h->mid_out_h &&
+        !h->stage_timing && (n_bytes + h->chunk_tokens - 1) / h->chunk_tokens <= kOneTextMaxChunks)
+      return encode_host_one_text(h, bytes, n_bytes, kernel_ms);
     if (n_bytes >= kSliceThresholdBytes) return encode_host_sliced(h, mode, bytes, text_offsets, n_texts, n_bytes, kernel_ms);
     cudaStream_t s = h->stream;
     h->d_bytes.reserve(size_t(n_bytes) + 32);

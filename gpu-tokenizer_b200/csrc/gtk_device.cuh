@@ -108,6 +108,10 @@ int launch_output_scans(const EncodeBuffers& b, int mode_base, cudaStream_t stre
 int launch_pack(const EncodeBuffers& b, int mode_base, int grid, cudaStream_t stream);
 // totals[0..1] and counters[0..3] to `mapped` (page-locked host memory as the device sees it), laid out as 4 x int64
 int launch_publish_totals(const EncodeBuffers& b, int64_t* mapped, cudaStream_t stream);
+// one text of at most kFinishMaxTiles tiles with a host-made chunk table: scans, pack and results into mapped
+// host memory, then totals and the call number into mapped[0..3], in one launch (one CTA per tile) behind the tile
+// kernel; uses counters[8] (zero at the start of the call)
+int launch_finish_one_text(const EncodeBuffers& b, int64_t* mapped, int64_t seq, cudaStream_t stream);
 // the device result arena of a single-piece batch into mapped host memory, then totals {n_chunks, n_ids, status} and,
 // last, the call number into mapped[0..3]; uses counters[8] (zero at the start of the call)
 int launch_results_to_host(const EncodeBuffers& b, const void* src, void* dst, int64_t prefix_bytes, int64_t* mapped,
@@ -117,6 +121,7 @@ int launch_results_to_host(const EncodeBuffers& b, const void* src, void* dst, i
 int launch_encode_small(const EncodeBuffers& b, const DeviceTable& t, cudaStream_t stream);
 constexpr int64_t kSmallMaxBytes = 16384;  // four tiles one after the other in one CTA (95 us) still beat the general path's ~105 us
 constexpr int64_t kSmallMaxTexts = 1024;
+constexpr int kFinishMaxTiles = 32;  // one text through launch_finish_one_text: at most this many tiles
 // What the allocation-free entry point needs from a handle (defined in gtk_api.cu).
 struct HandleView {
   int device;

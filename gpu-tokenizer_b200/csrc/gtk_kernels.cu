@@ -2610,6 +2610,70 @@ __global__ void __launch_bounds__(256) k_results_to_host(const uint4* __restrict
   }
 }
 
+// One text of a few tiles whose chunk table the host has laid out (every chunk but the last is chunk_bytes long):
+// everything behind the tile kernel in one launch, one CTA per tile -- the CTA packs its tile's token run into int32
+// ids (the runs' offsets are a sum over at most kFinishMaxTiles counts, which every CTA forms for itself), CTA 0
+// also scans the per-chunk counts into id offsets and writes the text's two id offsets -- straight into mapped host
+// memory (b.chunk_id_off, b.text_id_off, b.out_ids point there).  The CTA that finishes last (a counter, no
+// waiting) adds {n_chunks, n_ids, status} and, as the very last store behind a system-wide fence, the call number
+// the host polls for.
+__global__ void __launch_bounds__(kMediumThreads) k_finish_one_text(EncodeBuffers b, int64_t* mapped, int64_t seq)
+{
+  __shared__ int scanbuf[33];
+  __shared__ int64_t carry_s;
+  __shared__ __align__(16) int stage[4 * kMediumThreads];
+  __shared__ int64_t s_base, s_total;
+  __shared__ int last;
+  const int tid   = threadIdx.x;
+  const int64_t u = blockIdx.x;
+  const int64_t C = b.totals[0];
+  if (tid == 0) {
+    int64_t run = 0, base = 0;
+    for (int64_t v = 0; v < b.n_tiles; ++v) {
+      if (v == u) base = run;
+      run += b.unit_cnt[v];
+    }
+    s_base  = base;
+    s_total = run;
+  }
+  __syncthreads();
+  const int64_t N = s_total;
+  {
+    const uint16_t* sp = b.staging + b.unit_first[u];
+    int32_t* dp        = b.out_ids + s_base;
+    int64_t m          = b.unit_cnt[u];
+    if (s_base + m > b.out_capacity) m = b.out_capacity > s_base ? b.out_capacity - s_base : 0;
+    for (int64_t i = tid; i < m; i += kMediumThreads) {
+      const uint32_t t = sp[i];
+      dp[i] = int32_t((b.low_id_map && t < 256u) ? uint32_t(__ldg(b.low_id_map + t)) : t);
+    }
+  }
+  if (u == 0) {
+    cta_exclusive_scan_medium(CountsI32{b.chunk_cnt}, C, b.chunk_id_off, scanbuf, &carry_s, stage);
+    if (tid == 0) {
+      b.text_id_off[0] = 0;
+      b.text_id_off[1] = N;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) last = (atomicAdd(b.counters + 8, 1) == int(gridDim.x) - 1);
+  __syncthreads();
+  if (last && tid == 0) {
+    mapped[0] = C;
+    mapped[1] = N;
+    mapped[2] = int64_t(b.counters[1]);  // status word
+    __threadfence_system();
+    *reinterpret_cast<volatile int64_t*>(mapped + 3) = seq;
+  }
+}
+
+int launch_finish_one_text(const EncodeBuffers& b, int64_t* mapped, int64_t seq, cudaStream_t stream)
+{
+  k_finish_one_text<<<unsigned(b.n_tiles), kMediumThreads, 0, stream>>>(b, mapped, seq);
+  return 1;
+}
+
 int launch_results_to_host(const EncodeBuffers& b, const void* src, void* dst, int64_t prefix_bytes, int64_t* mapped,
                            int64_t seq, cudaStream_t stream)
 {

@@ -396,6 +396,25 @@ def test_path_selector_boundaries(lib, merges_path, oracle):
     check("32 KiB", 2048, [32768])
     check("1024 texts", 2048, [20] * 1024)
     check("1025 texts", 2048, [20] * 1025)
+    # one text in two launches (host entry): up to 64 KiB and 4096 chunks
+    check("64 KiB", 2048, [65536])
+    check("64 KiB + 1", 2048, [65537])
+    check("64 KiB in 4096 chunks", 16, [65536])
+    check("40 000 bytes in 5715 chunks", 7, [40000])
+    check("one text of 50 000 bytes, chunk longer than the text", 65536, [50000])
+    t = make_tok(lib, merges_path, 1000)                      # ... and in GPT-2's id space
+    ref, _, _, _ = t.encode(src[:60000])
+    t.set_id_space(True)
+    ids, _, _, _ = t.encode(src[:60000])
+    gpt2_of_byte = {b: i for i, b in enumerate(list(range(33, 127)) + list(range(161, 173)) + list(range(174, 256)))}
+    nxt = 188
+    for b in range(256):
+        if b not in gpt2_of_byte:
+            gpt2_of_byte[b] = nxt
+            nxt += 1
+    lut = np.arange(65536, dtype=np.int32)
+    lut[:256] = [gpt2_of_byte[b] for b in range(256)]
+    assert np.array_equal(ids, lut[ref])
     # sliced host path: one byte below and at 8 MiB
     check("8 MiB - 1", 4096, [(8 << 20) - 1])
     check("8 MiB", 4096, [8 << 20])
@@ -425,11 +444,13 @@ def test_interleaved_paths_on_one_handle(lib, merges_path, oracle):
     batches = {
         "single kernel": offsets([300, 0, 212]),
         "single piece, one text": offsets([200_000]),
+        "one text in two launches": offsets([40_000]),
         "single piece, many texts": offsets(rng.integers(0, 90, size=6000)),
         "sliced": offsets([5 << 20, 0, (4 << 20) + 77]),
     }
     want = {k: expected(src[:v[-1]], v) for k, v in batches.items()}
-    order = ["sliced", "single kernel", "single piece, many texts", "single piece, one text", "single kernel"]
+    order = ["sliced", "one text in two launches", "single kernel", "single piece, many texts", "single piece, one text",
+             "one text in two launches", "single kernel"]
     for rnd in range(2):
         for k in order:
             toff_in = batches[k]
