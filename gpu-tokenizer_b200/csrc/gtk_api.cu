@@ -830,54 +830,79 @@ int encode_host_small(gtk_tokenizer* h, const uint8_t* bytes, const int64_t* tex
   return GTK_OK;
 }
 
-// One text of 16..64 KiB (GTK_MODE_OPT, 16-bit table): two launches.  The host lays out the chunk table (every
-// chunk but the last is chunk_tokens long) and sends it with zeroed counters and the text in ONE copy; the tile
-// kernel runs as for any batch; one more kernel (a CTA per tile) does the scans and the pack and writes the results
-// into mapped host memory, where the host polls the call number.  No chunker launch, no copy back, no synchronisation.
-constexpr int64_t kOneTextMaxBytes  = int64_t(gtk::kFinishMaxTiles / 2) * gtk::kTile;  // 64 KiB
-constexpr int64_t kOneTextMaxChunks = 4096;
+// Batches of up to 64 KiB and 1024 texts (GTK_MODE_OPT, 16-bit table): two launches.  The host lays out the chunk
+// table (a few thousand entries at most) and sends it with zeroed counters and the text in ONE copy; the tile kernel
+// runs as for any batch; one more kernel (a CTA per tile) does the scans and the pack and writes the results into
+// mapped host memory, where the host polls the call number.  No chunker launch, no copy back, no synchronisation.
+constexpr int64_t kTwoLaunchMaxBytes  = int64_t(gtk::kFinishMaxTiles / 2) * gtk::kTile;  // 64 KiB
+constexpr int64_t kTwoLaunchMaxChunks = 4096;
 
-int encode_host_one_text(gtk_tokenizer* h, const uint8_t* bytes, int64_t n_bytes, float* kernel_ms)
+// number of chunks of the batch, or -1 when it does not qualify for the two-launch path
+int64_t two_launch_chunks(const gtk_tokenizer* h, int mode, const int64_t* text_offsets, int64_t n_texts, int64_t n_bytes)
+{
+  if (h->wide || mode != GTK_MODE_OPT || !h->mid_out_h || h->stage_timing) return -1;
+  if (n_bytes > kTwoLaunchMaxBytes || n_texts > gtk::kSmallMaxTexts) return -1;
+  const int64_t chunk = h->chunk_tokens;
+  int64_t C = 0;
+  for (int64_t t = 0; t < n_texts; ++t) C += (text_offsets[t + 1] - text_offsets[t] + chunk - 1) / chunk;
+  return C <= kTwoLaunchMaxChunks ? C : -1;
+}
+
+int encode_host_two_launches(gtk_tokenizer* h, const uint8_t* bytes, const int64_t* text_offsets, int64_t n_texts,
+                             int64_t n_bytes, int64_t C, float* kernel_ms)
 {
   auto up = [](size_t x) { return (x + 63) & ~size_t(63); };
   const int64_t chunk = h->chunk_tokens;
-  const int64_t C     = (n_bytes + chunk - 1) / chunk;
   const int64_t K     = (n_bytes + gtk::kTile - 1) / gtk::kTile;
   const size_t o_cnt = 128, o_coff = up(o_cnt + size_t(C + 1) * 4), o_tile = up(o_coff + size_t(C + 1) * 8);
-  const size_t o_bytes = up(o_tile + size_t(K) * 4), total = o_bytes + size_t(n_bytes) + 32;
+  const size_t o_tbase = up(o_tile + size_t(K) * 4), o_bytes = up(o_tbase + size_t(n_texts + 1) * 8);
+  const size_t total = o_bytes + size_t(n_bytes) + 32;
   h->h_fast_in.reserve(total);
   h->d_fast_in.reserve(total);
   uint8_t* hp = static_cast<uint8_t*>(h->h_fast_in.p);
   std::memset(hp, 0, o_coff);  // totals, counters, per-chunk counts
   reinterpret_cast<int64_t*>(hp)[0] = C;
-  int64_t* coff = reinterpret_cast<int64_t*>(hp + o_coff);
-  for (int64_t c = 0; c <= C; ++c) coff[c] = std::min(c * chunk, n_bytes);
+  int64_t* coff  = reinterpret_cast<int64_t*>(hp + o_coff);
+  int64_t* tbase = reinterpret_cast<int64_t*>(hp + o_tbase);
+  int64_t c = 0;
+  for (int64_t t = 0; t < n_texts; ++t) {
+    tbase[t] = c;
+    for (int64_t pos = text_offsets[t]; pos < text_offsets[t + 1]; pos += chunk) coff[c++] = pos;
+  }
+  tbase[n_texts] = c;
+  coff[c]        = n_bytes;
   int32_t* tile0 = reinterpret_cast<int32_t*>(hp + o_tile);
-  for (int64_t k = 0; k < K; ++k) tile0[k] = int32_t(k * gtk::kTile / chunk);
+  for (int64_t k = 0, cc = 0; k < K; ++k) {  // last chunk that starts at or before the tile's first byte
+    while (cc + 1 < C && coff[cc + 1] <= k * gtk::kTile) ++cc;
+    tile0[k] = int32_t(cc);
+  }
   std::memcpy(hp + o_bytes, bytes, size_t(n_bytes));
   std::memset(hp + o_bytes + n_bytes, 0, 32);
   cudaStream_t s = h->stream;
   uint8_t* dp = h->d_fast_in.as<uint8_t>();
   GTK_CUDA(cudaMemcpyAsync(dp, hp, total, cudaMemcpyHostToDevice, s));
 
-  const size_t chunk_b = up(size_t(C + 1) * 8);
-  uint8_t* md = h->mid_out_d;
-  Plan p = plan_batch(h, dp + o_bytes, n_bytes, nullptr, 1, reinterpret_cast<int32_t*>(md + 128 + chunk_b), n_bytes,
-                      reinterpret_cast<int64_t*>(md + 128), false);
-  p.b.text_id_off = reinterpret_cast<int64_t*>(md + 64);
-  p.b.totals      = reinterpret_cast<int64_t*>(dp);
-  p.b.counters    = reinterpret_cast<int32_t*>(dp + 16);
-  p.b.chunk_cnt   = reinterpret_cast<int32_t*>(dp + o_cnt);
-  p.b.chunk_off   = reinterpret_cast<int64_t*>(dp + o_coff);
-  p.b.tile_chunk0 = reinterpret_cast<int32_t*>(dp + o_tile);
+  const size_t text_b = up(size_t(n_texts + 1) * 8), chunk_b = up(size_t(C + 1) * 8);
+  uint8_t* md = h->mid_out_d;  // [64-byte header | text id offsets | chunk id offsets | ids]
+  Plan p = plan_batch(h, dp + o_bytes, n_bytes, nullptr, n_texts, reinterpret_cast<int32_t*>(md + 64 + text_b + chunk_b),
+                      n_bytes, reinterpret_cast<int64_t*>(md + 64 + text_b), false);
+  p.b.text_id_off     = reinterpret_cast<int64_t*>(md + 64);
+  p.b.totals          = reinterpret_cast<int64_t*>(dp);
+  p.b.counters        = reinterpret_cast<int32_t*>(dp + 16);
+  p.b.chunk_cnt       = reinterpret_cast<int32_t*>(dp + o_cnt);
+  p.b.chunk_off       = reinterpret_cast<int64_t*>(dp + o_coff);
+  p.b.tile_chunk0     = reinterpret_cast<int32_t*>(dp + o_tile);
+  p.b.text_chunk_base = reinterpret_cast<int64_t*>(dp + o_tbase);
+  h->d_chunk_id_off.reserve(size_t(kTwoLaunchMaxChunks + 1) * 8);
+  p.b.chunk_id_mirror = h->d_chunk_id_off.as<int64_t>();  // the scan's own copy in HBM: the text offsets index it
   const int64_t seq = ++h->mid_seq;
   GTK_CUDA(cudaEventRecord(h->ev[0], s));
   int launches = gtk::launch_merge_opt(p.b, h->dtab, h->opt_grid, s);
-  launches += gtk::launch_finish_one_text(p.b, reinterpret_cast<int64_t*>(md), seq, s);
+  launches += gtk::launch_finish_small_batch(p.b, reinterpret_cast<int64_t*>(md), seq, s);
   GTK_CUDA(cudaEventRecord(h->ev[4], s));
   GTK_CUDA(cudaGetLastError());
   volatile const int64_t* tot = reinterpret_cast<volatile const int64_t*>(h->mid_out_h);
-  if (!wait_for_mark(tot + 3, seq, s, "one-text finish kernel"))
+  if (!wait_for_mark(tot + 3, seq, s, "finish kernel"))
     return h->fail(GTK_ERR_KERNEL, "finish kernel ended without publishing its results");
   if (tot[2] != gtk::kStatusOk) return h->fail(GTK_ERR_KERNEL, status_text(int(tot[2])));
   if (tot[0] != C || tot[1] > n_bytes) return h->fail(GTK_ERR_KERNEL, "inconsistent totals");
@@ -885,7 +910,7 @@ int encode_host_one_text(gtk_tokenizer* h, const uint8_t* bytes, int64_t n_bytes
   GTK_CUDA(cudaEventElapsedTime(&h->stage_ms[4], h->ev[0], h->ev[4]));
   h->result_is_packed = true;
   h->pack_base        = h->mid_out_h + 64;
-  h->pack_text_bytes  = 64;
+  h->pack_text_bytes  = text_b;
   h->pack_chunk_bytes = chunk_b;
   h->last_launches    = launches;
   h->res_n_chunks     = C;
@@ -1153,9 +1178,8 @@ GTK_API int gtk_encode(gtk_tokenizer* h, int mode, const uint8_t* bytes, const i
     if (h->wide && mode == GTK_MODE_LOCALMIN) return h->fail(GTK_ERR_TABLE, kWideNoLocalmin);
     if (!h->wide && mode == GTK_MODE_OPT && n_bytes <= gtk::kSmallMaxBytes && n_texts <= gtk::kSmallMaxTexts)
       return encode_host_small(h, bytes, text_offsets, n_texts, n_bytes, kernel_ms);
-    if (!h->wide && mode == GTK_MODE_OPT && n_texts == 1 && n_bytes <= kOneTextMaxBytes && h->mid_out_h &&
-        !h->stage_timing && (n_bytes + h->chunk_tokens - 1) / h->chunk_tokens <= kOneTextMaxChunks)
-      return encode_host_one_text(h, bytes, n_bytes, kernel_ms);
+    if (const int64_t C2 = two_launch_chunks(h, mode, text_offsets, n_texts, n_bytes); C2 >= 0)
+      return encode_host_two_launches(h, bytes, text_offsets, n_texts, n_bytes, C2, kernel_ms);
     if (n_bytes >= kSliceThresholdBytes) return encode_host_sliced(h, mode, bytes, text_offsets, n_texts, n_bytes, kernel_ms);
     cudaStream_t s = h->stream;
     h->d_bytes.reserve(size_t(n_bytes) + 32);

@@ -80,7 +80,7 @@ struct EncodeBuffers {
   int64_t* unit_base;        // [n_tiles+1]
   int64_t* chunk_id_off;     // [chunk_cap+1] packed id offset of each chunk (caller visible)
   int64_t* text_id_off;      // [n_texts+1] or nullptr
-  int64_t* chunk_id_mirror;  // small-batch kernel only: device copy of chunk_id_off when that lives in host memory
+  int64_t* chunk_id_mirror;  // single-CTA and finish kernels: device copy of chunk_id_off when that lives in host memory
   int64_t small_seq;         // small-batch kernel only: call number, written to totals[3] as the last store of the kernel
   int32_t* out_ids;
   const uint16_t* low_id_map;  // nullptr, or 256 entries: output id of every id < 256 (GPT-2 id space)
@@ -108,10 +108,10 @@ int launch_output_scans(const EncodeBuffers& b, int mode_base, cudaStream_t stre
 int launch_pack(const EncodeBuffers& b, int mode_base, int grid, cudaStream_t stream);
 // totals[0..1] and counters[0..3] to `mapped` (page-locked host memory as the device sees it), laid out as 4 x int64
 int launch_publish_totals(const EncodeBuffers& b, int64_t* mapped, cudaStream_t stream);
-// one text of at most kFinishMaxTiles tiles with a host-made chunk table: scans, pack and results into mapped
-// host memory, then totals and the call number into mapped[0..3], in one launch (one CTA per tile) behind the tile
-// kernel; uses counters[8] (zero at the start of the call)
-int launch_finish_one_text(const EncodeBuffers& b, int64_t* mapped, int64_t seq, cudaStream_t stream);
+// a batch of at most kFinishMaxTiles tiles with a host-made chunk table (chunk_off, tile_chunk0, text_chunk_base):
+// scans, pack and results into mapped host memory, then totals and the call number into mapped[0..3], in one launch
+// (one CTA per tile) behind the tile kernel; uses counters[8] (zero at the start of the call) and chunk_id_mirror
+int launch_finish_small_batch(const EncodeBuffers& b, int64_t* mapped, int64_t seq, cudaStream_t stream);
 // the device result arena of a single-piece batch into mapped host memory, then totals {n_chunks, n_ids, status} and,
 // last, the call number into mapped[0..3]; uses counters[8] (zero at the start of the call)
 int launch_results_to_host(const EncodeBuffers& b, const void* src, void* dst, int64_t prefix_bytes, int64_t* mapped,
@@ -119,9 +119,13 @@ int launch_results_to_host(const EncodeBuffers& b, const void* src, void* dst, i
 // Whole pipeline in one single-CTA kernel for small batches; totals[0..2] receive n_chunks, n_ids, status,
 // totals[4] the kernel's own duration in nanoseconds and, as the very last store, totals[3] the call number.
 int launch_encode_small(const EncodeBuffers& b, const DeviceTable& t, cudaStream_t stream);
-constexpr int64_t kSmallMaxBytes = 16384;  // four tiles one after the other in one CTA (95 us) still beat the general path's ~105 us
+#ifndef GTK_SMALL_MAX_BYTES
+#define GTK_SMALL_MAX_BYTES 8192
+#endif
+// two tiles one after the other in one CTA (57 us) still beat the two-launch path's 58..64 us; three (75 us) do not
+constexpr int64_t kSmallMaxBytes = GTK_SMALL_MAX_BYTES;
 constexpr int64_t kSmallMaxTexts = 1024;
-constexpr int kFinishMaxTiles = 32;  // one text through launch_finish_one_text: at most this many tiles
+constexpr int kFinishMaxTiles = 32;  // batches through launch_finish_small_batch: at most this many tiles
 // What the allocation-free entry point needs from a handle (defined in gtk_api.cu).
 struct HandleView {
   int device;

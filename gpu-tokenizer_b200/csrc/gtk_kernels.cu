@@ -2610,14 +2610,14 @@ __global__ void __launch_bounds__(256) k_results_to_host(const uint4* __restrict
   }
 }
 
-// One text of a few tiles whose chunk table the host has laid out (every chunk but the last is chunk_bytes long):
+// A batch of a few tiles whose chunk table the host has laid out (chunk_off, tile_chunk0, text_chunk_base):
 // everything behind the tile kernel in one launch, one CTA per tile -- the CTA packs its tile's token run into int32
 // ids (the runs' offsets are a sum over at most kFinishMaxTiles counts, which every CTA forms for itself), CTA 0
-// also scans the per-chunk counts into id offsets and writes the text's two id offsets -- straight into mapped host
-// memory (b.chunk_id_off, b.text_id_off, b.out_ids point there).  The CTA that finishes last (a counter, no
-// waiting) adds {n_chunks, n_ids, status} and, as the very last store behind a system-wide fence, the call number
-// the host polls for.
-__global__ void __launch_bounds__(kMediumThreads) k_finish_one_text(EncodeBuffers b, int64_t* mapped, int64_t seq)
+// also scans the per-chunk counts into id offsets (into chunk_id_mirror in HBM, then out) and writes the texts' id
+// offsets -- straight into mapped host memory (b.chunk_id_off, b.text_id_off, b.out_ids point there).  The CTA
+// that finishes last (a counter, no waiting) adds {n_chunks, n_ids, status} and, as the very last store behind a
+// system-wide fence, the call number the host polls for.
+__global__ void __launch_bounds__(kMediumThreads) k_finish_small_batch(EncodeBuffers b, int64_t* mapped, int64_t seq)
 {
   __shared__ int scanbuf[33];
   __shared__ int64_t carry_s;
@@ -2649,11 +2649,9 @@ __global__ void __launch_bounds__(kMediumThreads) k_finish_one_text(EncodeBuffer
     }
   }
   if (u == 0) {
-    cta_exclusive_scan_medium(CountsI32{b.chunk_cnt}, C, b.chunk_id_off, scanbuf, &carry_s, stage);
-    if (tid == 0) {
-      b.text_id_off[0] = 0;
-      b.text_id_off[1] = N;
-    }
+    cta_exclusive_scan_medium(CountsI32{b.chunk_cnt}, C, b.chunk_id_mirror, scanbuf, &carry_s, stage);
+    for (int64_t c = tid; c <= C; c += kMediumThreads) b.chunk_id_off[c] = b.chunk_id_mirror[c];
+    for (int64_t t = tid; t <= b.n_texts; t += kMediumThreads) b.text_id_off[t] = b.chunk_id_mirror[b.text_chunk_base[t]];
   }
   __threadfence_system();
   __syncthreads();
@@ -2668,9 +2666,9 @@ __global__ void __launch_bounds__(kMediumThreads) k_finish_one_text(EncodeBuffer
   }
 }
 
-int launch_finish_one_text(const EncodeBuffers& b, int64_t* mapped, int64_t seq, cudaStream_t stream)
+int launch_finish_small_batch(const EncodeBuffers& b, int64_t* mapped, int64_t seq, cudaStream_t stream)
 {
-  k_finish_one_text<<<unsigned(b.n_tiles), kMediumThreads, 0, stream>>>(b, mapped, seq);
+  k_finish_small_batch<<<unsigned(b.n_tiles), kMediumThreads, 0, stream>>>(b, mapped, seq);
   return 1;
 }
 

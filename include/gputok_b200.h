@@ -126,7 +126,7 @@ GTK_API int gtk_table_info_get(const gtk_tokenizer* h, gtk_table_info* out);
  * (cudaEvent pair, as :790-805).  Results stay valid until the next call on
  * the handle; read them with gtk_result_sizes/_view/_copy.
  * An empty batch or a batch of empty texts is not an error: 0 ids, 0 chunks.
- * Small batches (up to 16 KiB and 1024 texts, GTK_MODE_OPT) run as one kernel that reads the text from and
+ * Small batches (up to 8 KiB and 1024 texts, GTK_MODE_OPT) run as one kernel that reads the text from and
  * writes the results to mapped page-locked memory; the call returns when the kernel's completion mark has
  * arrived there (its last store, behind a system-wide fence), which is when the results are complete -- the
  * stream may still be retiring the kernel for a few microseconds.  *kernel_ms is then the kernel's own

@@ -347,7 +347,8 @@ def test_medium_batches_of_many_short_texts(lib, merges_path, oracle):
 def test_path_selector_boundaries(lib, merges_path, oracle):
     """Batches on both sides of every size limit that picks a code path: the single-CTA chunker by search (256
     texts, 2048 chunks, 1024 tiles) and per text (16 384 items, 2048 tiles), the single-CTA scans (16 384 items), the
-    small-batch kernel (16 KiB, 1024 texts) and the sliced host path (8 MiB).  Host and device-resident entry."""
+    small-batch kernel (8 KiB, 1024 texts), the two-launch path (64 KiB, 1024 texts, 4096 chunks) and the sliced
+    host path (8 MiB).  Host and device-resident entry."""
     import torch
 
     src = lib.TextGen(8).text(9 << 20, mix=lib.MIX_STRESS)
@@ -390,12 +391,18 @@ def test_path_selector_boundaries(lib, merges_path, oracle):
     # per text: 2048 / 2049 tiles (8 MiB: device-resident entry only, the host entry slices such a batch)
     assert check("2048 tiles, many texts", 4096, [1024] * 8192, host=False) == 4
     assert check("2049 tiles, many texts", 4096, [1024] * 8192 + [1], host=False) > 4
-    # small-batch kernel: 16 KiB / one byte more; 1024 / 1025 texts
+    # small-batch kernel: 8 KiB / one byte more; 1024 / 1025 texts
+    check("8 KiB", 2048, [8192])
+    check("8 KiB + 1", 2048, [8193])
     check("16 KiB", 2048, [16384])
-    check("16 KiB + 1", 2048, [16385])
     check("32 KiB", 2048, [32768])
     check("1024 texts", 2048, [20] * 1024)
     check("1025 texts", 2048, [20] * 1025)
+    # several texts in two launches (host entry): up to 64 KiB, 1024 texts and 4096 chunks
+    check("50 texts of 1000 bytes", 300, [1000] * 50)
+    check("1024 short texts, some empty", 64, [60, 0, 61, 59] * 256)
+    check("1025 short texts", 64, [60] * 1025)
+    check("ragged texts across tiles", 4096, [5000, 1, 0, 4095, 4097, 8192, 12000, 3])
     # one text in two launches (host entry): up to 64 KiB and 4096 chunks
     check("64 KiB", 2048, [65536])
     check("64 KiB + 1", 2048, [65537])
